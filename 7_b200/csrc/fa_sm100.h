@@ -1,0 +1,29 @@
+// Internal interface between the C-ABI backend and the sm_100a flash-attention
+// forward kernel.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace wave {
+
+struct FaParams {
+  int batch_heads, seq_q, seq_k, head_dim;
+  int causal, is_bf16;
+  float scale;       // softmax scale applied to q.k
+  float scale_log2e; // scale * log2(e): scores enter exp2 as fma(s, scale_log2e, -max)
+  void *O;           // [batch_heads][seq_q][head_dim], same 16-bit type as the inputs
+  float *lse;        // optional [batch_heads][seq_q] natural-log sum-exp, or null
+};
+
+// Builds the tensor maps and launches.  Returns a WAVE_* code (0 = ok).
+int launch_flash_attention(const FaParams &p, const void *Q, const void *K, const void *V, int sm_count,
+                           cudaStream_t stream);
+cudaError_t fa_read_status(int out[4], bool clear);
+
+// Provided by the backend: rank-2/3 tensor map over 16-bit elements with the
+// 128-byte swizzle and zero fill outside the tensor.
+int make_tensor_map_16bit(CUtensorMap *map, int is_bf16, const void *base, int rank, const uint64_t *dims,
+                          const uint64_t *strides_bytes, const uint32_t *box);
+
+} // namespace wave

@@ -1,0 +1,487 @@
+// Tiled f16/bf16 GEMM for sm_100a: D[M x N] = A[M x K] * B[N x K]^T with f32
+// accumulation in tensor memory.  This is the B200 stand-in for the kernel the
+// reference generates as `wmma_f16_matmul_tiled`
+// (python/mlir/dialects/wave_matmul.py:11163-11241) and, in its Stream-K mode,
+// for `gfx950_f16_streamk_gemm` (wave_matmul.py:9987-10150, 11521-11578).
+//
+// Structure (one persistent CTA per SM, 192 threads):
+//   warp 0      TMA producer: A and B tiles -> 128B-swizzled shared memory
+//   warp 1      UMMA issuer (one thread): tcgen05.mma 128 x BN x 16, K-major
+//               operands straight from shared memory, accumulator in TMEM
+//   warps 2..5  epilogue: tcgen05.ld -> round to the C type -> global stores
+// Shared-memory stages are handed over with full/empty mbarriers; the TMEM
+// accumulator is double buffered so the epilogue of tile i overlaps the main
+// loop of tile i+1.  No load uses cluster multicast.
+//
+// Numerics (they decide parity with the reference's CPU check,
+// tools/wave-matmul-calibrate/wave-matmul-calibrate-runner.cpp:1586-1595):
+// operands are used as given (already f16/bf16), products are exact, the
+// accumulator is f32, and there is a single round-to-nearest-even to the C
+// element type at the end.  No alpha/beta: C is overwritten.
+#include "gemm_sm100.h"
+#include "sm100_ptx.cuh"
+
+namespace wave {
+
+__device__ int g_gemm_status[4]; // [0] code, [1] block, [2] role, [3] detail
+
+namespace {
+
+constexpr int kBM = 128;      // UMMA M (rows of the accumulator = TMEM lanes)
+constexpr int kBK = 64;       // 64 16-bit elements = one 128-byte swizzle row
+constexpr int kUmmaK = 16;    // K per tcgen05.mma for 16-bit operands
+constexpr int kThreads = 192; // 6 warps
+constexpr int kEpiThreads = 128;
+
+template <int BN> struct TileCfg {
+  static constexpr int kStages = BN >= 256 ? 4 : BN >= 128 ? 6 : BN >= 64 ? 8 : 10;
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kAccCols = BN < 32 ? 32 : BN; // TMEM columns per accumulator buffer
+  static constexpr int kTmemCols = 2 * kAccCols < 32 ? 32 : 2 * kAccCols;
+  // tiles + barriers + bookkeeping + slack for 1024-byte alignment
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+};
+
+struct Shared {
+  uint64_t full[10];
+  uint64_t empty[10];
+  uint64_t tfull[2];
+  uint64_t tempty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  int last_arriver; // Stream-K: broadcast of the arrival-counter result
+};
+
+__device__ __forceinline__ void report(int code, int role, int detail) {
+  if (atomicCAS(&g_gemm_status[0], 0, code) == 0) {
+    g_gemm_status[1] = static_cast<int>(blockIdx.x);
+    g_gemm_status[2] = role;
+    g_gemm_status[3] = detail;
+  }
+}
+
+// Linear tile id -> (m block, n block) with grouped-M rasterisation, the
+// portable half of the reference's CTA remap (wave_matmul.py:1248-1276):
+// consecutive ids walk down `group_m` row blocks before moving one column
+// block over, so CTAs running at the same time share A and B panels in L2.
+__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int group_m, int &mb, int &nb) {
+  const int per_group = group_m * num_n;
+  const int group = tile / per_group;
+  const int first_m = group * group_m;
+  const int rows = min(num_m - first_m, group_m);
+  const int in_group = tile - group * per_group;
+  mb = first_m + in_group % rows;
+  nb = in_group / rows;
+}
+
+// Balanced contiguous split of `total` iterations over `workers`
+// (wave_matmul.py:88-100, streamk_worker_interval).
+__device__ __forceinline__ void streamk_interval(long long total, int workers, int worker, long long &begin,
+                                                 long long &end) {
+  const long long q = total / workers, r = total % workers;
+  begin = worker * q + min(static_cast<long long>(worker), r);
+  end = begin + q + (worker < r ? 1 : 0);
+}
+// Owner of one iteration (wave_matmul.py:103-116, streamk_owner_for_iteration).
+__device__ __forceinline__ int streamk_owner(long long total, int workers, long long it) {
+  const long long q = total / workers, r = total % workers;
+  const long long large_end = r * (q + 1);
+  if (it < large_end)
+    return static_cast<int>(it / (q + 1));
+  return static_cast<int>(r + (it - large_end) / q);
+}
+// Scratch slot (0 or 1) that `owner` uses for its partial of `tile`
+// (wave_matmul.py:135-159, streamk_worker_segments): partial tiles are
+// numbered in tile order and a contiguous interval has at most two.
+__device__ __forceinline__ int streamk_slot(long long total, int workers, int k_iters, int owner, int tile) {
+  long long b, e;
+  streamk_interval(total, workers, owner, b, e);
+  const long long first_tile = b / k_iters;
+  if (tile == first_tile)
+    return 0;
+  const bool first_partial = (b % k_iters != 0) || (e < (first_tile + 1) * static_cast<long long>(k_iters));
+  return first_partial ? 1 : 0;
+}
+
+struct Segment {
+  int tile, k_begin, k_end; // k in units of kBK iterations
+};
+
+// Work iterator shared by the three roles so that they agree on the sequence
+// of (tile, k range) segments without talking to each other.
+struct WorkIter {
+  const GemmParams &p;
+  long long cur, end; // data-parallel: tile ids (strided); Stream-K: iterations
+  __device__ WorkIter(const GemmParams &params) : p(params) {
+    if (p.streamk_workers > 0) {
+      streamk_interval(static_cast<long long>(p.num_tiles) * p.k_iters, p.streamk_workers, blockIdx.x, cur, end);
+    } else {
+      cur = blockIdx.x;
+      end = p.num_tiles;
+    }
+  }
+  __device__ bool next(Segment &s) {
+    if (cur >= end)
+      return false;
+    if (p.streamk_workers > 0) {
+      const long long tile = cur / p.k_iters;
+      const long long tile_begin = tile * p.k_iters;
+      const long long seg_end = min(end, tile_begin + p.k_iters);
+      s.tile = static_cast<int>(tile);
+      s.k_begin = static_cast<int>(cur - tile_begin);
+      s.k_end = static_cast<int>(seg_end - tile_begin);
+      cur = seg_end;
+    } else {
+      s.tile = static_cast<int>(cur);
+      s.k_begin = 0;
+      s.k_end = p.k_iters;
+      cur += gridDim.x;
+    }
+    return true;
+  }
+};
+
+template <int OUT> struct OutT;
+template <> struct OutT<WAVE_GEMM_OUT_F32> { using type = float; };
+template <> struct OutT<WAVE_GEMM_OUT_F16> { using type = __half; };
+template <> struct OutT<WAVE_GEMM_OUT_BF16> { using type = __nv_bfloat16; };
+
+__device__ __forceinline__ void store_elem(float *p, float v) { *p = v; }
+__device__ __forceinline__ void store_elem(__half *p, float v) { *p = __float2half_rn(v); }
+__device__ __forceinline__ void store_elem(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
+
+// Stores `W` consecutive-n values of row m.  When n is the contiguous
+// direction the values go out as 16-byte vectors; otherwise (m contiguous)
+// each value is a scalar store that coalesces across the warp's 32 rows.
+template <typename T, int W>
+__device__ __forceinline__ void store_row_chunk(const GemmParams &p, int m, int n0, const float (&v)[W]) {
+  if (m >= p.M)
+    return;
+  T *base = reinterpret_cast<T *>(p.C) + static_cast<long long>(m) * p.stride_m +
+            static_cast<long long>(n0) * p.stride_n;
+  if (p.stride_n == 1) {
+    constexpr int per_vec = 16 / sizeof(T);
+#pragma unroll
+    for (int j = 0; j < W; j += per_vec) {
+      if (n0 + j < p.N) { // N is a multiple of 16, so a started vector is whole
+        if constexpr (sizeof(T) == 4) {
+          float4 q = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+          *reinterpret_cast<float4 *>(base + j) = q;
+        } else {
+          T tmp[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e)
+            store_elem(&tmp[e], v[j + e]);
+          *reinterpret_cast<uint4 *>(base + j) = *reinterpret_cast<uint4 *>(tmp);
+        }
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < W; ++j)
+      if (n0 + j < p.N)
+        store_elem(base + static_cast<long long>(j) * p.stride_n, v[j]);
+  }
+}
+
+template <int BN, int OUT>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+            const GemmParams p) {
+  using Cfg = TileCfg<BN>;
+  using T = typename OutT<OUT>::type;
+  constexpr int kStages = Cfg::kStages;
+  constexpr int CW = BN >= 32 ? 32 : 16; // columns per TMEM load
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *tiles = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Shared *sh = reinterpret_cast<Shared *>(tiles + kStages * Cfg::kStageBytes);
+  volatile int *abort_flag = &sh->abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&sh->full[s], 1);
+      mbar_init(&sh->empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&sh->tfull[a], 1);
+      mbar_init(&sh->tempty[a], 4);
+    }
+    sh->abort_flag = 0;
+    sh->last_arriver = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&sh->tmem_base, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = sh->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_a);
+      tma_prefetch_desc(&tmap_b);
+      WorkIter work(p);
+      Segment seg;
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      while (ok && work.next(seg)) {
+        int mb, nb;
+        tile_coords(seg.tile, p.num_m_blocks, p.num_n_blocks, p.group_m, mb, nb);
+        for (int kb = seg.k_begin; kb < seg.k_end; ++kb) {
+          if (!mbar_wait(&sh->empty[stage], phase ^ 1, abort_flag)) {
+            report(kStatusWaitTimeout, 0, stage);
+            ok = false;
+            break;
+          }
+          uint8_t *a_dst = tiles + stage * Cfg::kStageBytes;
+          uint8_t *b_dst = a_dst + Cfg::kABytes;
+          mbar_arrive_expect_tx(&sh->full[stage], Cfg::kStageBytes);
+          tma_load_2d(a_dst, &tmap_a, &sh->full[stage], kb * kBK, mb * kBM);
+          tma_load_2d(b_dst, &tmap_b, &sh->full[stage], kb * kBK, nb * BN);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok)
+        bounded_delay(1 << 21); // let copies in flight land before teardown
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------- UMMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_f16 = umma_idesc_f16(kBM, BN, 0);
+      constexpr uint32_t idesc_bf16 = umma_idesc_f16(kBM, BN, 1);
+      const uint32_t idesc = p.in_type == WAVE_GEMM_IN_BF16 ? idesc_bf16 : idesc_f16;
+      WorkIter work(p);
+      Segment seg;
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      while (ok && work.next(seg)) {
+        if (!mbar_wait(&sh->tempty[acc], acc_phase ^ 1, abort_flag)) {
+          report(kStatusWaitTimeout, 1, 100 + acc);
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * Cfg::kAccCols);
+        for (int kb = seg.k_begin; kb < seg.k_end; ++kb) {
+          if (!mbar_wait(&sh->full[stage], phase, abort_flag)) {
+            report(kStatusWaitTimeout, 1, stage);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(tiles + stage * Cfg::kStageBytes);
+          const uint64_t a_desc = umma_desc_kmajor_sw128(a_addr);
+          const uint64_t b_desc = umma_desc_kmajor_sw128(a_addr + Cfg::kABytes);
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            // +32 bytes per K step inside the 128-byte swizzle row (>>4 = 2)
+            umma_ss(tmem_d, a_desc + static_cast<uint64_t>(k * 2), b_desc + static_cast<uint64_t>(k * 2), idesc,
+                    (kb > seg.k_begin || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&sh->empty[stage]); // frees the stage once the MMAs have read it
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok)
+          break;
+        umma_commit(&sh->tfull[acc]); // accumulator complete
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;          // TMEM lane quarter this warp may read
+    const int row_in_tile = quarter * 32 + lane;
+    const int epi_tid = row_in_tile;       // 0..127, unique per epilogue thread
+    WorkIter work(p);
+    Segment seg;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const long long total_iters = static_cast<long long>(p.num_tiles) * p.k_iters;
+    while (work.next(seg)) {
+      int mb, nb;
+      tile_coords(seg.tile, p.num_m_blocks, p.num_n_blocks, p.group_m, mb, nb);
+      if (!mbar_wait(&sh->tfull[acc], acc_phase, abort_flag)) {
+        if (lane == 0)
+          report(kStatusWaitTimeout, 2, 200 + acc);
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                             static_cast<uint32_t>(acc * Cfg::kAccCols);
+      const int m = mb * kBM + row_in_tile;
+      const bool whole = seg.k_begin == 0 && seg.k_end == p.k_iters;
+      if (whole) {
+#pragma unroll 1
+        for (int c = 0; c < BN; c += CW) {
+          uint32_t r[CW];
+          if constexpr (CW == 32)
+            tmem_ld_32x32b_x32(taddr + c, r);
+          else
+            tmem_ld_32x32b_x16(taddr + c, r);
+          tmem_ld_wait();
+          float v[CW];
+#pragma unroll
+          for (int j = 0; j < CW; ++j)
+            v[j] = __uint_as_float(r[j]);
+          store_row_chunk<T, CW>(p, m, nb * BN + c, v);
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0)
+          mbar_arrive(&sh->tempty[acc]);
+      } else {
+        // Stream-K partial: raw f32 accumulator -> this worker's scratch slot,
+        // element (row, col) at col*128 + row so a warp writes 128 contiguous
+        // bytes.  Then count the arrival; the last arriver reduces.
+        const int slot = streamk_slot(total_iters, p.streamk_workers, p.k_iters, blockIdx.x, seg.tile);
+        float *mine = p.scratch + (static_cast<size_t>(blockIdx.x) * 2 + slot) * (kBM * BN);
+#pragma unroll 1
+        for (int c = 0; c < BN; c += CW) {
+          uint32_t r[CW];
+          if constexpr (CW == 32)
+            tmem_ld_32x32b_x32(taddr + c, r);
+          else
+            tmem_ld_32x32b_x16(taddr + c, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < CW; ++j)
+            mine[(c + j) * kBM + row_in_tile] = __uint_as_float(r[j]);
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0)
+          mbar_arrive(&sh->tempty[acc]); // TMEM buffer is free; the rest is global memory only
+        __threadfence();
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+        const long long tile_begin = static_cast<long long>(seg.tile) * p.k_iters;
+        const int first_owner = streamk_owner(total_iters, p.streamk_workers, tile_begin);
+        const int last_owner = streamk_owner(total_iters, p.streamk_workers, tile_begin + p.k_iters - 1);
+        const int parts = last_owner - first_owner + 1;
+        if (epi_tid == 0) {
+          const int old = atomicAdd(&p.counters[seg.tile], 1);
+          sh->last_arriver = (old + 1 == parts) ? 1 : 0;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+        const bool last = sh->last_arriver != 0;
+        if (last) {
+          __threadfence();
+          // Fixed order: ascending owner id, starting from zero
+          // (wave_matmul.py:9756-9784), so the result is run-to-run identical.
+#pragma unroll 1
+          for (int c = 0; c < BN; c += CW) {
+            float v[CW];
+#pragma unroll
+            for (int j = 0; j < CW; ++j)
+              v[j] = 0.0f;
+            for (int owner = first_owner; owner <= last_owner; ++owner) {
+              const int oslot = streamk_slot(total_iters, p.streamk_workers, p.k_iters, owner, seg.tile);
+              const float *src = p.scratch + (static_cast<size_t>(owner) * 2 + oslot) * (kBM * BN);
+#pragma unroll
+              for (int j = 0; j < CW; ++j)
+                v[j] += __ldcg(&src[(c + j) * kBM + row_in_tile]);
+            }
+            store_row_chunk<T, CW>(p, m, nb * BN + c, v);
+          }
+          if (epi_tid == 0)
+            atomicAdd(&p.counters[seg.tile], -parts); // back to zero for the next launch
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory"); // sh->last_arriver may be rewritten
+      }
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+template <int BN, int OUT>
+cudaError_t launch_one(const CUtensorMap &ta, const CUtensorMap &tb, const GemmParams &p, int grid,
+                       cudaStream_t stream) {
+  using Cfg = TileCfg<BN>;
+  // The attribute belongs to the current device's context, so it is set on
+  // every launch rather than cached per process.
+  cudaError_t err =
+      cudaFuncSetAttribute(gemm_kernel<BN, OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+  if (err != cudaSuccess)
+    return err;
+  gemm_kernel<BN, OUT><<<grid, kThreads, Cfg::kSmemBytes, stream>>>(ta, tb, p);
+  return cudaGetLastError();
+}
+
+template <int BN>
+cudaError_t launch_bn(const CUtensorMap &ta, const CUtensorMap &tb, const GemmParams &p, int grid,
+                      cudaStream_t stream) {
+  switch (p.out_type) {
+  case WAVE_GEMM_OUT_F32:
+    return launch_one<BN, WAVE_GEMM_OUT_F32>(ta, tb, p, grid, stream);
+  case WAVE_GEMM_OUT_F16:
+    return launch_one<BN, WAVE_GEMM_OUT_F16>(ta, tb, p, grid, stream);
+  case WAVE_GEMM_OUT_BF16:
+    return launch_one<BN, WAVE_GEMM_OUT_BF16>(ta, tb, p, grid, stream);
+  }
+  return cudaErrorInvalidValue;
+}
+
+} // namespace
+
+int gemm_tile_m() { return kBM; }
+int gemm_tile_k() { return kBK; }
+
+cudaError_t launch_gemm(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, const GemmParams &p, int tile_n,
+                        int grid, cudaStream_t stream) {
+  switch (tile_n) {
+  case 16:
+    return launch_bn<16>(tmap_a, tmap_b, p, grid, stream);
+  case 32:
+    return launch_bn<32>(tmap_a, tmap_b, p, grid, stream);
+  case 64:
+    return launch_bn<64>(tmap_a, tmap_b, p, grid, stream);
+  case 128:
+    return launch_bn<128>(tmap_a, tmap_b, p, grid, stream);
+  case 256:
+    return launch_bn<256>(tmap_a, tmap_b, p, grid, stream);
+  }
+  return cudaErrorInvalidValue;
+}
+
+cudaError_t gemm_read_status(int out[4], bool clear) {
+  cudaError_t err = cudaMemcpyFromSymbol(out, g_gemm_status, sizeof(int) * 4);
+  if (err == cudaSuccess && clear) {
+    int zero[4] = {0, 0, 0, 0};
+    err = cudaMemcpyToSymbol(g_gemm_status, zero, sizeof(zero));
+  }
+  return err;
+}
+
+} // namespace wave

@@ -1,0 +1,35 @@
+// Internal interface between the C-ABI backend and the sm_100a GEMM kernel.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#define WAVE_GEMM_IN_F16 0
+#define WAVE_GEMM_IN_BF16 1
+#define WAVE_GEMM_OUT_F32 0
+#define WAVE_GEMM_OUT_F16 1
+#define WAVE_GEMM_OUT_BF16 2
+
+namespace wave {
+
+// Kernel-space problem: D[M x N] = A[M x K] * B[N x K]^T.  The backend may
+// have swapped the caller's operands (skinny M), in which case stride_m and
+// stride_n are swapped too and the caller's C comes out in its own layout.
+struct GemmParams {
+  int M, N, K;
+  void *C;
+  long long stride_m, stride_n; // element strides of D in the output buffer
+  int in_type, out_type;
+  int num_m_blocks, num_n_blocks, num_tiles, k_iters;
+  int group_m;
+  int streamk_workers; // 0: persistent data-parallel tiles; >0: Stream-K with that grid
+  float *scratch;      // Stream-K: [workers][2][128 x tile_n] f32 partial tiles
+  int *counters;       // Stream-K: one arrival counter per output tile, zero on entry and exit
+};
+
+int gemm_tile_m();
+int gemm_tile_k();
+cudaError_t launch_gemm(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, const GemmParams &p, int tile_n,
+                        int grid, cudaStream_t stream);
+cudaError_t gemm_read_status(int out[4], bool clear);
+
+} // namespace wave

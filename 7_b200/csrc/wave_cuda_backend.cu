@@ -1,0 +1,647 @@
+// Host side of libwave_cuda.so: the C ABI declared in include/wave_cuda.h.
+// It is the CUDA sibling of the reference's runtime/wave_runtime.cpp (the
+// memref -> pointer shims are restated here) plus what the reference's
+// calibrate runners do on the host around a launch: argument validation
+// (python/mlir/dialects/wave_matmul.py:533-619), launch geometry
+// (wave-matmul-calibrate-runner.cpp:1744-1764), Stream-K workspace sizing
+// (runner.cpp:393-408) and the kernel-argument blocks (runner.cpp:1790-1816).
+// There is no CPU fallback anywhere in this file.
+#include "../../include/wave_cuda.h"
+#include "fa_sm100.h"
+#include "gemm_sm100.h"
+
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int fail(int code, const char *fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  g_last_error = buf;
+  return code;
+}
+
+int cuda_fail(cudaError_t err, const char *what) {
+  return fail(WAVE_E_CUDA, "%s: %s", what, cudaGetErrorString(err));
+}
+
+bool is_pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
+
+// ---------------------------------------------------------------- tensor maps
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+} // namespace
+
+namespace wave {
+
+// rank-2 or rank-3 map over 16-bit elements, 128-byte swizzle, zero fill
+// outside the tensor.  dims/strides innermost first; strides in bytes for
+// dims 1.. (dim 0 is contiguous).
+int make_tensor_map_16bit(CUtensorMap *map, int is_bf16, const void *base, int rank, const uint64_t *dims,
+                          const uint64_t *strides_bytes, const uint32_t *box) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn)
+    return fail(WAVE_E_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t gdim[3], gstr[2];
+  cuuint32_t bdim[3], estr[3];
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    bdim[i] = box[i];
+    estr[i] = 1;
+  }
+  for (int i = 0; i + 1 < rank; ++i)
+    gstr[i] = strides_bytes[i];
+  CUresult r = fn(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                  static_cast<cuuint32_t>(rank), const_cast<void *>(base), gdim, gstr, bdim, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(WAVE_E_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (rank %d, dims %llu x %llu, box %u x %u)",
+                static_cast<int>(r), rank, static_cast<unsigned long long>(dims[0]),
+                static_cast<unsigned long long>(dims[1]), box[0], box[1]);
+  return WAVE_OK;
+}
+
+} // namespace wave
+
+namespace {
+
+int sm_count(int *out) {
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess)
+    return cuda_fail(err, "cudaGetDevice");
+  int sms = 0;
+  err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (err != cudaSuccess)
+    return cuda_fail(err, "cudaDeviceGetAttribute");
+  *out = sms;
+  return WAVE_OK;
+}
+
+int elem_size(int type) { return type == WAVE_F32 ? 4 : 2; }
+
+// ---------------------------------------------------------------- GEMM plan
+struct GemmPlan {
+  bool swapped;       // kernel computes C^T = B * A^T (skinny M)
+  int Mk, Nk;         // kernel-space extents
+  int tile_n;         // kernel-space tile columns
+  int num_m, num_n, k_iters;
+  int grid;
+  int streamk_workers; // 0 = data-parallel
+  size_t scratch_bytes, counter_bytes;
+};
+
+int snap_tile_n(int want) {
+  const int options[5] = {16, 32, 64, 128, 256};
+  for (int o : options)
+    if (want <= o)
+      return o;
+  return 256;
+}
+
+// `sms` <= 0 means "unknown" (no device query): only legal when the
+// descriptor does not ask for automatic Stream-K.
+int make_plan(const wave_gemm_desc &d, int sms, bool have_workspace, GemmPlan *plan) {
+  const int tile_m = wave::gemm_tile_m(), tile_k = wave::gemm_tile_k();
+  const int want_m = 16 * d.bm * d.wave_m_tiles, want_n = 16 * d.bn * d.wave_n_tiles;
+  GemmPlan p{};
+  // A 128-row UMMA wastes most of its rows on a skinny M; put N on the rows
+  // instead and M on the (narrow) column tile.
+  p.swapped = d.M < tile_m && d.N > d.M;
+  p.Mk = p.swapped ? d.N : d.M;
+  p.Nk = p.swapped ? d.M : d.N;
+  const int want = p.swapped ? want_m : want_n;
+  p.tile_n = snap_tile_n(want);
+  const int cap = snap_tile_n(p.Nk);
+  if (p.tile_n > cap)
+    p.tile_n = cap;
+  p.num_m = (p.Mk + tile_m - 1) / tile_m;
+  p.num_n = (p.Nk + p.tile_n - 1) / p.tile_n;
+  p.k_iters = (d.K + tile_k - 1) / tile_k;
+  const long long tiles = static_cast<long long>(p.num_m) * p.num_n;
+  const long long total_iters = tiles * p.k_iters;
+  if (tiles > 0x7FFFFFFF)
+    return fail(WAVE_E_INVALID, "too many output tiles");
+  int workers = d.streamk_workers;
+  if (workers == 0) { // auto
+    workers = 1;
+    if (sms > 0 && have_workspace) {
+      const long long waves = (tiles + sms - 1) / sms;
+      const double efficiency = static_cast<double>(tiles) / static_cast<double>(waves * sms);
+      if (efficiency < 0.8 && total_iters >= sms && p.k_iters >= 8)
+        workers = sms;
+    }
+  }
+  if (workers > 1) {
+    if (workers > total_iters)
+      return fail(WAVE_E_INVALID, "workers must be in [1, total_iterations]; got workers=%d, total_iterations=%lld",
+                  workers, total_iters);
+    p.streamk_workers = workers;
+    p.grid = workers;
+    p.scratch_bytes = static_cast<size_t>(workers) * 2 * tile_m * p.tile_n * sizeof(float);
+    p.counter_bytes = static_cast<size_t>(tiles) * sizeof(int);
+  } else {
+    p.streamk_workers = 0;
+    p.grid = sms > 0 ? static_cast<int>(tiles < sms ? tiles : sms) : static_cast<int>(tiles);
+  }
+  *plan = p;
+  return WAVE_OK;
+}
+
+// ------------------------------------------------------- host staging arena
+struct Arena {
+  void *ptr = nullptr;
+  size_t bytes = 0;
+  int device = -1;
+};
+std::mutex g_arena_mu;
+Arena g_arena;
+
+int arena_reserve(size_t bytes, void **out) {
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess)
+    return cuda_fail(err, "cudaGetDevice");
+  if (g_arena.device != dev || g_arena.bytes < bytes) {
+    if (g_arena.ptr && g_arena.device == dev)
+      cudaFree(g_arena.ptr);
+    g_arena = Arena{};
+    err = cudaMalloc(&g_arena.ptr, bytes);
+    if (err != cudaSuccess)
+      return cuda_fail(err, "cudaMalloc (host-call staging)");
+    g_arena.bytes = bytes;
+    g_arena.device = dev;
+  }
+  *out = g_arena.ptr;
+  return WAVE_OK;
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct FnHandle {
+  int kind; // 0 gemm, 1 stream-K gemm, 2 flash attention
+  wave_gemm_desc gemm;
+  wave_fa_desc fa;
+};
+
+struct MemRef1D {
+  void *base;
+  char *data;
+  int64_t offset;
+  int64_t size;
+  int64_t stride;
+};
+template <int ElemBytes> void *memref_ptr(void *m) {
+  MemRef1D *d = static_cast<MemRef1D *>(m);
+  return d->data + d->offset * ElemBytes;
+}
+
+} // namespace
+
+extern "C" {
+
+const char *wave_cuda_last_error(void) { return g_last_error.c_str(); }
+const char *wave_cuda_version(void) { return "wave_cuda sm_100a 0.1"; }
+
+// runtime/wave_runtime.cpp:35-40, 46-74: data + offset (in elements).
+void *_mlir_ciface_wave_memref_to_ptr_global_i32(void *m) { return memref_ptr<4>(m); }
+void *_mlir_ciface_wave_memref_to_ptr_global_i8(void *m) { return memref_ptr<1>(m); }
+void *_mlir_ciface_wave_memref_to_ptr_global_f32(void *m) { return memref_ptr<4>(m); }
+void *_mlir_ciface_wave_memref_to_ptr_global_f16(void *m) { return memref_ptr<2>(m); }
+void *_mlir_ciface_wave_memref_to_ptr_global_bf16(void *m) { return memref_ptr<2>(m); }
+void *_mlir_ciface_wave_memref_to_ptr_global_i64(void *m) { return memref_ptr<8>(m); }
+void *_mlir_ciface_wave_memref_to_ptr_global_f64(void *m) { return memref_ptr<8>(m); }
+
+void wave_cuda_gemm_desc_init(wave_gemm_desc *d, int M, int N, int K) {
+  memset(d, 0, sizeof *d);
+  d->M = M;
+  d->N = N;
+  d->K = K;
+  d->bm = 1;
+  d->bn = 2;
+  d->wave_m_tiles = d->wave_n_tiles = d->wave_k_tiles = 1;
+  d->in_type = WAVE_F16;
+  d->out_type = WAVE_F32;
+  d->out_layout = WAVE_ROW_MAJOR;
+  d->cta_group_m = 1;
+  d->streamk_workers = 1;
+  d->ldc = 0;
+}
+
+int wave_cuda_gemm_validate(const wave_gemm_desc *d) {
+  if (!d)
+    return fail(WAVE_E_INVALID, "descriptor is null");
+  // wave_matmul.py:533-536
+  const int dims[3] = {d->M, d->N, d->K};
+  const char *names[3] = {"M", "N", "K"};
+  for (int i = 0; i < 3; ++i)
+    if (dims[i] <= 0 || dims[i] % 16 != 0)
+      return fail(WAVE_E_INVALID, "%s must be a positive multiple of 16; got %d", names[i], dims[i]);
+  // wave_matmul.py:537-538
+  if (d->bm < 1 || d->bn < 1)
+    return fail(WAVE_E_INVALID, "BM and BN must be >= 1; got BM=%d, BN=%d", d->bm, d->bn);
+  // wave_matmul.py:556-560
+  if (d->cta_group_m < 1)
+    return fail(WAVE_E_INVALID, "cta_group_m must be >= 1; got %d", d->cta_group_m);
+  // wave_matmul.py:563-570
+  if (d->wave_m_tiles < 1 || d->wave_n_tiles < 1 || d->wave_k_tiles < 1)
+    return fail(WAVE_E_INVALID,
+                "wave_m_tiles, wave_n_tiles and wave_k_tiles must be >= 1; got wave_m_tiles=%d, "
+                "wave_n_tiles=%d, wave_k_tiles=%d",
+                d->wave_m_tiles, d->wave_n_tiles, d->wave_k_tiles);
+  if (d->out_type != WAVE_F32 && d->out_type != WAVE_F16 && d->out_type != WAVE_BF16)
+    return fail(WAVE_E_INVALID, "output_type must be one of f32, f16, bf16; got %d", d->out_type);
+  if (d->out_layout != WAVE_ROW_MAJOR && d->out_layout != WAVE_COL_MAJOR)
+    return fail(WAVE_E_UNSUPPORTED, "output_layout must be one of row-major, column-major; got %d "
+                                    "(tile-packed output is not implemented by this backend)",
+                d->out_layout);
+  if (d->in_type != WAVE_F16 && d->in_type != WAVE_BF16)
+    return fail(WAVE_E_UNSUPPORTED, "input_type must be one of f16, bf16; got %d (mxfp4 is outside this backend)",
+                d->in_type);
+  // wave_matmul.py:575-579
+  if (!is_pow2(d->bn))
+    return fail(WAVE_E_INVALID,
+                "BN must be a positive power of two (for the wave-id decomposition); got BN=%d", d->bn);
+  // wave_matmul.py:580-591
+  const int m_tiles = d->bm * d->wave_m_tiles, n_tiles = d->bn * d->wave_n_tiles;
+  if ((d->M / 16) % m_tiles != 0)
+    return fail(WAVE_E_INVALID, "BM * wave_m_tiles (=%d) must divide M/16 (=%d)", m_tiles, d->M / 16);
+  if ((d->N / 16) % n_tiles != 0)
+    return fail(WAVE_E_INVALID, "BN * wave_n_tiles (=%d) must divide N/16 (=%d)", n_tiles, d->N / 16);
+  // wave_matmul.py:597-601 with k_tile = 16
+  if ((d->K / 16) % d->wave_k_tiles != 0)
+    return fail(WAVE_E_INVALID, "wave_k_tiles (=%d) must divide K/16 (=%d)", d->wave_k_tiles, d->K / 16);
+  // wave_matmul.py:603-607
+  if (d->bm * d->bn > 32)
+    return fail(WAVE_E_INVALID, "BM * BN must be <= 32 (RDNA3 workgroup wave cap); got BM=%d, BN=%d (product=%d)",
+                d->bm, d->bn, d->bm * d->bn);
+  // wave_matmul.py:615-619
+  const int m_blocks = (d->M / 16) / m_tiles;
+  if (m_blocks % d->cta_group_m != 0)
+    return fail(WAVE_E_INVALID,
+                "cta_group_m currently requires M_blocks to divide evenly; got M_blocks=%d, cta_group_m=%d",
+                m_blocks, d->cta_group_m);
+  if (d->streamk_workers < 0)
+    return fail(WAVE_E_INVALID, "streamk_workers must be >= 0; got %d", d->streamk_workers);
+  const int min_ld = d->out_layout == WAVE_ROW_MAJOR ? d->N : d->M;
+  if (d->ldc != 0 && (d->ldc < min_ld || d->ldc % 16 != 0))
+    return fail(WAVE_E_INVALID, "ldc must be 0 or a multiple of 16 that is >= %d; got %d", min_ld, d->ldc);
+  return WAVE_OK;
+}
+
+int wave_cuda_gemm_workspace_bytes(const wave_gemm_desc *d, size_t *scratch_bytes, size_t *counter_bytes) {
+  int rc = wave_cuda_gemm_validate(d);
+  if (rc != WAVE_OK)
+    return rc;
+  int sms = -1;
+  if (d->streamk_workers == 0 && (rc = sm_count(&sms)) != WAVE_OK)
+    return rc;
+  GemmPlan plan;
+  if ((rc = make_plan(*d, sms, true, &plan)) != WAVE_OK)
+    return rc;
+  if (scratch_bytes)
+    *scratch_bytes = plan.scratch_bytes;
+  if (counter_bytes)
+    *counter_bytes = plan.counter_bytes;
+  return WAVE_OK;
+}
+
+int wave_cuda_gemm_plan(const wave_gemm_desc *d, int *tile_m, int *tile_n, int *grid, int *streamk_workers,
+                        int *swapped) {
+  int rc = wave_cuda_gemm_validate(d);
+  if (rc != WAVE_OK)
+    return rc;
+  int sms = 0;
+  if ((rc = sm_count(&sms)) != WAVE_OK)
+    return rc;
+  GemmPlan plan;
+  if ((rc = make_plan(*d, sms, true, &plan)) != WAVE_OK)
+    return rc;
+  if (tile_m)
+    *tile_m = wave::gemm_tile_m();
+  if (tile_n)
+    *tile_n = plan.tile_n;
+  if (grid)
+    *grid = plan.grid;
+  if (streamk_workers)
+    *streamk_workers = plan.streamk_workers;
+  if (swapped)
+    *swapped = plan.swapped ? 1 : 0;
+  return WAVE_OK;
+}
+
+int wave_cuda_gemm(const wave_gemm_desc *d, const void *A, const void *B, void *C, void *workspace,
+                   void *stream) {
+  int rc = wave_cuda_gemm_validate(d);
+  if (rc != WAVE_OK)
+    return rc;
+  if (!A || !B || !C)
+    return fail(WAVE_E_INVALID, "A, B and C must be non-null device pointers");
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)
+    return fail(WAVE_E_INVALID, "A, B and C must be 16-byte aligned");
+  int sms = 0;
+  if ((rc = sm_count(&sms)) != WAVE_OK)
+    return rc;
+  GemmPlan plan;
+  if ((rc = make_plan(*d, sms, workspace != nullptr, &plan)) != WAVE_OK)
+    return rc;
+  if (plan.streamk_workers > 0 && !workspace)
+    return fail(WAVE_E_INVALID, "Stream-K with %d workers needs a workspace of %zu + %zu bytes",
+                plan.streamk_workers, plan.scratch_bytes, plan.counter_bytes);
+
+  const int tile_m = wave::gemm_tile_m(), tile_k = wave::gemm_tile_k();
+  const void *Ak = plan.swapped ? B : A;
+  const void *Bk = plan.swapped ? A : B;
+  CUtensorMap ta, tb;
+  const int bf16 = d->in_type == WAVE_BF16;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(d->K), static_cast<uint64_t>(plan.Mk)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(d->K) * 2};
+    const uint32_t box[2] = {static_cast<uint32_t>(tile_k), static_cast<uint32_t>(tile_m)};
+    if ((rc = wave::make_tensor_map_16bit(&ta, bf16, Ak, 2, dims, strides, box)) != WAVE_OK)
+      return rc;
+  }
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(d->K), static_cast<uint64_t>(plan.Nk)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(d->K) * 2};
+    const uint32_t box[2] = {static_cast<uint32_t>(tile_k), static_cast<uint32_t>(plan.tile_n)};
+    if ((rc = wave::make_tensor_map_16bit(&tb, bf16, Bk, 2, dims, strides, box)) != WAVE_OK)
+      return rc;
+  }
+
+  wave::GemmParams p{};
+  p.M = plan.Mk;
+  p.N = plan.Nk;
+  p.K = d->K;
+  p.C = C;
+  const long long ld = d->ldc ? d->ldc : (d->out_layout == WAVE_ROW_MAJOR ? d->N : d->M);
+  // caller-space strides of C[m][n]
+  long long sm = d->out_layout == WAVE_ROW_MAJOR ? ld : 1;
+  long long sn = d->out_layout == WAVE_ROW_MAJOR ? 1 : ld;
+  p.stride_m = plan.swapped ? sn : sm; // kernel rows are the caller's n when swapped
+  p.stride_n = plan.swapped ? sm : sn;
+  p.in_type = bf16 ? WAVE_GEMM_IN_BF16 : WAVE_GEMM_IN_F16;
+  p.out_type = d->out_type == WAVE_F32 ? WAVE_GEMM_OUT_F32 : d->out_type == WAVE_F16 ? WAVE_GEMM_OUT_F16
+                                                                                       : WAVE_GEMM_OUT_BF16;
+  p.num_m_blocks = plan.num_m;
+  p.num_n_blocks = plan.num_n;
+  p.num_tiles = plan.num_m * plan.num_n;
+  p.k_iters = plan.k_iters;
+  // The descriptor's cta_group_m counts the reference's (smaller) workgroup
+  // tiles; keep the same number of rows per group, at least one 128-row block.
+  {
+    long long rows = static_cast<long long>(d->cta_group_m) * 16 * d->bm * d->wave_m_tiles;
+    int g = static_cast<int>(rows / tile_m);
+    if (d->cta_group_m == 1)
+      g = 16; // the reference's "no grouping" default: use the backend's own
+    if (g < 1)
+      g = 1;
+    if (g > plan.num_m)
+      g = plan.num_m;
+    p.group_m = g;
+  }
+  p.streamk_workers = plan.streamk_workers;
+  p.scratch = static_cast<float *>(workspace);
+  p.counters = workspace ? reinterpret_cast<int *>(static_cast<char *>(workspace) + plan.scratch_bytes) : nullptr;
+
+  cudaError_t err = wave::launch_gemm(ta, tb, p, plan.tile_n, plan.grid, static_cast<cudaStream_t>(stream));
+  if (err != cudaSuccess)
+    return cuda_fail(err, "gemm launch");
+  return WAVE_OK;
+}
+
+int wave_cuda_gemm_host(const wave_gemm_desc *d, const void *A_host, const void *B_host, void *C_host,
+                        void *stream) {
+  int rc = wave_cuda_gemm_validate(d);
+  if (rc != WAVE_OK)
+    return rc;
+  if (!A_host || !B_host || !C_host)
+    return fail(WAVE_E_INVALID, "A, B and C must be non-null host pointers");
+  size_t scratch = 0, counters = 0;
+  if ((rc = wave_cuda_gemm_workspace_bytes(d, &scratch, &counters)) != WAVE_OK)
+    return rc;
+  const size_t a_bytes = static_cast<size_t>(d->M) * d->K * 2, b_bytes = static_cast<size_t>(d->N) * d->K * 2;
+  const size_t ld = d->ldc ? d->ldc : (d->out_layout == WAVE_ROW_MAJOR ? d->N : d->M);
+  const size_t c_bytes = ld * (d->out_layout == WAVE_ROW_MAJOR ? d->M : d->N) * elem_size(d->out_type);
+  const size_t off_b = align_up(a_bytes, 256), off_c = off_b + align_up(b_bytes, 256);
+  const size_t off_ws = off_c + align_up(c_bytes, 256);
+  const size_t total = off_ws + align_up(scratch, 256) + align_up(counters, 256);
+  std::lock_guard<std::mutex> lock(g_arena_mu);
+  void *base = nullptr;
+  if ((rc = arena_reserve(total, &base)) != WAVE_OK)
+    return rc;
+  char *dev = static_cast<char *>(base);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t err;
+  if ((err = cudaMemcpyAsync(dev, A_host, a_bytes, cudaMemcpyHostToDevice, s)) != cudaSuccess)
+    return cuda_fail(err, "copy A to device");
+  if ((err = cudaMemcpyAsync(dev + off_b, B_host, b_bytes, cudaMemcpyHostToDevice, s)) != cudaSuccess)
+    return cuda_fail(err, "copy B to device");
+  void *ws = nullptr;
+  if (scratch + counters > 0) {
+    ws = dev + off_ws;
+    if ((err = cudaMemsetAsync(dev + off_ws + scratch, 0, counters, s)) != cudaSuccess)
+      return cuda_fail(err, "clear Stream-K counters");
+  }
+  if ((rc = wave_cuda_gemm(d, dev, dev + off_b, dev + off_c, ws, stream)) != WAVE_OK)
+    return rc;
+  if ((err = cudaMemcpyAsync(C_host, dev + off_c, c_bytes, cudaMemcpyDeviceToHost, s)) != cudaSuccess)
+    return cuda_fail(err, "copy C to host");
+  if ((err = cudaStreamSynchronize(s)) != cudaSuccess)
+    return cuda_fail(err, "synchronise after GEMM");
+  return WAVE_OK;
+}
+
+// ------------------------------------------------------------ flash attention
+int wave_cuda_fa_validate(const wave_fa_desc *d) {
+  if (!d)
+    return fail(WAVE_E_INVALID, "descriptor is null");
+  if (d->batch <= 0 || d->heads <= 0)
+    return fail(WAVE_E_INVALID, "batch and heads must be positive; got batch=%d, heads=%d", d->batch, d->heads);
+  if (d->seq_q <= 0 || d->seq_k <= 0 || d->seq_q % 16 != 0 || d->seq_k % 16 != 0)
+    return fail(WAVE_E_INVALID, "sequence lengths must be positive multiples of 16; got seq_q=%d, seq_k=%d",
+                d->seq_q, d->seq_k);
+  if (d->head_dim != 128 && d->head_dim != 64)
+    return fail(WAVE_E_UNSUPPORTED, "head_dim must be 128 or 64; got %d", d->head_dim);
+  if (d->io_type != WAVE_BF16 && d->io_type != WAVE_F16)
+    return fail(WAVE_E_UNSUPPORTED, "io_type must be bf16 or f16; got %d", d->io_type);
+  if (d->causal && d->seq_q != d->seq_k)
+    return fail(WAVE_E_UNSUPPORTED, "causal attention requires seq_q == seq_k; got %d and %d", d->seq_q, d->seq_k);
+  if (!(d->scale >= 0.0f) || std::isinf(d->scale))
+    return fail(WAVE_E_INVALID, "scale must be finite and >= 0 (0 selects 1/sqrt(head_dim))");
+  return WAVE_OK;
+}
+
+int wave_cuda_flash_attention_fwd(const wave_fa_desc *d, const void *Q, const void *K, const void *V, void *O,
+                                  float *lse, void *stream) {
+  int rc = wave_cuda_fa_validate(d);
+  if (rc != WAVE_OK)
+    return rc;
+  if (!Q || !K || !V || !O)
+    return fail(WAVE_E_INVALID, "Q, K, V and O must be non-null device pointers");
+  if ((reinterpret_cast<uintptr_t>(Q) | reinterpret_cast<uintptr_t>(K) | reinterpret_cast<uintptr_t>(V) |
+       reinterpret_cast<uintptr_t>(O)) & 15)
+    return fail(WAVE_E_INVALID, "Q, K, V and O must be 16-byte aligned");
+  wave::FaParams p{};
+  p.batch_heads = d->batch * d->heads;
+  p.seq_q = d->seq_q;
+  p.seq_k = d->seq_k;
+  p.head_dim = d->head_dim;
+  p.causal = d->causal ? 1 : 0;
+  p.is_bf16 = d->io_type == WAVE_BF16;
+  const double scale = d->scale > 0.0f ? static_cast<double>(d->scale) : 1.0 / std::sqrt(static_cast<double>(d->head_dim));
+  p.scale = static_cast<float>(scale);
+  p.scale_log2e = static_cast<float>(scale * 1.4426950408889634);
+  p.O = O;
+  p.lse = lse;
+  int sms = 0;
+  if ((rc = sm_count(&sms)) != WAVE_OK)
+    return rc;
+  rc = wave::launch_flash_attention(p, Q, K, V, sms, static_cast<cudaStream_t>(stream));
+  return rc;
+}
+
+int wave_cuda_flash_attention_fwd_host(const wave_fa_desc *d, const void *Q_host, const void *K_host,
+                                       const void *V_host, void *O_host, void *stream) {
+  int rc = wave_cuda_fa_validate(d);
+  if (rc != WAVE_OK)
+    return rc;
+  if (!Q_host || !K_host || !V_host || !O_host)
+    return fail(WAVE_E_INVALID, "Q, K, V and O must be non-null host pointers");
+  const size_t bh = static_cast<size_t>(d->batch) * d->heads;
+  const size_t q_bytes = bh * d->seq_q * d->head_dim * 2, kv_bytes = bh * d->seq_k * d->head_dim * 2;
+  const size_t off_k = align_up(q_bytes, 256), off_v = off_k + align_up(kv_bytes, 256);
+  const size_t off_o = off_v + align_up(kv_bytes, 256), total = off_o + align_up(q_bytes, 256);
+  std::lock_guard<std::mutex> lock(g_arena_mu);
+  void *base = nullptr;
+  if ((rc = arena_reserve(total, &base)) != WAVE_OK)
+    return rc;
+  char *dev = static_cast<char *>(base);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t err;
+  if ((err = cudaMemcpyAsync(dev, Q_host, q_bytes, cudaMemcpyHostToDevice, s)) != cudaSuccess)
+    return cuda_fail(err, "copy Q to device");
+  if ((err = cudaMemcpyAsync(dev + off_k, K_host, kv_bytes, cudaMemcpyHostToDevice, s)) != cudaSuccess)
+    return cuda_fail(err, "copy K to device");
+  if ((err = cudaMemcpyAsync(dev + off_v, V_host, kv_bytes, cudaMemcpyHostToDevice, s)) != cudaSuccess)
+    return cuda_fail(err, "copy V to device");
+  if ((rc = wave_cuda_flash_attention_fwd(d, dev, dev + off_k, dev + off_v, dev + off_o, nullptr, stream)) != WAVE_OK)
+    return rc;
+  if ((err = cudaMemcpyAsync(O_host, dev + off_o, q_bytes, cudaMemcpyDeviceToHost, s)) != cudaSuccess)
+    return cuda_fail(err, "copy O to host");
+  if ((err = cudaStreamSynchronize(s)) != cudaSuccess)
+    return cuda_fail(err, "synchronise after attention");
+  return WAVE_OK;
+}
+
+// ------------------------------------------------------- name-based facade
+int wave_cuda_module_get_function(const char *kernel_name, const void *desc, void **fn) {
+  if (!kernel_name || !desc || !fn)
+    return fail(WAVE_E_INVALID, "kernel name, descriptor and result pointer must be non-null");
+  FnHandle *h = new FnHandle{};
+  if (strcmp(kernel_name, "wmma_f16_matmul_tiled") == 0) {
+    h->kind = 0;
+    h->gemm = *static_cast<const wave_gemm_desc *>(desc);
+    if (h->gemm.streamk_workers != 1)
+      h->gemm.streamk_workers = 1; // this ABI carries no workspace
+  } else if (strcmp(kernel_name, "gfx950_f16_streamk_gemm") == 0) {
+    h->kind = 1;
+    h->gemm = *static_cast<const wave_gemm_desc *>(desc);
+  } else if (strcmp(kernel_name, "flash_attention_bf16_gfx950") == 0 || strcmp(kernel_name, "flash_attention_f32") == 0) {
+    h->kind = 2;
+    h->fa = *static_cast<const wave_fa_desc *>(desc);
+  } else {
+    delete h;
+    return fail(WAVE_E_NOT_FOUND, "no kernel named '%s' in this backend", kernel_name);
+  }
+  int rc = h->kind == 2 ? wave_cuda_fa_validate(&h->fa) : wave_cuda_gemm_validate(&h->gemm);
+  if (rc != WAVE_OK) {
+    delete h;
+    return rc;
+  }
+  *fn = h;
+  return WAVE_OK;
+}
+
+int wave_cuda_launch(void *fn, void **args, void *stream) {
+  if (!fn || !args)
+    return fail(WAVE_E_INVALID, "function handle and argument block must be non-null");
+  FnHandle *h = static_cast<FnHandle *>(fn);
+  if (h->kind == 0) {
+    // {&A, &B, &C, &trip}: trip = K/(k_tile*wave_k_tiles) - 1 (wave_matmul.py:6964)
+    const int trip = *static_cast<int *>(args[3]);
+    const int expect = h->gemm.K / (16 * h->gemm.wave_k_tiles) - 1;
+    if (trip != expect)
+      return fail(WAVE_E_INVALID, "trip count %d does not match K/(16*wave_k_tiles)-1 = %d", trip, expect);
+    return wave_cuda_gemm(&h->gemm, *static_cast<void **>(args[0]), *static_cast<void **>(args[1]),
+                          *static_cast<void **>(args[2]), nullptr, stream);
+  }
+  if (h->kind == 1) {
+    // {&A, &B, &C, &scratch, &counters, &workers}: scratch and counters must be
+    // one allocation, counters directly after the scratch.
+    wave_gemm_desc d = h->gemm;
+    d.streamk_workers = *static_cast<int *>(args[5]);
+    size_t scratch = 0, counters = 0;
+    int rc = wave_cuda_gemm_workspace_bytes(&d, &scratch, &counters);
+    if (rc != WAVE_OK)
+      return rc;
+    char *ws = *static_cast<char **>(args[3]);
+    if (scratch + counters > 0 && *static_cast<char **>(args[4]) != ws + scratch)
+      return fail(WAVE_E_INVALID, "counters must directly follow the %zu-byte scratch area", scratch);
+    return wave_cuda_gemm(&d, *static_cast<void **>(args[0]), *static_cast<void **>(args[1]),
+                          *static_cast<void **>(args[2]), ws, stream);
+  }
+  return wave_cuda_flash_attention_fwd(&h->fa, *static_cast<void **>(args[0]), *static_cast<void **>(args[1]),
+                                       *static_cast<void **>(args[2]), *static_cast<void **>(args[3]), nullptr,
+                                       stream);
+}
+
+void wave_cuda_function_release(void *fn) { delete static_cast<FnHandle *>(fn); }
+
+int wave_cuda_check_device_status(int *out4) {
+  cudaError_t err = cudaDeviceSynchronize();
+  if (err != cudaSuccess)
+    return cuda_fail(err, "cudaDeviceSynchronize");
+  int g[4] = {0, 0, 0, 0}, f[4] = {0, 0, 0, 0};
+  if ((err = wave::gemm_read_status(g, true)) != cudaSuccess)
+    return cuda_fail(err, "read GEMM status");
+  if ((err = wave::fa_read_status(f, true)) != cudaSuccess)
+    return cuda_fail(err, "read attention status");
+  const int *bad = g[0] ? g : (f[0] ? f : nullptr);
+  if (out4)
+    for (int i = 0; i < 4; ++i)
+      out4[i] = bad ? bad[i] : 0;
+  if (bad)
+    return fail(WAVE_E_DEVICE_STATUS, "%s kernel reported status %d (block %d, role %d, detail %d)",
+                bad == g ? "GEMM" : "attention", bad[0], bad[1], bad[2], bad[3]);
+  return WAVE_OK;
+}
+
+} // extern "C"

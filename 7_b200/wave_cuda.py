@@ -1,0 +1,148 @@
+"""ctypes binding of libwave_cuda.so (the C ABI declared in include/wave_cuda.h).
+
+This is the only way Python reaches the CUDA kernels.  There is no CPU or
+PyTorch fallback: if the library is missing it is built, and if that fails or
+no CUDA device is present the compute calls raise.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libwave_cuda.so")
+
+F16, BF16, F32 = 0, 1, 2
+ROW_MAJOR, COL_MAJOR = 0, 1
+OK, E_INVALID, E_UNSUPPORTED, E_CUDA, E_DEVICE_STATUS, E_NOT_FOUND = 0, -1, -2, -3, -4, -5
+
+TYPE_BY_NAME = {"f16": F16, "bf16": BF16, "f32": F32}
+LAYOUT_BY_NAME = {"row-major": ROW_MAJOR, "column-major": COL_MAJOR}
+
+
+class WaveCudaError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"wave_cuda error {code}: {message}")
+        self.code = code
+        self.message = message
+
+
+class GemmDesc(C.Structure):
+    _fields_ = [(n, C.c_int) for n in (
+        "M", "N", "K", "bm", "bn", "wave_m_tiles", "wave_n_tiles", "wave_k_tiles", "in_type", "out_type",
+        "out_layout", "cta_group_m", "streamk_workers", "ldc")]
+
+
+class FaDesc(C.Structure):
+    _fields_ = [("batch", C.c_int), ("heads", C.c_int), ("seq_q", C.c_int), ("seq_k", C.c_int),
+                ("head_dim", C.c_int), ("scale", C.c_float), ("causal", C.c_int), ("io_type", C.c_int)]
+
+
+EXPORTS = [
+    "wave_cuda_last_error", "wave_cuda_version",
+    "_mlir_ciface_wave_memref_to_ptr_global_i32", "_mlir_ciface_wave_memref_to_ptr_global_i8",
+    "_mlir_ciface_wave_memref_to_ptr_global_f32", "_mlir_ciface_wave_memref_to_ptr_global_f16",
+    "_mlir_ciface_wave_memref_to_ptr_global_bf16", "_mlir_ciface_wave_memref_to_ptr_global_i64",
+    "_mlir_ciface_wave_memref_to_ptr_global_f64",
+    "wave_cuda_gemm_desc_init", "wave_cuda_gemm_validate", "wave_cuda_gemm_workspace_bytes", "wave_cuda_gemm",
+    "wave_cuda_gemm_host", "wave_cuda_gemm_plan", "wave_cuda_fa_validate", "wave_cuda_flash_attention_fwd",
+    "wave_cuda_flash_attention_fwd_host", "wave_cuda_module_get_function", "wave_cuda_launch",
+    "wave_cuda_function_release", "wave_cuda_check_device_status",
+]
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """Loads (building first if needed) the backend library."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        from . import build as _build
+        _build.build()
+    L = C.CDLL(LIB_PATH)
+    vp, ip = C.c_void_p, C.POINTER(C.c_int)
+    L.wave_cuda_last_error.restype = C.c_char_p
+    L.wave_cuda_version.restype = C.c_char_p
+    for name in EXPORTS[2:9]:
+        getattr(L, name).restype = vp
+        getattr(L, name).argtypes = [vp]
+    L.wave_cuda_gemm_desc_init.argtypes = [C.POINTER(GemmDesc), C.c_int, C.c_int, C.c_int]
+    L.wave_cuda_gemm_desc_init.restype = None
+    L.wave_cuda_gemm_validate.argtypes = [C.POINTER(GemmDesc)]
+    L.wave_cuda_gemm_workspace_bytes.argtypes = [C.POINTER(GemmDesc), C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]
+    L.wave_cuda_gemm.argtypes = [C.POINTER(GemmDesc), vp, vp, vp, vp, vp]
+    L.wave_cuda_gemm_host.argtypes = [C.POINTER(GemmDesc), vp, vp, vp, vp]
+    L.wave_cuda_gemm_plan.argtypes = [C.POINTER(GemmDesc), ip, ip, ip, ip, ip]
+    L.wave_cuda_fa_validate.argtypes = [C.POINTER(FaDesc)]
+    L.wave_cuda_flash_attention_fwd.argtypes = [C.POINTER(FaDesc), vp, vp, vp, vp, vp, vp]
+    L.wave_cuda_flash_attention_fwd_host.argtypes = [C.POINTER(FaDesc), vp, vp, vp, vp, vp]
+    L.wave_cuda_module_get_function.argtypes = [C.c_char_p, vp, C.POINTER(vp)]
+    L.wave_cuda_launch.argtypes = [vp, C.POINTER(vp), vp]
+    L.wave_cuda_function_release.argtypes = [vp]
+    L.wave_cuda_function_release.restype = None
+    L.wave_cuda_check_device_status.argtypes = [ip]
+    _lib = L
+    return L
+
+
+def check(rc: int) -> None:
+    if rc != OK:
+        raise WaveCudaError(rc, lib().wave_cuda_last_error().decode())
+
+
+def gemm_desc(M: int, N: int, K: int, *, bm: int = 1, bn: int = 2, wave_m_tiles: int = 1, wave_n_tiles: int = 1,
+              wave_k_tiles: int = 1, in_type: int = F16, out_type: int = F32, out_layout: int = ROW_MAJOR,
+              cta_group_m: int = 1, streamk_workers: int = 1, ldc: int = 0) -> GemmDesc:
+    return GemmDesc(M, N, K, bm, bn, wave_m_tiles, wave_n_tiles, wave_k_tiles, in_type, out_type, out_layout,
+                    cta_group_m, streamk_workers, ldc)
+
+
+def gemm_validate(desc: GemmDesc) -> None:
+    check(lib().wave_cuda_gemm_validate(C.byref(desc)))
+
+
+def gemm_workspace_bytes(desc: GemmDesc) -> tuple[int, int]:
+    s, c = C.c_size_t(0), C.c_size_t(0)
+    check(lib().wave_cuda_gemm_workspace_bytes(C.byref(desc), C.byref(s), C.byref(c)))
+    return s.value, c.value
+
+
+def gemm_plan(desc: GemmDesc) -> dict:
+    v = [C.c_int(0) for _ in range(5)]
+    check(lib().wave_cuda_gemm_plan(C.byref(desc), *[C.byref(x) for x in v]))
+    return dict(tile_m=v[0].value, tile_n=v[1].value, grid=v[2].value, streamk_workers=v[3].value,
+                swapped=bool(v[4].value))
+
+
+def gemm(desc: GemmDesc, a_ptr: int, b_ptr: int, c_ptr: int, workspace_ptr: int = 0, stream: int = 0) -> None:
+    check(lib().wave_cuda_gemm(C.byref(desc), a_ptr, b_ptr, c_ptr, workspace_ptr or None, stream or None))
+
+
+def gemm_host(desc: GemmDesc, a_ptr: int, b_ptr: int, c_ptr: int, stream: int = 0) -> None:
+    check(lib().wave_cuda_gemm_host(C.byref(desc), a_ptr, b_ptr, c_ptr, stream or None))
+
+
+def fa_desc(batch: int, heads: int, seq_q: int, seq_k: int, head_dim: int = 128, *, scale: float = 0.0,
+            causal: bool = False, io_type: int = BF16) -> FaDesc:
+    return FaDesc(batch, heads, seq_q, seq_k, head_dim, scale, int(causal), io_type)
+
+
+def fa_validate(desc: FaDesc) -> None:
+    check(lib().wave_cuda_fa_validate(C.byref(desc)))
+
+
+def flash_attention_fwd(desc: FaDesc, q_ptr: int, k_ptr: int, v_ptr: int, o_ptr: int, lse_ptr: int = 0,
+                        stream: int = 0) -> None:
+    check(lib().wave_cuda_flash_attention_fwd(C.byref(desc), q_ptr, k_ptr, v_ptr, o_ptr, lse_ptr or None,
+                                              stream or None))
+
+
+def flash_attention_fwd_host(desc: FaDesc, q_ptr: int, k_ptr: int, v_ptr: int, o_ptr: int, stream: int = 0) -> None:
+    check(lib().wave_cuda_flash_attention_fwd_host(C.byref(desc), q_ptr, k_ptr, v_ptr, o_ptr, stream or None))
+
+
+def check_device_status() -> None:
+    out = (C.c_int * 4)()
+    check(lib().wave_cuda_check_device_status(out))

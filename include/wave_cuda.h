@@ -1,0 +1,169 @@
+/*
+ * wave_cuda.h -- C ABI of the B200 (sm_100a) backend for the two dense kernels
+ * the Wave compiler produces: the tiled f16/bf16 GEMM and the flash-attention
+ * forward.  The library (libwave_cuda.so) stands where the reference's AMDGPU
+ * assembly emission (lib/Target/Wave/AMDGPU.cpp, WaveCompileKernels.cpp) and
+ * its ROCm launch (hipModuleLoad / hipModuleLaunchKernel in the calibrate
+ * runners, mgpu* in mlir-runner) stand today, for these two kernels only.
+ *
+ * Conventions: every function returns 0 on success or a negative WAVE_E_* code
+ * and never exits the process; wave_cuda_last_error() gives the message of the
+ * calling thread's last failure.  The caller owns every device buffer.  Plain
+ * pointers and sizes only; `stream` is a cudaStream_t passed as void*.
+ * There is no CPU fallback: without a CUDA device every compute entry point
+ * fails with WAVE_E_CUDA.
+ */
+#ifndef WAVE_CUDA_H
+#define WAVE_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- error codes ------------------------------------------------------- */
+#define WAVE_OK 0
+#define WAVE_E_INVALID (-1)     /* argument validation failed (runner exit code 2) */
+#define WAVE_E_UNSUPPORTED (-2) /* legal in the reference, outside this backend    */
+#define WAVE_E_CUDA (-3)        /* a CUDA call failed (runner exit code 1)          */
+#define WAVE_E_DEVICE_STATUS (-4) /* a kernel reported a bounded wait that ran out */
+#define WAVE_E_NOT_FOUND (-5)
+
+/* ---- element types and layouts ---------------------------------------- */
+#define WAVE_F16 0
+#define WAVE_BF16 1
+#define WAVE_F32 2
+#define WAVE_ROW_MAJOR 0 /* C[m*ldc + n]   (wave_matmul.py:1040) */
+#define WAVE_COL_MAJOR 1 /* C[n*ldc + m]   (wave_matmul.py:1040) */
+
+const char *wave_cuda_last_error(void);
+const char *wave_cuda_version(void);
+
+/* ---- mlir-runner host ABI ---------------------------------------------- *
+ * Same seven symbols as runtime/wave_runtime.cpp:46-74: a rank-1 strided
+ * memref descriptor {base, data, offset, size, stride} -> data + offset, the
+ * address handed to the kernel as a `!wave.ptr<T, #wave.global>`.           */
+void *_mlir_ciface_wave_memref_to_ptr_global_i32(void *memref1d);
+void *_mlir_ciface_wave_memref_to_ptr_global_i8(void *memref1d);
+void *_mlir_ciface_wave_memref_to_ptr_global_f32(void *memref1d);
+void *_mlir_ciface_wave_memref_to_ptr_global_f16(void *memref1d);
+void *_mlir_ciface_wave_memref_to_ptr_global_bf16(void *memref1d);
+void *_mlir_ciface_wave_memref_to_ptr_global_i64(void *memref1d);
+void *_mlir_ciface_wave_memref_to_ptr_global_f64(void *memref1d);
+
+/* ---- tiled GEMM --------------------------------------------------------- *
+ * C[M x N] = A[M x K] * B, with B stored N x K row-major (the reference keeps
+ * B transposed: wave_matmul.py:328-332), f32 accumulation, one final
+ * round-to-nearest-even to out_type.  The descriptor carries what the
+ * reference bakes into the kernel at code generation (_MatmulConfig,
+ * wave_matmul.py:288-530) and what its runner takes as flags
+ * (wave-matmul-calibrate-runner.cpp:36-64).  The tiling knobs never change
+ * results; they choose the CTA tile:
+ *   16*bm*wave_m_tiles x 16*bn*wave_n_tiles, snapped to a legal UMMA shape
+ *   (rows 128; columns the next of 16/32/64/128/256).                        */
+typedef struct wave_gemm_desc {
+  int M, N, K;                 /* positive multiples of 16 (wave_matmul.py:533-536)      */
+  int bm, bn;                  /* waves per workgroup along M / N; bn a power of two      */
+  int wave_m_tiles, wave_n_tiles, wave_k_tiles; /* 16x16 tiles per wave, K slices per step */
+  int in_type;                 /* WAVE_F16 | WAVE_BF16                                      */
+  int out_type;                /* WAVE_F32 | WAVE_F16 | WAVE_BF16                           */
+  int out_layout;              /* WAVE_ROW_MAJOR | WAVE_COL_MAJOR                           */
+  int cta_group_m;             /* grouped-M rasterisation (wave_matmul.py:1267-1272); >= 1 */
+  int streamk_workers;         /* 0 auto, 1 plain tiles, >1 persistent Stream-K grid
+                                  (--streamk-workers, wave-matmul-calibrate.py:1170)      */
+  int ldc;                     /* leading dimension of C in elements; 0 = N (row-major) or
+                                  M (column-major).  Lets a rank write its column shard
+                                  into a larger C in place.                                */
+} wave_gemm_desc;
+
+/* Fills the descriptor with the runner's defaults (bm 1, bn 2, tiles 1, f16 in,
+ * f32 out, row-major: runner.cpp:36-64). */
+void wave_cuda_gemm_desc_init(wave_gemm_desc *desc, int M, int N, int K);
+
+/* Same rules and messages as _validate_positive_shape / _validate_tile_shape
+ * (wave_matmul.py:533-619).  Needs no GPU. */
+int wave_cuda_gemm_validate(const wave_gemm_desc *desc);
+
+/* Bytes of device workspace wave_cuda_gemm needs for this descriptor: f32
+ * partial tiles then int32 arrival counters (zero on entry; the kernel leaves
+ * them zero).  Both are 0 when the launch does not split K.  Mirrors
+ * getStreamKWorkspaceSizes (runner.cpp:393-408).  Needs no GPU unless
+ * streamk_workers is 0 (auto), which asks the device for its SM count. */
+int wave_cuda_gemm_workspace_bytes(const wave_gemm_desc *desc, size_t *scratch_bytes, size_t *counter_bytes);
+
+/* Launches the GEMM on `stream`.  A, B, C are device pointers, 16-byte
+ * aligned; `workspace` is scratch_bytes + counter_bytes (counters follow the
+ * scratch, zero-initialised by the caller once) or NULL when both are 0.
+ * Replaces hipModuleLaunchKernel with {&A,&B,&C,&trip} / the Stream-K block
+ * {&A,&B,&C,&scratch,&counters,&workers} (runner.cpp:1790-1791, 1811-1816).  */
+int wave_cuda_gemm(const wave_gemm_desc *desc, const void *A, const void *B, void *C, void *workspace,
+                   void *stream);
+
+/* Host-buffer form (what the mlir-runner host main does with host-registered
+ * memrefs, wave_matmul.py:6926-6937): copies A and B to the device, runs,
+ * copies C back, all on `stream`, then synchronises it.  Device staging
+ * buffers are cached in the library and grow on demand. */
+int wave_cuda_gemm_host(const wave_gemm_desc *desc, const void *A_host, const void *B_host, void *C_host,
+                        void *stream);
+
+/* Launch geometry the backend chose (tile rows, tile columns, grid size,
+ * Stream-K workers or 0, operands swapped or not) -- the counterpart of the
+ * runner's `grid:` / `shape:` lines (runner.cpp:1881-1908). */
+int wave_cuda_gemm_plan(const wave_gemm_desc *desc, int *tile_m, int *tile_n, int *grid, int *streamk_workers,
+                        int *swapped);
+
+/* ---- flash-attention forward ------------------------------------------- *
+ * O = softmax(scale * Q K^T [+ causal mask]) V per (batch, head).  Layout
+ * (B, H, S, D) contiguous, the same bytes as the gfx950 runner's [B*H][S][D]
+ * (wave_flash_attention.py:242-254; operator surface
+ * integrations/tlx/workloads/amd_fa_wave.py:1671-1682).  f32 online-softmax
+ * statistics, exp2 with scale*log2(e) folded into the exponent
+ * (wave_flash_attention.py:596-600), probabilities rounded to io_type before
+ * P*V, output rounded once to io_type.  `causal` keeps key <= query (top-left
+ * aligned; an extension, the reference's Wave kernel is non-causal).         */
+typedef struct wave_fa_desc {
+  int batch, heads;
+  int seq_q, seq_k; /* multiples of 16 */
+  int head_dim;     /* 128 (the reference kernel's only value) or 64 */
+  float scale;      /* 0 = 1/sqrt(head_dim) */
+  int causal;
+  int io_type;      /* WAVE_BF16 | WAVE_F16 */
+} wave_fa_desc;
+
+int wave_cuda_fa_validate(const wave_fa_desc *desc);
+
+/* Q, K, V, O device pointers (16-byte aligned); lse_or_null, when given,
+ * receives the natural-log sum-exp of the scaled scores per row, f32
+ * [batch*heads][seq_q].  Replaces hipModuleLaunchKernel with {&Q,&K,&V,&O}
+ * (wave-fa-gfx950-runner.cpp:396-402, 446). */
+int wave_cuda_flash_attention_fwd(const wave_fa_desc *desc, const void *Q, const void *K, const void *V, void *O,
+                                  float *lse_or_null, void *stream);
+
+int wave_cuda_flash_attention_fwd_host(const wave_fa_desc *desc, const void *Q_host, const void *K_host,
+                                       const void *V_host, void *O_host, void *stream);
+
+/* ---- name-based launch facade ------------------------------------------ *
+ * Keeps the runners' call shape (hipModuleGetFunction by kernel name, then a
+ * launch with a void* args[] block of pointers-to-values): names
+ * "wmma_f16_matmul_tiled" (args {&A,&B,&C,&trip}), "gfx950_f16_streamk_gemm"
+ * (args {&A,&B,&C,&scratch,&counters,&workers}), "flash_attention_bf16_gfx950"
+ * and "flash_attention_f32" (args {&Q,&K,&V,&O})
+ * (wave_matmul.py:777-779; wave_flash_attention.py:16; wave_attention.py:18).
+ * `desc` is a wave_gemm_desc or wave_fa_desc and is copied into the handle. */
+int wave_cuda_module_get_function(const char *kernel_name, const void *desc, void **fn);
+int wave_cuda_launch(void *fn, void **args, void *stream);
+void wave_cuda_function_release(void *fn);
+
+/* ---- device status ------------------------------------------------------ *
+ * Every device-side wait is bounded; a wait that runs out records
+ * {code, block, role, detail} and the kernel unwinds.  This synchronises the
+ * device, returns WAVE_E_DEVICE_STATUS if any kernel since the last call
+ * reported a problem (details in out4 if non-NULL), and clears the record. */
+int wave_cuda_check_device_status(int *out4);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WAVE_CUDA_H */

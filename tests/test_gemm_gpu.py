@@ -1,0 +1,179 @@
+"""GPU parity of the tiled GEMM against the CPU oracle, through the C ABI.
+
+Mirrors the reference's integration strategy (``--compare-cpu`` runs over a
+shape/tiling/dtype/seed matrix, e.g. test/Integration/wave_mfma_per_wave_tiles.mlir:3-11
+and wave_wmma_per_wave_tiles.mlir:10-48, and calibrate-runner runs that must
+print ``output_check: passed``).
+"""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from _util import device_out, out_to_f32, runner_tolerance_ok, to_device_bits
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def run_gemm(torch, wc, a_bits, b_bits, in_name, out_name, layout="row-major", streamk=1, ldc=0, **knobs):
+    M, K = a_bits.shape
+    N = b_bits.shape[0]
+    desc = wc.gemm_desc(M, N, K, in_type=wc.TYPE_BY_NAME[in_name], out_type=wc.TYPE_BY_NAME[out_name],
+                        out_layout=wc.LAYOUT_BY_NAME[layout], streamk_workers=streamk, ldc=ldc, **knobs)
+    a = to_device_bits(torch, a_bits)
+    b = to_device_bits(torch, b_bits)
+    ld = ldc or (N if layout == "row-major" else M)
+    outer = M if layout == "row-major" else N
+    c = device_out(torch, ld * outer, out_name)
+    scratch, counters = wc.gemm_workspace_bytes(desc)
+    ws = None
+    if scratch + counters:
+        ws = torch.zeros(scratch + counters, dtype=torch.uint8, device="cuda")
+    wc.gemm(desc, a.data_ptr(), b.data_ptr(), c.data_ptr(), ws.data_ptr() if ws is not None else 0,
+            torch.cuda.current_stream().cuda_stream)
+    wc.check_device_status()
+    got = out_to_f32(torch, c).reshape(outer, ld)
+    inner = N if layout == "row-major" else M
+    got = got[:, :inner]
+    logical = got if layout == "row-major" else got.T
+    counters_np = None
+    if ws is not None:
+        counters_np = ws[scratch:].cpu().numpy().view(np.int32)
+    return np.ascontiguousarray(logical), counters_np
+
+
+def expected(oracle, a_bits, b_bits, in_name, out_name):
+    t = oracle.F16 if in_name == "f16" else oracle.BF16
+    return oracle.round_output(oracle.gemm_ref(a_bits, b_bits, t), out_name)
+
+
+def lcg_inputs(oracle, M, N, K, in_name, seed):
+    t = oracle.F16 if in_name == "f16" else oracle.BF16
+    return (oracle.make_input_bits(M, K, t, seed, 0, oracle.MODE_LCG),
+            oracle.make_input_bits(N, K, t, seed, 1, oracle.MODE_LCG))
+
+
+def test_config1_matches_reference_golden(cuda, wc, oracle):
+    """32x32x64 f16 -> f32, seed 7, bm=bn=2, wave-k-tiles=2: the reference's own
+    --compare-cpu case.  LCG inputs make every partial sum exact, so the match
+    is bit-for-bit against the reference's Python output."""
+    with open(os.path.join(GOLDEN, "gemm_golden.json")) as f:
+        cases = json.load(f)["cases"]
+    case = next(c for c in cases if c["case"].get("M") == 32 and c["case"].get("K") == 64
+                and c["case"].get("input_type", "f16") == "f16")
+    a, b = lcg_inputs(oracle, 32, 32, 64, "f16", 7)
+    got, _ = run_gemm(cuda, wc, a, b, "f16", "f32", bm=2, bn=2, wave_k_tiles=2)
+    want = np.asarray(case["out"], np.float32).reshape(32, 32)
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("M,N,K,in_name,out_name,layout,knobs", [
+    (16, 16, 16, "f16", "f32", "row-major", dict()),
+    (32, 32, 64, "bf16", "f32", "row-major", dict(bm=2, bn=2, wave_k_tiles=2)),
+    (32, 48, 32, "f16", "f32", "column-major", dict(wave_m_tiles=2, wave_n_tiles=3, wave_k_tiles=2, bn=1)),
+    (128, 256, 64, "f16", "f16", "row-major", dict(bm=4, bn=4, wave_m_tiles=2, wave_n_tiles=4)),
+    (256, 512, 256, "bf16", "bf16", "row-major", dict(bm=4, bn=4, wave_m_tiles=2, wave_n_tiles=4)),
+    (144, 80, 48, "f16", "f32", "row-major", dict(bn=1)),
+    (144, 80, 48, "bf16", "bf16", "column-major", dict(bn=1)),
+    (400, 272, 208, "f16", "f16", "column-major", dict(bn=1, wave_n_tiles=17)),
+    (1024, 1024, 512, "bf16", "f32", "row-major", dict(bm=4, bn=8, wave_m_tiles=2, wave_n_tiles=2)),
+    (512, 384, 1040, "f16", "f32", "row-major", dict(bm=2, bn=4, wave_n_tiles=2, wave_k_tiles=5)),
+    (16, 1024, 512, "bf16", "f32", "row-major", dict(bn=1)),
+    (16, 1024, 512, "bf16", "bf16", "column-major", dict(bn=1)),
+    (64, 4096, 256, "f16", "f16", "row-major", dict(bm=4, bn=1)),
+])
+def test_lcg_inputs_bit_exact(cuda, wc, oracle, M, N, K, in_name, out_name, layout, knobs):
+    """Reference LCG inputs are multiples of 0.25 in [-2, 2]: all partial sums
+    are exact in f32, so any summation order must give the oracle's bits."""
+    a, b = lcg_inputs(oracle, M, N, K, in_name, seed=M + N + K)
+    got, _ = run_gemm(cuda, wc, a, b, in_name, out_name, layout, **knobs)
+    want = expected(oracle, a, b, in_name, out_name)
+    assert got.shape == want.shape
+    assert np.array_equal(got, want), f"max abs diff {np.nanmax(np.abs(got - want))}"
+
+
+@pytest.mark.parametrize("M,N,K,in_name,out_name,dist,scale", [
+    (256, 256, 512, "f16", "f16", "uniform", 1.0),
+    (512, 768, 2048, "bf16", "bf16", "normal", 2048 ** -0.5),
+    (1024, 512, 4096, "f16", "f32", "uniform", 1.0),
+    (16, 2048, 8192, "bf16", "f32", "normal", 8192 ** -0.5),
+])
+def test_random_inputs_within_runner_tolerance(cuda, wc, oracle, M, N, K, in_name, out_name, dist, scale):
+    """Tolerance of the reference runner, |d| <= 1e-2 + 1e-3*|exp|
+    (wave-matmul-calibrate-runner.cpp:907), plus mean absolute error <= 1e-3."""
+    t = oracle.F16 if in_name == "f16" else oracle.BF16
+    a = oracle.baseline_inputs((M, K), dist, 11, 0, t, scale=1.0 if dist == "uniform" else 1.0)
+    b = oracle.baseline_inputs((N, K), dist, 11, 1, t, scale=scale)
+    knobs = dict(bm=4, bn=4, wave_m_tiles=2, wave_n_tiles=4) if M % 128 == 0 and N % 256 == 0 else dict(bn=1)
+    got, _ = run_gemm(cuda, wc, a, b, in_name, out_name, **knobs)
+    want = expected(oracle, a, b, in_name, out_name)
+    ok, worst, nbad = runner_tolerance_ok(got, want)
+    assert ok, f"{nbad} elements out of tolerance, worst abs diff {worst}"
+    assert float(np.mean(np.abs(got - want))) <= 1e-3
+
+
+@pytest.mark.parametrize("M,N,K,workers,knobs", [
+    (256, 256, 1024, 3, dict(bm=4, bn=4, wave_m_tiles=2, wave_n_tiles=4)),
+    (512, 512, 2048, 5, dict(bm=4, bn=4, wave_m_tiles=2, wave_n_tiles=4)),
+    (384, 640, 1536, 37, dict(bm=4, bn=4, wave_m_tiles=2, wave_n_tiles=2)),
+    (16, 4096, 4096, 148, dict(bn=1)),
+    (16, 28672, 8192, 0, dict(bn=1)),
+])
+def test_streamk_matches_oracle_and_resets_counters(cuda, wc, oracle, M, N, K, workers, knobs):
+    """Stream-K: fixed-order reduction makes two launches bit-identical, and the
+    arrival counters are back to zero afterwards (the reference runner's
+    streamk_counter_check, runner.cpp:1718-1733)."""
+    a, b = lcg_inputs(oracle, M, N, K, "bf16", seed=5)
+    got1, counters1 = run_gemm(cuda, wc, a, b, "bf16", "f32", streamk=workers, **knobs)
+    want = expected(oracle, a, b, "bf16", "f32")
+    assert np.array_equal(got1, want)
+    assert counters1 is not None and not counters1.any()
+    t = oracle.BF16
+    a = oracle.baseline_inputs((M, K), "normal", 3, 0, t)
+    b = oracle.baseline_inputs((N, K), "normal", 3, 1, t, scale=K ** -0.5)
+    r1, _ = run_gemm(cuda, wc, a, b, "bf16", "f32", streamk=workers, **knobs)
+    r2, _ = run_gemm(cuda, wc, a, b, "bf16", "f32", streamk=workers, **knobs)
+    assert np.array_equal(r1, r2)
+    ok, worst, nbad = runner_tolerance_ok(r1, expected(oracle, a, b, "bf16", "f32"))
+    assert ok, f"{nbad} elements out of tolerance, worst {worst}"
+
+
+def test_ldc_writes_column_shard_in_place(cuda, wc, oracle):
+    """A rank's N-column shard written straight into a wider row-major C."""
+    M, N, K, ldc = 128, 64, 128, 256
+    a, b = lcg_inputs(oracle, M, N, K, "f16", seed=1)
+    got, _ = run_gemm(cuda, wc, a, b, "f16", "f32", ldc=ldc, bn=1)
+    assert np.array_equal(got, expected(oracle, a, b, "f16", "f32"))
+
+
+def test_host_buffer_call(cuda, wc, oracle):
+    M, N, K = 256, 128, 320
+    a, b = lcg_inputs(oracle, M, N, K, "bf16", seed=9)
+    c = np.full((M, N), np.nan, np.float32)
+    desc = wc.gemm_desc(M, N, K, in_type=wc.BF16, out_type=wc.F32)
+    wc.gemm_host(desc, a.ctypes.data, b.ctypes.data, c.ctypes.data)
+    wc.check_device_status()
+    assert np.array_equal(c, expected(oracle, a, b, "bf16", "f32"))
+
+
+def test_name_based_launch_facade(cuda, wc, oracle):
+    """Same call shape as the reference runner: look a kernel up by name, then
+    launch with an array of pointers to the argument values
+    (wave-matmul-calibrate-runner.cpp:1790-1791, 1846-1862)."""
+    import ctypes as C
+    M, N, K = 64, 64, 128
+    a_bits, b_bits = lcg_inputs(oracle, M, N, K, "f16", seed=2)
+    a, b = to_device_bits(cuda, a_bits), to_device_bits(cuda, b_bits)
+    c = device_out(cuda, M * N, "f32")
+    desc = wc.gemm_desc(M, N, K, wave_k_tiles=2)
+    fn = C.c_void_p()
+    wc.check(wc.lib().wave_cuda_module_get_function(b"wmma_f16_matmul_tiled", C.byref(desc), C.byref(fn)))
+    pa, pb, pc = C.c_void_p(a.data_ptr()), C.c_void_p(b.data_ptr()), C.c_void_p(c.data_ptr())
+    trip = C.c_int(K // (16 * 2) - 1)
+    args = (C.c_void_p * 4)(C.addressof(pa), C.addressof(pb), C.addressof(pc), C.addressof(trip))
+    wc.check(wc.lib().wave_cuda_launch(fn, args, None))
+    wc.check_device_status()
+    wc.lib().wave_cuda_function_release(fn)
+    assert np.array_equal(out_to_f32(cuda, c).reshape(M, N), expected(oracle, a_bits, b_bits, "f16", "f32"))
