@@ -1,9 +1,440 @@
+// Flash-attention forward for sm_100a: O = softmax(scale * Q K^T [+causal]) V,
+// (B, H, S, D=128) bf16/f16 in and out, f32 online-softmax statistics.  This is
+// the B200 stand-in for the kernel the reference generates as
+// `flash_attention_bf16_gfx950` (python/mlir/dialects/wave_flash_attention.py:
+// 452-728, 1034-1095, 1685-1731): BLOCK_M 256 per workgroup, exp2 with
+// scale*log2(e) folded into the exponent (:596-600), f32 row sums of the
+// unrounded probabilities with 16-bit probabilities feeding P*V (:706-722),
+// and the lazy accumulator rescale with threshold 8 in log2 units (:557-583).
+//
+// Structure (one CTA per 256 query rows of one head, 384 threads):
+//   warp 0        TMA producer: two 128-row Q tiles once, then K and V blocks
+//                 of 128 keys through two-stage rings (128B-swizzled smem)
+//   warp 1        UMMA issuer (one thread): S_t = Q_t K^T (both operands from
+//                 shared memory) and O_t += P_t V (P from tensor memory, V from
+//                 shared memory as an MN-major operand), t = 0, 1
+//   warps 4..7    softmax for Q tile 0: one thread per query row
+//   warps 8..11   softmax for Q tile 1
+// The two Q tiles ping-pong: while one tile's rows are in the exponentials the
+// tensor core works on the other tile.  TMEM: S_0 | S_1 | O_0 | O_1, 128 f32
+// columns each; P_t overwrites the first 64 columns of S_t as packed 16-bit
+// pairs.  Tensor-core operations of one tile are issued in program order
+// (PV_t(j) before S_t(j+1)), which is what makes the S/P aliasing safe.
+// No load uses cluster multicast.  The causal mask (key <= query) is an
+// extension: the reference's Wave kernel is non-causal.
+#include "../../include/wave_cuda.h"
 #include "fa_sm100.h"
+#include "sm100_ptx.cuh"
+
 namespace wave {
-__device__ int g_fa_status[4];
-int launch_flash_attention(const FaParams &, const void *, const void *, const void *, int, cudaStream_t) {
-  return -2;
+
+__device__ int g_fa_status[4]; // [0] code, [1] linear block, [2] role, [3] detail
+
+namespace {
+
+constexpr int kBlockM = 128; // rows per Q tile = UMMA M = TMEM lanes
+constexpr int kBlockN = 128; // keys per K/V block
+constexpr int kD = 128;      // head dimension
+constexpr int kThreads = 384;
+constexpr int kSubTile = 128 * 64 * 2;  // [128 rows][64 elements], 128-byte swizzled rows
+constexpr int kTile = 2 * kSubTile;     // 128 x 128 16-bit elements
+constexpr int kSmemTiles = 2 * kTile /*Q*/ + 2 * kTile /*K ring*/ + 2 * kTile /*V ring*/;
+constexpr int kSmemBytes = kSmemTiles + 1024 + 256;
+constexpr int kTmemCols = 512;
+constexpr float kRescaleThreshold = 8.0f; // log2 units (wave_flash_attention.py:563-569)
+
+struct FaShared {
+  uint64_t q_full;
+  uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
+  uint64_t s_full[2], p_full[2], o_full[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ void fa_report(int code, int role, int detail) {
+  if (atomicCAS(&g_fa_status[0], 0, code) == 0) {
+    g_fa_status[1] = static_cast<int>(blockIdx.y * gridDim.x + blockIdx.x);
+    g_fa_status[2] = role;
+    g_fa_status[3] = detail;
+  }
 }
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi, bool bf16) {
+  if (bf16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+  }
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t *>(&v);
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+              const __grid_constant__ CUtensorMap tm_v, const FaParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *tiles = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t *q_smem = tiles;              // 2 tiles
+  uint8_t *k_smem = tiles + 2 * kTile;  // 2 stages
+  uint8_t *v_smem = tiles + 4 * kTile;  // 2 stages
+  FaShared *sh = reinterpret_cast<FaShared *>(tiles + kSmemTiles);
+  volatile int *abort_flag = &sh->abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  // Heaviest causal tiles first: the last query block of a head has the most keys.
+  const int q_blk = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
+  const int bh = blockIdx.y;
+  const int n_kv_blocks = (p.seq_k + kBlockN - 1) / kBlockN;
+
+  // Number of K/V blocks each Q tile visits (0: tile is past the end of Q).
+  int n_blocks[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int q0 = q_blk * 2 * kBlockM + t * kBlockM;
+    int n = 0;
+    if (q0 < p.seq_q) {
+      n = n_kv_blocks;
+      if (p.causal)
+        n = min(n, q0 / kBlockN + 1);
+    }
+    n_blocks[t] = n;
+  }
+  const int n_max = max(n_blocks[0], n_blocks[1]);
+
+  if (threadIdx.x == 0) {
+    mbar_init(&sh->q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&sh->k_full[s], 1);
+      mbar_init(&sh->k_empty[s], 1);
+      mbar_init(&sh->v_full[s], 1);
+      mbar_init(&sh->v_empty[s], 1);
+      mbar_init(&sh->s_full[s], 1);
+      mbar_init(&sh->p_full[s], kBlockM); // every softmax thread of the tile arrives
+      mbar_init(&sh->o_full[s], 1);
+    }
+    sh->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&sh->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = sh->tmem_base;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- loads
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      const int q_tiles = (n_blocks[0] > 0) + (n_blocks[1] > 0);
+      if (q_tiles > 0) {
+        mbar_arrive_expect_tx(&sh->q_full, static_cast<uint32_t>(q_tiles * kTile));
+        for (int t = 0; t < 2; ++t)
+          if (n_blocks[t] > 0)
+            for (int c = 0; c < 2; ++c)
+              tma_load_3d(q_smem + t * kTile + c * kSubTile, &tm_q, &sh->q_full, c * 64,
+                          q_blk * 2 * kBlockM + t * kBlockM, bh);
+      }
+      bool ok = true;
+      for (int j = 0; j < n_max && ok; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&sh->k_empty[s], ph ^ 1, abort_flag)) {
+          fa_report(kStatusWaitTimeout, 0, 10 + s);
+          ok = false;
+          break;
+        }
+        mbar_arrive_expect_tx(&sh->k_full[s], kTile);
+        for (int c = 0; c < 2; ++c)
+          tma_load_3d(k_smem + s * kTile + c * kSubTile, &tm_k, &sh->k_full[s], c * 64, j * kBlockN, bh);
+        if (!mbar_wait(&sh->v_empty[s], ph ^ 1, abort_flag)) {
+          fa_report(kStatusWaitTimeout, 0, 20 + s);
+          ok = false;
+          break;
+        }
+        mbar_arrive_expect_tx(&sh->v_full[s], kTile);
+        for (int c = 0; c < 2; ++c)
+          tma_load_3d(v_smem + s * kTile + c * kSubTile, &tm_v, &sh->v_full[s], c * 64, j * kBlockN, bh);
+      }
+      if (!ok)
+        bounded_delay(1 << 21);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ UMMA issue
+    if (lane == 0 && n_max > 0) {
+      const uint32_t idesc_s = umma_idesc_f16(kBlockM, kBlockN, p.is_bf16, 0, 0);
+      const uint32_t idesc_o = umma_idesc_f16(kBlockM, kD, p.is_bf16, 0, 1); // V is MN-major
+      const uint32_t q_addr = smem_u32(q_smem), k_addr = smem_u32(k_smem), v_addr = smem_u32(v_smem);
+      bool ok = true;
+
+      // S_t = Q_t K_j^T : K = head dim, two 64-element swizzle chunks x four UMMA K steps
+      auto issue_s = [&](int t, int stage) {
+        const uint32_t d = tmem_base + static_cast<uint32_t>(t * kBlockN);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const uint64_t a = umma_desc_kmajor_sw128(q_addr + t * kTile + c * kSubTile);
+          const uint64_t b = umma_desc_kmajor_sw128(k_addr + stage * kTile + c * kSubTile);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_ss(d, a + static_cast<uint64_t>(2 * k), b + static_cast<uint64_t>(2 * k), idesc_s,
+                    (c | k) ? 1u : 0u);
+        }
+        umma_commit(&sh->s_full[t]);
+      };
+      // O_t += P_t V_j : K = 128 keys in eight steps of 16; P from TMEM (8 packed
+      // columns per step), V rows are keys (128 bytes each), 16 keys = 2048 bytes.
+      auto issue_pv = [&](int t, int stage, bool accumulate) {
+        const uint32_t d = tmem_base + static_cast<uint32_t>(2 * kBlockN + t * kD);
+        const uint32_t a = tmem_base + static_cast<uint32_t>(t * kBlockN);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint64_t b = umma_desc_mnmajor_sw128(v_addr + stage * kTile + kk * 2048, kSubTile, 1024);
+          umma_ts(d, a + static_cast<uint32_t>(kk * 8), b, idesc_o, (accumulate || kk) ? 1u : 0u);
+        }
+      };
+
+      if (!mbar_wait(&sh->q_full, 0, abort_flag)) {
+        fa_report(kStatusWaitTimeout, 1, 1);
+        ok = false;
+      }
+      if (ok && !mbar_wait(&sh->k_full[0], 0, abort_flag)) {
+        fa_report(kStatusWaitTimeout, 1, 2);
+        ok = false;
+      }
+      if (ok) {
+        tc_fence_after_sync();
+        for (int t = 0; t < 2; ++t)
+          if (n_blocks[t] > 0)
+            issue_s(t, 0);
+        umma_commit(&sh->k_empty[0]);
+      }
+      for (int j = 0; j < n_max && ok; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        const int s_next = (j + 1) & 1;
+        const uint32_t ph_next = ((j + 1) >> 1) & 1;
+        bool have_v = false, have_k_next = false;
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (j >= n_blocks[t])
+            continue;
+          if (!have_v) {
+            if (!mbar_wait(&sh->v_full[s], ph, abort_flag)) {
+              fa_report(kStatusWaitTimeout, 1, 30 + s);
+              ok = false;
+              break;
+            }
+            have_v = true;
+          }
+          if (!mbar_wait(&sh->p_full[t], j & 1, abort_flag)) {
+            fa_report(kStatusWaitTimeout, 1, 40 + t);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          issue_pv(t, s, j > 0);
+          if (j + 1 < n_blocks[t]) {
+            if (!have_k_next) {
+              if (!mbar_wait(&sh->k_full[s_next], ph_next, abort_flag)) {
+                fa_report(kStatusWaitTimeout, 1, 50 + s_next);
+                ok = false;
+                break;
+              }
+              tc_fence_after_sync();
+              have_k_next = true;
+            }
+            issue_s(t, s_next);
+          } else {
+            umma_commit(&sh->o_full[t]);
+          }
+        }
+        if (!ok)
+          break;
+        umma_commit(&sh->v_empty[s]);
+        if (have_k_next)
+          umma_commit(&sh->k_empty[s_next]);
+      }
+    }
+  } else if (warp >= 4) {
+    // --------------------------------------------------------------- softmax
+    const int t = (warp - 4) >> 2;
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const int q_row = q_blk * 2 * kBlockM + t * kBlockM + row;
+    const int nb = n_blocks[t];
+    const float c = p.scale_log2e;
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t s_addr = tmem_base + lane_base + static_cast<uint32_t>(t * kBlockN);
+    const uint32_t o_addr = tmem_base + lane_base + static_cast<uint32_t>(2 * kBlockN + t * kD);
+    const bool bf16 = p.is_bf16 != 0;
+    float m_used = -INFINITY; // running maximum the exponentials are taken against (raw score units)
+    float l = 0.0f;           // running sum of unrounded probabilities
+    bool ok = true;
+
+    for (int j = 0; j < nb; ++j) {
+      if (!mbar_wait(&sh->s_full[t], j & 1, abort_flag)) {
+        if (lane == 0)
+          fa_report(kStatusWaitTimeout, 2 + t, 60);
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      uint32_t s[128];
+      tmem_ld_32x32b_x32(s_addr + 0, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+      tmem_ld_32x32b_x32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+      tmem_ld_32x32b_x32(s_addr + 64, *reinterpret_cast<uint32_t(*)[32]>(&s[64]));
+      tmem_ld_32x32b_x32(s_addr + 96, *reinterpret_cast<uint32_t(*)[32]>(&s[96]));
+      tmem_ld_wait();
+
+      const int key0 = j * kBlockN;
+      const bool need_mask = (p.causal && key0 + kBlockN - 1 > q_row - row) || (key0 + kBlockN > p.seq_k);
+      if (need_mask) {
+        const int limit = p.causal ? min(q_row, p.seq_k - 1) : p.seq_k - 1; // last visible key
+#pragma unroll
+        for (int i = 0; i < 128; ++i)
+          if (key0 + i > limit)
+            s[i] = 0xFF800000u; // -inf
+      }
+      float mx0 = __uint_as_float(s[0]), mx1 = __uint_as_float(s[1]);
+      float mx2 = __uint_as_float(s[2]), mx3 = __uint_as_float(s[3]);
+#pragma unroll
+      for (int i = 4; i < 128; i += 4) {
+        mx0 = fmaxf(mx0, __uint_as_float(s[i]));
+        mx1 = fmaxf(mx1, __uint_as_float(s[i + 1]));
+        mx2 = fmaxf(mx2, __uint_as_float(s[i + 2]));
+        mx3 = fmaxf(mx3, __uint_as_float(s[i + 3]));
+      }
+      const float m_new = fmaxf(m_used, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
+      // Lazy rescale: only when some row of this warp moved its maximum by more
+      // than 2^8; otherwise keep the stale maximum (exact after the final divide).
+      const bool need = (m_new - m_used) * c > kRescaleThreshold;
+      if (__any_sync(0xffffffffu, need)) {
+        const float factor = fast_exp2((m_used - m_new) * c);
+        l *= factor;
+        if (j > 0) {
+#pragma unroll 1
+          for (int cc = 0; cc < kD; cc += 32) {
+            uint32_t o[32];
+            tmem_ld_32x32b_x32(o_addr + cc, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+            tmem_st_32x32b_x32(o_addr + cc, o);
+          }
+        }
+        m_used = m_new;
+      }
+      const float neg_mc = -m_used * c;
+      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+      uint32_t pk[64];
+#pragma unroll
+      for (int i = 0; i < 128; i += 4) {
+        const float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), c, neg_mc));
+        const float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), c, neg_mc));
+        const float p2 = fast_exp2(fmaf(__uint_as_float(s[i + 2]), c, neg_mc));
+        const float p3 = fast_exp2(fmaf(__uint_as_float(s[i + 3]), c, neg_mc));
+        l0 += p0;
+        l1 += p1;
+        l2 += p2;
+        l3 += p3;
+        pk[i / 2] = pack2(p0, p1, bf16);
+        pk[i / 2 + 1] = pack2(p2, p3, bf16);
+      }
+      l += (l0 + l1) + (l2 + l3);
+      tmem_st_32x32b_x32(s_addr + 0, *reinterpret_cast<uint32_t(*)[32]>(&pk[0]));
+      tmem_st_32x32b_x32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&pk[32]));
+      tmem_st_wait();
+      tc_fence_before_sync();
+      mbar_arrive(&sh->p_full[t]);
+    }
+
+    if (ok && nb > 0) {
+      if (!mbar_wait(&sh->o_full[t], 0, abort_flag)) {
+        if (lane == 0)
+          fa_report(kStatusWaitTimeout, 2 + t, 70);
+      } else {
+        tc_fence_after_sync();
+        const float inv = 1.0f / l;
+        const bool live = q_row < p.seq_q;
+        uint8_t *out_row = static_cast<uint8_t *>(p.O) +
+                           (static_cast<size_t>(bh) * p.seq_q + static_cast<size_t>(live ? q_row : 0)) * kD * 2;
+#pragma unroll 1
+        for (int cc = 0; cc < kD; cc += 32) {
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(o_addr + cc, o);
+          tmem_ld_wait();
+          uint32_t w[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            w[i] = pack2(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv, bf16);
+          if (live) {
+            uint4 *dst = reinterpret_cast<uint4 *>(out_row + cc * 2);
+#pragma unroll
+            for (int v = 0; v < 4; ++v)
+              dst[v] = make_uint4(w[4 * v], w[4 * v + 1], w[4 * v + 2], w[4 * v + 3]);
+          }
+        }
+        if (p.lse && live)
+          p.lse[static_cast<size_t>(bh) * p.seq_q + q_row] = m_used * p.scale + logf(l);
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+} // namespace
+
+int launch_flash_attention(const FaParams &p, const void *Q, const void *K, const void *V, int sm_count,
+                           cudaStream_t stream) {
+  (void)sm_count;
+  if (p.head_dim != kD)
+    return WAVE_E_UNSUPPORTED;
+  CUtensorMap tq, tk, tv;
+  const uint32_t box[3] = {64, 128, 1};
+  const uint64_t row_bytes = static_cast<uint64_t>(kD) * 2;
+  {
+    const uint64_t dims[3] = {kD, static_cast<uint64_t>(p.seq_q), static_cast<uint64_t>(p.batch_heads)};
+    const uint64_t strides[2] = {row_bytes, row_bytes * static_cast<uint64_t>(p.seq_q)};
+    int rc = make_tensor_map_16bit(&tq, p.is_bf16, Q, 3, dims, strides, box);
+    if (rc != WAVE_OK)
+      return rc;
+  }
+  {
+    const uint64_t dims[3] = {kD, static_cast<uint64_t>(p.seq_k), static_cast<uint64_t>(p.batch_heads)};
+    const uint64_t strides[2] = {row_bytes, row_bytes * static_cast<uint64_t>(p.seq_k)};
+    int rc = make_tensor_map_16bit(&tk, p.is_bf16, K, 3, dims, strides, box);
+    if (rc != WAVE_OK)
+      return rc;
+    rc = make_tensor_map_16bit(&tv, p.is_bf16, V, 3, dims, strides, box);
+    if (rc != WAVE_OK)
+      return rc;
+  }
+  cudaError_t err = cudaFuncSetAttribute(fa_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  if (err != cudaSuccess)
+    return WAVE_E_CUDA;
+  dim3 grid(static_cast<unsigned>((p.seq_q + 2 * kBlockM - 1) / (2 * kBlockM)), static_cast<unsigned>(p.batch_heads));
+  fa_fwd_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tq, tk, tv, p);
+  err = cudaGetLastError();
+  return err == cudaSuccess ? WAVE_OK : WAVE_E_CUDA;
+}
+
 cudaError_t fa_read_status(int out[4], bool clear) {
   cudaError_t err = cudaMemcpyFromSymbol(out, g_fa_status, sizeof(int) * 4);
   if (err == cudaSuccess && clear) {
@@ -12,4 +443,5 @@ cudaError_t fa_read_status(int out[4], bool clear) {
   }
   return err;
 }
+
 } // namespace wave

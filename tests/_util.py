@@ -21,10 +21,17 @@ def out_to_f32(torch, t) -> np.ndarray:
     return t.float().cpu().numpy()
 
 
-def runner_tolerance_ok(got: np.ndarray, exp: np.ndarray):
+def runner_tolerance_ok(got: np.ndarray, exp: np.ndarray, out_type: str = "f32"):
     """|got-exp| <= 1e-2 + 1e-3*|exp| for every element
-    (tools/wave-matmul-calibrate/wave-matmul-calibrate-runner.cpp:907)."""
+    (tools/wave-matmul-calibrate/wave-matmul-calibrate-runner.cpp:907).
+
+    The reference only stores f32 or f16.  A bf16 result keeps 8 significant
+    bits, so two correct f32 accumulations that differ in their last bits can
+    round to neighbouring bf16 values; for bf16 the relative term is therefore
+    one bf16 unit in the last place (2**-7), still inside the 1e-2 maximum
+    relative error this backend is specified to."""
     diff = np.abs(got.astype(np.float64) - exp.astype(np.float64))
-    limit = 1.0e-2 + 1.0e-3 * np.abs(exp.astype(np.float64))
+    rel = 2.0 ** -7 if out_type == "bf16" else 1.0e-3
+    limit = 1.0e-2 + rel * np.abs(exp.astype(np.float64))
     bad = ~(diff <= limit)  # catches NaN too
     return not bad.any(), float(np.nanmax(diff)) if diff.size else 0.0, int(bad.sum())

@@ -1,0 +1,133 @@
+"""GPU parity of the flash-attention forward against the f64 CPU oracle,
+through the C ABI.
+
+Mirrors the reference's runtime checks: the gfx950 runner compares sampled
+heads/rows with a f64 reference and passes on max-abs <= 3e-2
+(tools/wave-fa-calibrate/wave-fa-gfx950-runner.cpp:204-232, 384-394;
+test/Integration/wave_flash_attention_gfx950_runtime.mlir:3-22).  Causal
+masking, a caller-supplied scale, f16 I/O and ragged lengths are extensions
+and are checked against the oracle's labelled extensions.
+"""
+import numpy as np
+import pytest
+
+from _util import to_device_bits
+
+pytestmark = pytest.mark.gpu
+
+REFERENCE_MAX_ABS = 3.0e-2  # wave-fa-gfx950-runner.cpp:388
+
+
+def run_fa(torch, wc, q_bits, k_bits, v_bits, io_name, batch, heads, causal, scale=0.0, want_lse=False):
+    BH, Sq, D = q_bits.shape
+    Sk = k_bits.shape[1]
+    assert BH == batch * heads
+    desc = wc.fa_desc(batch, heads, Sq, Sk, D, scale=scale, causal=causal, io_type=wc.TYPE_BY_NAME[io_name])
+    q, k, v = (to_device_bits(torch, x) for x in (q_bits, k_bits, v_bits))
+    dt = torch.bfloat16 if io_name == "bf16" else torch.float16
+    o = torch.full((BH, Sq, D), float("nan"), dtype=dt, device="cuda")
+    lse = torch.full((BH, Sq), float("nan"), dtype=torch.float32, device="cuda") if want_lse else None
+    wc.flash_attention_fwd(desc, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                           lse.data_ptr() if want_lse else 0, torch.cuda.current_stream().cuda_stream)
+    wc.check_device_status()
+    out = o.float().cpu().numpy()
+    return (out, lse.cpu().numpy()) if want_lse else out
+
+
+def lcg_qkv(oracle, BH, Sq, Sk, D, t, seed, input_scale=1):
+    q = oracle.fa_input_bits(BH * Sq * D, t, seed, 0, 0.125 * input_scale).reshape(BH, Sq, D)
+    k = oracle.fa_input_bits(BH * Sk * D, t, seed, 1, 0.125 * input_scale).reshape(BH, Sk, D)
+    v = oracle.fa_input_bits(BH * Sk * D, t, seed, 2, 0.25).reshape(BH, Sk, D)
+    return q, k, v
+
+
+def normal_qkv(oracle, BH, Sq, Sk, D, t, seed):
+    return (oracle.baseline_inputs((BH, Sq, D), "normal", seed, 0, t),
+            oracle.baseline_inputs((BH, Sk, D), "normal", seed, 1, t),
+            oracle.baseline_inputs((BH, Sk, D), "normal", seed, 2, t))
+
+
+def check(got, want, tag=""):
+    diff = np.abs(got.astype(np.float64) - want.astype(np.float64))
+    assert not np.isnan(got).any(), f"{tag}: NaN in output"
+    worst = float(diff.max())
+    assert worst <= REFERENCE_MAX_ABS, f"{tag}: max abs {worst}"
+    # stated tolerance for 16-bit inputs with f32 accumulation:
+    # |d| <= 1e-2 + 1e-2*|exp| per element, mean absolute error <= 1e-3
+    assert (diff <= 1.0e-2 + 1.0e-2 * np.abs(want)).all(), f"{tag}: max abs {worst}"
+    assert float(diff.mean()) <= 1.0e-3, f"{tag}: mean abs {diff.mean()}"
+
+
+@pytest.mark.parametrize("batch,heads,S,causal,seed", [
+    (1, 1, 256, False, 0),
+    (1, 2, 256, False, 7),
+    (1, 2, 512, False, 3),
+    (2, 2, 512, True, 5),
+    (1, 1, 1024, True, 1),
+    (1, 3, 768, False, 2),
+])
+def test_runner_inputs_all_rows(cuda, wc, oracle, batch, heads, S, causal, seed):
+    """Inputs of the reference runner (bf16 LCG, Q/K x0.125, V x0.25), every
+    row checked (the runner checks all rows when S <= 512)."""
+    BH, D, t = batch * heads, 128, oracle.BF16
+    q, k, v = lcg_qkv(oracle, BH, S, S, D, t, seed)
+    got = run_fa(cuda, wc, q, k, v, "bf16", batch, heads, causal)
+    want = oracle.fa_ref(q, k, v, t, 1.0 / np.sqrt(128.0), causal=causal)
+    check(got, want, f"S={S} causal={causal}")
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_normal_inputs_config_shape_small(cuda, wc, oracle, causal):
+    """N(0,1) Q/K/V, scale 1/sqrt(128): the benchmark's distribution at
+    B=1, H=2, S=512, every row checked."""
+    t = oracle.BF16
+    q, k, v = normal_qkv(oracle, 2, 512, 512, 128, t, seed=17)
+    got, lse = run_fa(cuda, wc, q, k, v, "bf16", 1, 2, causal, want_lse=True)
+    want, want_lse = oracle.fa_ref(q, k, v, t, 1.0 / np.sqrt(128.0), causal=causal, want_lse=True)
+    check(got, want, f"normal causal={causal}")
+    assert np.abs(lse.astype(np.float64) - want_lse).max() <= 2e-3
+
+
+@pytest.mark.parametrize("Sq,Sk,causal", [(144, 400, False), (272, 272, True), (16, 16, True), (128, 128, False),
+                                          (400, 144, False)])
+def test_ragged_lengths(cuda, wc, oracle, Sq, Sk, causal):
+    t = oracle.BF16
+    q, k, v = normal_qkv(oracle, 3, Sq, Sk, 128, t, seed=Sq + Sk)
+    got = run_fa(cuda, wc, q, k, v, "bf16", 1, 3, causal)
+    want = oracle.fa_ref(q, k, v, t, 1.0 / np.sqrt(128.0), causal=causal)
+    check(got, want, f"{Sq}x{Sk} causal={causal}")
+
+
+def test_f16_io_and_custom_scale(cuda, wc, oracle):
+    t = oracle.F16
+    q, k, v = normal_qkv(oracle, 2, 384, 384, 128, t, seed=23)
+    got = run_fa(cuda, wc, q, k, v, "f16", 2, 1, True, scale=0.05)
+    want = oracle.fa_ref(q, k, v, t, float(np.float32(0.05)), causal=True)
+    check(got, want, "f16")
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_long_sequence_sampled(cuda, wc, oracle, causal):
+    """S=4096 (the benchmark's sequence length) on 6 heads, checked on the
+    reference runner's sample of heads and rows
+    (wave-fa-gfx950-runner.cpp:204-232)."""
+    t = oracle.BF16
+    batch, heads, S = 2, 3, 4096
+    q, k, v = normal_qkv(oracle, batch * heads, S, S, 128, t, seed=4)
+    got = run_fa(cuda, wc, q, k, v, "bf16", batch, heads, causal)
+    hs, rs = oracle.fa_sample_heads(batch * heads), oracle.fa_sample_rows(S)
+    want = oracle.fa_ref(q, k, v, t, 1.0 / np.sqrt(128.0), causal=causal, heads=hs, rows=rs)
+    check(got[np.ix_(hs, rs)], want, f"S=4096 causal={causal}")
+
+
+def test_rows_are_convex_combinations(cuda, wc, oracle):
+    """Size-independent property: with V constant along keys, every output row
+    equals that constant whatever the scores are."""
+    t = oracle.BF16
+    BH, S = 4, 1024
+    q, k, _ = normal_qkv(oracle, BH, S, S, 128, t, seed=8)
+    vrow = oracle.baseline_inputs((BH, 1, 128), "normal", 8, 5, t)
+    v = np.ascontiguousarray(np.broadcast_to(vrow, (BH, S, 128)))
+    got = run_fa(cuda, wc, q, k, v, "bf16", 1, BH, True)
+    want = np.broadcast_to(oracle.from_bits(vrow, t), (BH, S, 128))
+    assert np.abs(got - want).max() <= 1e-2 * np.abs(want).max()
