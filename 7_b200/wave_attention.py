@@ -1,0 +1,88 @@
+"""Host-side mirror of the reference's attention interfaces on top of the CUDA
+backend: the operator-level signature of
+integrations/tlx/workloads/amd_fa_wave.py:1671-1682
+(`attention(q, k, v, sm_scale=None, causal=False, *, out=None)`, rank-4
+contiguous (B, H, N, D) tensors) and the input generators of the calibrate
+runners (tools/wave-fa-calibrate/wave-fa-gfx950-runner.cpp:188-202,
+python/mlir/dialects/wave_attention.py:225-245).
+
+There is no CPU implementation of attention here.
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+
+from . import wave_cuda as wc
+from .wave_matmul import deterministic_random_values, input_bits
+
+HEAD_DIM = 128   # wave_flash_attention.py: the production kernel's only head dimension
+BLOCK_M = 256    # query rows per workgroup (wave_flash_attention.py:23)
+
+
+def make_runner_inputs(batch: int, heads: int, sequence: int, *, seed: int = 0, input_scale: int = 1,
+                       io_type: str = "bf16"):
+    """Q, K (x0.125*input_scale) and V (x0.25) from LCG streams 0, 1, 2, rounded
+    to the I/O type, shaped [B*H, S, 128] (wave-fa-gfx950-runner.cpp:410-413)."""
+    n = batch * heads * sequence * HEAD_DIM
+    shape = (batch * heads, sequence, HEAD_DIM)
+    q = deterministic_random_values(n, seed=seed, stream=0, scale=0.125 * input_scale)
+    k = deterministic_random_values(n, seed=seed, stream=1, scale=0.125 * input_scale)
+    v = deterministic_random_values(n, seed=seed, stream=2, scale=0.25)
+    return tuple(input_bits(x, io_type).reshape(shape) for x in (q, k, v))
+
+
+def flops(batch: int, heads: int, sequence: int, head_dim: int = HEAD_DIM, causal: bool = False) -> float:
+    """4*B*H*S^2*D (wave_flash_attention.py:138-139); for causal, the unmasked pairs only."""
+    pairs = sequence * (sequence + 1) / 2 if causal else float(sequence) * sequence
+    return 4.0 * batch * heads * head_dim * pairs
+
+
+def attention(q, k, v, sm_scale: float | None = None, causal: bool = False, *, out=None, lse=None):
+    """Flash-attention forward on CUDA tensors of shape (B, H, N, D), bf16 or
+    f16, contiguous, same device.  `sm_scale` defaults to 1/sqrt(D).  `out` may
+    alias `q` only in the sense of being a distinct tensor of the same shape;
+    returns `out`."""
+    import torch
+
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+        raise ValueError("q, k and v must be rank-4 (B, H, N, D) tensors")
+    if not (q.is_cuda and k.is_cuda and v.is_cuda):
+        raise ValueError("q, k and v must be CUDA tensors: this backend has no CPU path")
+    if k.shape != v.shape or q.shape[:2] != k.shape[:2] or q.shape[3] != k.shape[3]:
+        raise ValueError("q, k and v must agree on batch, heads and head_dim; k and v on sequence")
+    if q.dtype not in (torch.bfloat16, torch.float16) or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise ValueError("q, k and v must share dtype bf16 or f16")
+    if not (q.is_contiguous() and k.is_contiguous() and v.is_contiguous()):
+        raise ValueError("q, k and v must be contiguous")
+    B, H, Nq, D = q.shape
+    Nk = k.shape[2]
+    if out is None:
+        out = torch.empty_like(q)
+    elif out.shape != q.shape or out.dtype != q.dtype or not out.is_contiguous():
+        raise ValueError("out must match q in shape and dtype and be contiguous")
+    desc = wc.fa_desc(B, H, Nq, Nk, D, scale=float(sm_scale) if sm_scale is not None else 1.0 / math.sqrt(D),
+                      causal=causal, io_type=wc.BF16 if q.dtype == torch.bfloat16 else wc.F16)
+    try:
+        wc.fa_validate(desc)
+    except wc.WaveCudaError as err:
+        raise ValueError(err.message) from None
+    wc.flash_attention_fwd(desc, q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                           lse.data_ptr() if lse is not None else 0, torch.cuda.current_stream().cuda_stream)
+    return out
+
+
+def run_attention_host(q_bits: np.ndarray, k_bits: np.ndarray, v_bits: np.ndarray, batch: int, heads: int, *,
+                       sm_scale: float | None = None, causal: bool = False, io_type: str = "bf16") -> np.ndarray:
+    """Host-buffer form: [B*H, S, D] 16-bit patterns in, the same out."""
+    q, k, v = (np.ascontiguousarray(x, np.uint16) for x in (q_bits, k_bits, v_bits))
+    BH, Sq, D = q.shape
+    if BH != batch * heads:
+        raise ValueError("leading dimension must be batch*heads")
+    desc = wc.fa_desc(batch, heads, Sq, k.shape[1], D, scale=float(sm_scale or 0.0), causal=causal,
+                      io_type=wc.TYPE_BY_NAME[io_type])
+    out = np.zeros_like(q)
+    wc.flash_attention_fwd_host(desc, q.ctypes.data, k.ctypes.data, v.ctypes.data, out.ctypes.data)
+    wc.check_device_status()
+    return out

@@ -1,0 +1,137 @@
+"""The C-ABI library without a GPU: it loads, exports every symbol the header
+declares, validates descriptors with the reference's rules and messages
+(python/mlir/dialects/wave_matmul.py:533-619; the reference checks ~25
+argument failures the same way, test/Integration/wave_matmul_rand_int_inputs.mlir:29-64),
+sizes the Stream-K workspace like the reference runner, and fails loudly --
+never silently falls back -- when asked to compute without a device."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_functions():
+    text = open(os.path.join(ROOT, "include", "wave_cuda.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    names = re.findall(r"\b(wave_cuda_\w+|_mlir_ciface_\w+)\s*\(", text)
+    return sorted(set(names))
+
+
+def test_library_exports_every_declared_symbol(wc):
+    lib = wc.lib()
+    names = declared_functions()
+    assert len(names) >= 20
+    for name in names:
+        assert hasattr(lib, name), f"{name} is declared in include/wave_cuda.h but not exported"
+    assert sorted(wc.EXPORTS) == names
+    assert b"sm_100a" in lib.wave_cuda_version()
+
+
+@pytest.mark.parametrize("kwargs,message", [
+    (dict(M=33), "M must be a positive multiple of 16; got 33"),
+    (dict(N=0), "N must be a positive multiple of 16; got 0"),
+    (dict(K=-16), "K must be a positive multiple of 16; got -16"),
+    (dict(bm=0), "BM and BN must be >= 1; got BM=0, BN=2"),
+    (dict(bn=3), "BN must be a positive power of two (for the wave-id decomposition); got BN=3"),
+    (dict(wave_k_tiles=0), "wave_m_tiles, wave_n_tiles and wave_k_tiles must be >= 1; got wave_m_tiles=1, "
+                           "wave_n_tiles=1, wave_k_tiles=0"),
+    (dict(bm=3), "BM * wave_m_tiles (=3) must divide M/16 (=4)"),
+    (dict(bn=4, wave_n_tiles=3), "BN * wave_n_tiles (=12) must divide N/16 (=4)"),
+    (dict(wave_k_tiles=3), "wave_k_tiles (=3) must divide K/16 (=4)"),
+    (dict(M=1024, N=1024, bm=8, bn=8), "BM * BN must be <= 32 (RDNA3 workgroup wave cap); got BM=8, BN=8 (product=64)"),
+    (dict(cta_group_m=0), "cta_group_m must be >= 1; got 0"),
+    (dict(cta_group_m=3), "cta_group_m currently requires M_blocks to divide evenly; got M_blocks=4, cta_group_m=3"),
+    (dict(out_layout=2), "output_layout must be one of row-major, column-major; got 2"),
+    (dict(in_type=2), "input_type must be one of f16, bf16; got 2"),
+    (dict(ldc=72), "ldc must be 0 or a multiple of 16"),
+])
+def test_gemm_validation_messages(wc, kwargs, message):
+    base = dict(M=64, N=64, K=64)
+    base.update(kwargs)
+    M, N, K = base.pop("M"), base.pop("N"), base.pop("K")
+    with pytest.raises(wc.WaveCudaError) as err:
+        wc.gemm_validate(wc.gemm_desc(M, N, K, **base))
+    assert message in err.value.message
+    assert err.value.code in (wc.E_INVALID, wc.E_UNSUPPORTED)
+
+
+def test_valid_descriptors_pass(wc):
+    wc.gemm_validate(wc.gemm_desc(32, 32, 64, bm=2, bn=2, wave_k_tiles=2))  # the reference's --compare-cpu case
+    wc.gemm_validate(wc.gemm_desc(8192, 8192, 8192, bm=4, bn=4, wave_m_tiles=2, wave_n_tiles=4, in_type=wc.BF16,
+                                  out_type=wc.BF16, cta_group_m=4))
+    d = wc.GemmDesc()
+    wc.lib().wave_cuda_gemm_desc_init(C.byref(d), 32, 32, 32)
+    assert (d.bm, d.bn, d.in_type, d.out_type, d.streamk_workers) == (1, 2, wc.F16, wc.F32, 1)
+    wc.gemm_validate(d)
+
+
+def test_streamk_workspace_sizes(wc, oracle):
+    """Scratch = workers * 2 slots * tile * 4 bytes and one counter per output
+    tile, the reference's formula (runner.cpp:393-408) with this backend's
+    128 x tile_n tile in place of 256 x 256."""
+    d = wc.gemm_desc(512, 768, 1024, bm=4, bn=4, wave_m_tiles=2, wave_n_tiles=4, streamk_workers=5)
+    scratch, counters = wc.gemm_workspace_bytes(d)
+    assert scratch == 5 * 2 * 128 * 256 * 4
+    assert counters == (512 // 128) * (768 // 256) * 4
+    assert wc.gemm_workspace_bytes(wc.gemm_desc(512, 768, 1024, streamk_workers=1)) == (0, 0)
+    with pytest.raises(wc.WaveCudaError) as err:
+        wc.gemm_workspace_bytes(wc.gemm_desc(128, 256, 64, bm=4, bn=4, wave_m_tiles=2, wave_n_tiles=4,
+                                             streamk_workers=9))
+    assert "workers must be in [1, total_iterations]" in err.value.message
+    R = oracle.ref_lib()
+    if R is not None:  # the reference's own sizing for its 256x256 tiles
+        assert R.wave_ref_streamk_scratch_bytes(5) == 5 * 2 * 256 * 256 * 4
+        assert R.wave_ref_streamk_counter_elements(512, 768) == 6
+
+
+@pytest.mark.parametrize("kwargs,message", [
+    (dict(batch=0), "batch and heads must be positive"),
+    (dict(seq_q=100), "sequence lengths must be positive multiples of 16"),
+    (dict(head_dim=96), "head_dim must be 128 or 64"),
+    (dict(io_type=2), "io_type must be bf16 or f16"),
+    (dict(causal=True, seq_k=512), "causal attention requires seq_q == seq_k"),
+    (dict(scale=-1.0), "scale must be finite"),
+])
+def test_attention_validation_messages(wc, kwargs, message):
+    base = dict(batch=1, heads=2, seq_q=256, seq_k=256, head_dim=128)
+    base.update(kwargs)
+    with pytest.raises(wc.WaveCudaError) as err:
+        wc.fa_validate(wc.fa_desc(base.pop("batch"), base.pop("heads"), base.pop("seq_q"), base.pop("seq_k"),
+                                  base.pop("head_dim"), **base))
+    assert message in err.value.message
+
+
+def test_memref_shims_return_data_plus_offset(wc):
+    """runtime/wave_runtime.cpp:35-40: data + offset, in elements."""
+    class MemRef(C.Structure):
+        _fields_ = [("base", C.c_void_p), ("data", C.c_void_p), ("offset", C.c_int64), ("size", C.c_int64),
+                    ("stride", C.c_int64)]
+    lib = wc.lib()
+    m = MemRef(0x1000, 0x2000, 3, 16, 1)
+    for name, width in (("i8", 1), ("f16", 2), ("bf16", 2), ("i32", 4), ("f32", 4), ("i64", 8), ("f64", 8)):
+        fn = getattr(lib, f"_mlir_ciface_wave_memref_to_ptr_global_{name}")
+        assert fn(C.byref(m)) == 0x2000 + 3 * width
+
+
+def test_unknown_kernel_name_is_rejected(wc):
+    fn = C.c_void_p()
+    d = wc.gemm_desc(64, 64, 64)
+    rc = wc.lib().wave_cuda_module_get_function(b"no_such_kernel", C.byref(d), C.byref(fn))
+    assert rc == wc.E_NOT_FOUND and b"no kernel named" in wc.lib().wave_cuda_last_error()
+
+
+def test_compute_without_a_device_fails_loudly(wc):
+    """No CPU fallback: on a machine without a CUDA device the host-buffer GEMM
+    returns WAVE_E_CUDA instead of computing anything."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a CUDA device is present")
+    import numpy as np
+    a = np.zeros((16, 16), np.uint16)
+    c = np.zeros((16, 16), np.float32)
+    with pytest.raises(wc.WaveCudaError) as err:
+        wc.gemm_host(wc.gemm_desc(16, 16, 16, bn=1), a.ctypes.data, a.ctypes.data, c.ctypes.data)
+    assert err.value.code == wc.E_CUDA
