@@ -1,0 +1,68 @@
+// Pieces shared by the one-CTA and the CTA-pair GEMM kernels: tile
+// rasterisation and the register -> global-memory epilogue stores.
+#pragma once
+#include "gemm_sm100.h"
+#include "sm100_ptx.cuh"
+
+namespace wave {
+namespace gemm_detail {
+
+// Linear tile id -> (m block, n block) with grouped-M rasterisation, the
+// portable half of the reference's CTA remap (wave_matmul.py:1248-1276):
+// consecutive ids walk down `group_m` row blocks before moving one column
+// block over, so CTAs running at the same time share A and B panels in L2.
+__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int group_m, int &mb, int &nb) {
+  const int per_group = group_m * num_n;
+  const int group = tile / per_group;
+  const int first_m = group * group_m;
+  const int rows = min(num_m - first_m, group_m);
+  const int in_group = tile - group * per_group;
+  mb = first_m + in_group % rows;
+  nb = in_group / rows;
+}
+
+template <int OUT> struct OutT;
+template <> struct OutT<WAVE_GEMM_OUT_F32> { using type = float; };
+template <> struct OutT<WAVE_GEMM_OUT_F16> { using type = __half; };
+template <> struct OutT<WAVE_GEMM_OUT_BF16> { using type = __nv_bfloat16; };
+
+__device__ __forceinline__ void store_elem(float *p, float v) { *p = v; }
+__device__ __forceinline__ void store_elem(__half *p, float v) { *p = __float2half_rn(v); }
+__device__ __forceinline__ void store_elem(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
+
+// Stores `W` consecutive-n values of row m.  When n is the contiguous
+// direction the values go out as 16-byte vectors; otherwise (m contiguous)
+// each value is a scalar store that coalesces across the warp's 32 rows.
+template <typename T, int W>
+__device__ __forceinline__ void store_row_chunk(const GemmParams &p, int m, int n0, const float (&v)[W]) {
+  if (m >= p.M)
+    return;
+  T *base = reinterpret_cast<T *>(p.C) + static_cast<long long>(m) * p.stride_m +
+            static_cast<long long>(n0) * p.stride_n;
+  if (p.stride_n == 1) {
+    constexpr int per_vec = 16 / sizeof(T);
+#pragma unroll
+    for (int j = 0; j < W; j += per_vec) {
+      if (n0 + j < p.N) { // N is a multiple of 16, so a started vector is whole
+        if constexpr (sizeof(T) == 4) {
+          float4 q = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+          *reinterpret_cast<float4 *>(base + j) = q;
+        } else {
+          T tmp[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e)
+            store_elem(&tmp[e], v[j + e]);
+          *reinterpret_cast<uint4 *>(base + j) = *reinterpret_cast<uint4 *>(tmp);
+        }
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < W; ++j)
+      if (n0 + j < p.N)
+        store_elem(base + static_cast<long long>(j) * p.stride_n, v[j]);
+  }
+}
+
+} // namespace gemm_detail
+} // namespace wave

@@ -32,4 +32,12 @@ cudaError_t launch_gemm(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, co
                         int grid, cudaStream_t stream);
 cudaError_t gemm_read_status(int out[4], bool clear);
 
+// CTA-pair kernel (256 x 256 tiles, tcgen05 cta_group::2); data-parallel only.
+int gemm_pair_tile_m();
+int gemm_pair_tile_n();
+int gemm_pair_box_rows();
+cudaError_t launch_gemm_pair(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, const GemmParams &p, int grid,
+                             cudaStream_t stream);
+cudaError_t gemm_pair_read_status(int out[4], bool clear);
+
 } // namespace wave

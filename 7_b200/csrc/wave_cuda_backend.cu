@@ -13,6 +13,7 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -109,6 +110,8 @@ int elem_size(int type) { return type == WAVE_F32 ? 4 : 2; }
 
 // ---------------------------------------------------------------- GEMM plan
 struct GemmPlan {
+  bool pair;          // CTA-pair kernel: 256 x 256 tiles, two CTAs per tile
+  int tile_m;         // kernel-space tile rows
   bool swapped;       // kernel computes C^T = B * A^T (skinny M)
   int Mk, Nk;         // kernel-space extents
   int tile_n;         // kernel-space tile columns
@@ -142,7 +145,28 @@ int make_plan(const wave_gemm_desc &d, int sms, bool have_workspace, GemmPlan *p
   const int cap = snap_tile_n(p.Nk);
   if (p.tile_n > cap)
     p.tile_n = cap;
-  p.num_m = (p.Mk + tile_m - 1) / tile_m;
+  p.tile_m = tile_m;
+  // Large tiles on a large problem go to the CTA-pair kernel (data-parallel only).
+  p.pair = !p.swapped && want_m >= wave::gemm_pair_tile_m() && want_n >= wave::gemm_pair_tile_n() &&
+           d.M >= wave::gemm_pair_tile_m() && d.N >= wave::gemm_pair_tile_n() && d.streamk_workers <= 1;
+  // WAVE_CUDA_GEMM_KERNEL=pair|single overrides the size heuristic below (the
+  // tiling knobs and shape must still allow the pair kernel).
+  const char *force = getenv("WAVE_CUDA_GEMM_KERNEL");
+  if (force && strcmp(force, "single") == 0)
+    p.pair = false;
+  if (p.pair && sms > 0 && !(force && strcmp(force, "pair") == 0)) {
+    // With few 256 x 256 tiles per CTA pair the last, partly filled round of
+    // tiles costs more than the pair kernel saves; the one-CTA kernel's
+    // 128 x 256 tiles fill the machine better there (measured at 4096^3).
+    const long long pair_tiles = static_cast<long long>((d.M + 255) / 256) * ((d.N + 255) / 256);
+    if (pair_tiles < 6ll * (sms / 2))
+      p.pair = false;
+  }
+  if (p.pair) {
+    p.tile_m = wave::gemm_pair_tile_m();
+    p.tile_n = wave::gemm_pair_tile_n();
+  }
+  p.num_m = (p.Mk + p.tile_m - 1) / p.tile_m;
   p.num_n = (p.Nk + p.tile_n - 1) / p.tile_n;
   p.k_iters = (d.K + tile_k - 1) / tile_k;
   const long long tiles = static_cast<long long>(p.num_m) * p.num_n;
@@ -152,7 +176,7 @@ int make_plan(const wave_gemm_desc &d, int sms, bool have_workspace, GemmPlan *p
   int workers = d.streamk_workers;
   if (workers == 0) { // auto
     workers = 1;
-    if (sms > 0 && have_workspace) {
+    if (sms > 0 && have_workspace && !p.pair) {
       const long long waves = (tiles + sms - 1) / sms;
       const double efficiency = static_cast<double>(tiles) / static_cast<double>(waves * sms);
       if (efficiency < 0.8 && total_iters >= sms && p.k_iters >= 8)
@@ -170,6 +194,10 @@ int make_plan(const wave_gemm_desc &d, int sms, bool have_workspace, GemmPlan *p
   } else {
     p.streamk_workers = 0;
     p.grid = sms > 0 ? static_cast<int>(tiles < sms ? tiles : sms) : static_cast<int>(tiles);
+    if (p.pair) {
+      const long long pairs = sms > 0 ? (tiles < sms / 2 ? tiles : sms / 2) : tiles;
+      p.grid = static_cast<int>(2 * pairs);
+    }
   }
   *plan = p;
   return WAVE_OK;
@@ -345,7 +373,7 @@ int wave_cuda_gemm_plan(const wave_gemm_desc *d, int *tile_m, int *tile_n, int *
   if ((rc = make_plan(*d, sms, true, &plan)) != WAVE_OK)
     return rc;
   if (tile_m)
-    *tile_m = wave::gemm_tile_m();
+    *tile_m = plan.tile_m;
   if (tile_n)
     *tile_n = plan.tile_n;
   if (grid)
@@ -384,14 +412,16 @@ int wave_cuda_gemm(const wave_gemm_desc *d, const void *A, const void *B, void *
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(d->K), static_cast<uint64_t>(plan.Mk)};
     const uint64_t strides[1] = {static_cast<uint64_t>(d->K) * 2};
-    const uint32_t box[2] = {static_cast<uint32_t>(tile_k), static_cast<uint32_t>(tile_m)};
+    const uint32_t box[2] = {static_cast<uint32_t>(tile_k),
+                             static_cast<uint32_t>(plan.pair ? wave::gemm_pair_box_rows() : tile_m)};
     if ((rc = wave::make_tensor_map_16bit(&ta, bf16, Ak, 2, dims, strides, box)) != WAVE_OK)
       return rc;
   }
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(d->K), static_cast<uint64_t>(plan.Nk)};
     const uint64_t strides[1] = {static_cast<uint64_t>(d->K) * 2};
-    const uint32_t box[2] = {static_cast<uint32_t>(tile_k), static_cast<uint32_t>(plan.tile_n)};
+    const uint32_t box[2] = {static_cast<uint32_t>(tile_k),
+                             static_cast<uint32_t>(plan.pair ? wave::gemm_pair_box_rows() : plan.tile_n)};
     if ((rc = wave::make_tensor_map_16bit(&tb, bf16, Bk, 2, dims, strides, box)) != WAVE_OK)
       return rc;
   }
@@ -418,9 +448,9 @@ int wave_cuda_gemm(const wave_gemm_desc *d, const void *A, const void *B, void *
   // tiles; keep the same number of rows per group, at least one 128-row block.
   {
     long long rows = static_cast<long long>(d->cta_group_m) * 16 * d->bm * d->wave_m_tiles;
-    int g = static_cast<int>(rows / tile_m);
+    int g = static_cast<int>(rows / plan.tile_m);
     if (d->cta_group_m == 1)
-      g = 16; // the reference's "no grouping" default: use the backend's own
+      g = 2048 / plan.tile_m; // the reference's "no grouping" default: use the backend's own
     if (g < 1)
       g = 1;
     if (g > plan.num_m)
@@ -431,7 +461,8 @@ int wave_cuda_gemm(const wave_gemm_desc *d, const void *A, const void *B, void *
   p.scratch = static_cast<float *>(workspace);
   p.counters = workspace ? reinterpret_cast<int *>(static_cast<char *>(workspace) + plan.scratch_bytes) : nullptr;
 
-  cudaError_t err = wave::launch_gemm(ta, tb, p, plan.tile_n, plan.grid, static_cast<cudaStream_t>(stream));
+  cudaError_t err = plan.pair ? wave::launch_gemm_pair(ta, tb, p, plan.grid, static_cast<cudaStream_t>(stream))
+                              : wave::launch_gemm(ta, tb, p, plan.tile_n, plan.grid, static_cast<cudaStream_t>(stream));
   if (err != cudaSuccess)
     return cuda_fail(err, "gemm launch");
   return WAVE_OK;
@@ -488,8 +519,8 @@ int wave_cuda_fa_validate(const wave_fa_desc *d) {
   if (d->seq_q <= 0 || d->seq_k <= 0 || d->seq_q % 16 != 0 || d->seq_k % 16 != 0)
     return fail(WAVE_E_INVALID, "sequence lengths must be positive multiples of 16; got seq_q=%d, seq_k=%d",
                 d->seq_q, d->seq_k);
-  if (d->head_dim != 128 && d->head_dim != 64)
-    return fail(WAVE_E_UNSUPPORTED, "head_dim must be 128 or 64; got %d", d->head_dim);
+  if (d->head_dim != 128)
+    return fail(WAVE_E_UNSUPPORTED, "head_dim must be 128; got %d", d->head_dim);
   if (d->io_type != WAVE_BF16 && d->io_type != WAVE_F16)
     return fail(WAVE_E_UNSUPPORTED, "io_type must be bf16 or f16; got %d", d->io_type);
   if (d->causal && d->seq_q != d->seq_k)
@@ -629,9 +660,16 @@ int wave_cuda_check_device_status(int *out4) {
   cudaError_t err = cudaDeviceSynchronize();
   if (err != cudaSuccess)
     return cuda_fail(err, "cudaDeviceSynchronize");
-  int g[4] = {0, 0, 0, 0}, f[4] = {0, 0, 0, 0};
+  int g[4] = {0, 0, 0, 0}, f[4] = {0, 0, 0, 0}, g2[4] = {0, 0, 0, 0};
   if ((err = wave::gemm_read_status(g, true)) != cudaSuccess)
     return cuda_fail(err, "read GEMM status");
+  if ((err = wave::gemm_pair_read_status(g2, true)) != cudaSuccess)
+    return cuda_fail(err, "read GEMM (CTA pair) status");
+  if (!g[0] && g2[0]) {
+    for (int i = 0; i < 4; ++i)
+      g[i] = g2[i];
+    g[2] += 10; // roles 10.. : CTA-pair kernel
+  }
   if ((err = wave::fa_read_status(f, true)) != cudaSuccess)
     return cuda_fail(err, "read attention status");
   const int *bad = g[0] ? g : (f[0] ? f : nullptr);

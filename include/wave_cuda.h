@@ -62,7 +62,10 @@ void *_mlir_ciface_wave_memref_to_ptr_global_f64(void *memref1d);
  * (wave-matmul-calibrate-runner.cpp:36-64).  The tiling knobs never change
  * results; they choose the CTA tile:
  *   16*bm*wave_m_tiles x 16*bn*wave_n_tiles, snapped to a legal UMMA shape
- *   (rows 128; columns the next of 16/32/64/128/256).                        */
+ *   (rows 128; columns the next of 16/32/64/128/256).
+ * Requested tiles of at least 256 x 256 on a problem with enough of them run on
+ * CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles); the environment variable
+ * WAVE_CUDA_GEMM_KERNEL=pair|single overrides that size heuristic.            */
 typedef struct wave_gemm_desc {
   int M, N, K;                 /* positive multiples of 16 (wave_matmul.py:533-536)      */
   int bm, bn;                  /* waves per workgroup along M / N; bn a power of two      */
@@ -126,7 +129,7 @@ int wave_cuda_gemm_plan(const wave_gemm_desc *desc, int *tile_m, int *tile_n, in
 typedef struct wave_fa_desc {
   int batch, heads;
   int seq_q, seq_k; /* multiples of 16 */
-  int head_dim;     /* 128 (the reference kernel's only value) or 64 */
+  int head_dim;     /* 128, the reference kernel's only value (wave_flash_attention.py:43-60) */
   float scale;      /* 0 = 1/sqrt(head_dim) */
   int causal;
   int io_type;      /* WAVE_BF16 | WAVE_F16 */

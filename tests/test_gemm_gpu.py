@@ -18,6 +18,15 @@ GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
 
 
 def run_gemm(torch, wc, a_bits, b_bits, in_name, out_name, layout="row-major", streamk=1, ldc=0, **knobs):
+    # small shapes must still exercise the CTA-pair kernel when their knobs ask for 256 x 256 tiles
+    os.environ["WAVE_CUDA_GEMM_KERNEL"] = "pair"
+    try:
+        return _run_gemm(torch, wc, a_bits, b_bits, in_name, out_name, layout, streamk, ldc, **knobs)
+    finally:
+        del os.environ["WAVE_CUDA_GEMM_KERNEL"]
+
+
+def _run_gemm(torch, wc, a_bits, b_bits, in_name, out_name, layout="row-major", streamk=1, ldc=0, **knobs):
     M, K = a_bits.shape
     N = b_bits.shape[0]
     desc = wc.gemm_desc(M, N, K, in_type=wc.TYPE_BY_NAME[in_name], out_type=wc.TYPE_BY_NAME[out_name],
@@ -83,6 +92,12 @@ def test_config1_matches_reference_golden(cuda, wc, oracle):
     (16, 1024, 512, "bf16", "f32", "row-major", dict(bn=1)),
     (16, 1024, 512, "bf16", "bf16", "column-major", dict(bn=1)),
     (64, 4096, 256, "f16", "f16", "row-major", dict(bm=4, bn=1)),
+    # CTA-pair kernel (256 x 256 tiles): requested tile >= 256 in both directions
+    (256, 256, 64, "f16", "f32", "row-major", dict(bm=4, bn=4, wave_m_tiles=4, wave_n_tiles=4)),
+    (512, 768, 256, "bf16", "bf16", "row-major", dict(bm=4, bn=4, wave_m_tiles=4, wave_n_tiles=4)),
+    (1024, 1024, 1040, "bf16", "f32", "column-major", dict(bm=4, bn=4, wave_m_tiles=4, wave_n_tiles=4)),
+    (400, 272, 208, "f16", "f16", "row-major", dict(bm=1, bn=1, wave_m_tiles=25, wave_n_tiles=17)),
+    (2304, 2048, 512, "f16", "f32", "row-major", dict(bm=4, bn=4, wave_m_tiles=4, wave_n_tiles=4, cta_group_m=3)),
 ])
 def test_lcg_inputs_bit_exact(cuda, wc, oracle, M, N, K, in_name, out_name, layout, knobs):
     """Reference LCG inputs are multiples of 0.25 in [-2, 2]: all partial sums
@@ -138,6 +153,26 @@ def test_streamk_matches_oracle_and_resets_counters(cuda, wc, oracle, M, N, K, w
     assert np.array_equal(r1, r2)
     ok, worst, nbad = runner_tolerance_ok(r1, expected(oracle, a, b, "bf16", "f32"))
     assert ok, f"{nbad} elements out of tolerance, worst {worst}"
+
+
+def test_pair_kernel_is_selected_for_large_tiles(cuda, wc):
+    plan = wc.gemm_plan(wc.gemm_desc(8192, 8192, 8192, bm=4, bn=4, wave_m_tiles=4, wave_n_tiles=4, in_type=wc.BF16))
+    assert (plan["tile_m"], plan["tile_n"]) == (256, 256) and plan["grid"] % 2 == 0
+    plan = wc.gemm_plan(wc.gemm_desc(8192, 8192, 8192, bm=4, bn=4, wave_m_tiles=2, wave_n_tiles=4, in_type=wc.BF16))
+    assert (plan["tile_m"], plan["tile_n"]) == (128, 256)
+    # too few 256 x 256 tiles to fill the CTA pairs several times over: one-CTA kernel
+    plan = wc.gemm_plan(wc.gemm_desc(4096, 4096, 4096, bm=4, bn=4, wave_m_tiles=4, wave_n_tiles=4))
+    assert (plan["tile_m"], plan["tile_n"]) == (128, 256)
+
+
+def test_pair_kernel_random_inputs(cuda, wc, oracle):
+    t = oracle.BF16
+    M, N, K = 1024, 768, 4096
+    a = oracle.baseline_inputs((M, K), "normal", 21, 0, t, scale=K ** -0.5)
+    b = oracle.baseline_inputs((N, K), "normal", 21, 1, t, scale=1.0)
+    got, _ = run_gemm(cuda, wc, a, b, "bf16", "bf16", bm=4, bn=4, wave_m_tiles=4, wave_n_tiles=4)
+    ok, worst, nbad = runner_tolerance_ok(got, expected(oracle, a, b, "bf16", "bf16"), "bf16")
+    assert ok, f"{nbad} elements out of tolerance, worst abs diff {worst}"
 
 
 def test_ldc_writes_column_shard_in_place(cuda, wc, oracle):
