@@ -61,6 +61,9 @@ EncodeTiledFn encode_fn() {
 
 namespace wave {
 
+// Lets the library's other translation units record a failure message.
+void set_last_error(const char *message) { g_last_error = message ? message : ""; }
+
 // rank-2 or rank-3 map over 16-bit elements, 128-byte swizzle, zero fill
 // outside the tensor.  dims/strides innermost first; strides in bytes for
 // dims 1.. (dim 0 is contiguous).

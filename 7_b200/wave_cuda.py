@@ -45,7 +45,7 @@ EXPORTS = [
     "_mlir_ciface_wave_memref_to_ptr_global_bf16", "_mlir_ciface_wave_memref_to_ptr_global_i64",
     "_mlir_ciface_wave_memref_to_ptr_global_f64",
     "wave_cuda_gemm_desc_init", "wave_cuda_gemm_validate", "wave_cuda_gemm_workspace_bytes", "wave_cuda_gemm",
-    "wave_cuda_gemm_host", "wave_cuda_gemm_plan", "wave_cuda_fa_validate", "wave_cuda_flash_attention_fwd",
+    "wave_cuda_gemm_host", "wave_cuda_gemm_plan", "wave_cuda_gemm_streamk_static", "wave_cuda_fa_validate", "wave_cuda_flash_attention_fwd",
     "wave_cuda_flash_attention_fwd_host", "wave_cuda_module_get_function", "wave_cuda_launch",
     "wave_cuda_function_release", "wave_cuda_check_device_status",
 ]
@@ -74,6 +74,7 @@ def lib() -> C.CDLL:
     L.wave_cuda_gemm_workspace_bytes.argtypes = [C.POINTER(GemmDesc), C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]
     L.wave_cuda_gemm.argtypes = [C.POINTER(GemmDesc), vp, vp, vp, vp, vp]
     L.wave_cuda_gemm_host.argtypes = [C.POINTER(GemmDesc), vp, vp, vp, vp]
+    L.wave_cuda_gemm_streamk_static.argtypes = [C.POINTER(GemmDesc), vp, vp, vp, vp]
     L.wave_cuda_gemm_plan.argtypes = [C.POINTER(GemmDesc), ip, ip, ip, ip, ip]
     L.wave_cuda_fa_validate.argtypes = [C.POINTER(FaDesc)]
     L.wave_cuda_flash_attention_fwd.argtypes = [C.POINTER(FaDesc), vp, vp, vp, vp, vp, vp]
@@ -118,6 +119,15 @@ def gemm_plan(desc: GemmDesc) -> dict:
 
 def gemm(desc: GemmDesc, a_ptr: int, b_ptr: int, c_ptr: int, workspace_ptr: int = 0, stream: int = 0) -> None:
     check(lib().wave_cuda_gemm(C.byref(desc), a_ptr, b_ptr, c_ptr, workspace_ptr or None, stream or None))
+
+
+STATIC_WORKSPACE_BYTES = 8 * 1024 * 1024
+
+
+def gemm_streamk_static(desc: GemmDesc, a_ptr: int, b_ptr: int, c_ptr: int, stream: int = 0) -> None:
+    """Stream-K GEMM on the library's built-in workspace, for callers that
+    cannot pass or allocate one; see include/wave_cuda.h for its limits."""
+    check(lib().wave_cuda_gemm_streamk_static(C.byref(desc), a_ptr, b_ptr, c_ptr, stream or None))
 
 
 def gemm_host(desc: GemmDesc, a_ptr: int, b_ptr: int, c_ptr: int, stream: int = 0) -> None:

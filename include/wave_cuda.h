@@ -111,6 +111,22 @@ int wave_cuda_gemm(const wave_gemm_desc *desc, const void *A, const void *B, voi
 int wave_cuda_gemm_host(const wave_gemm_desc *desc, const void *A_host, const void *B_host, void *C_host,
                         void *stream);
 
+/* No counterpart in the reference.  Stream-K GEMM for callers that cannot
+ * supply (or allocate) the workspace wave_cuda_gemm asks for: hosts written to
+ * the reference's plain {A, B, C, trip} argument list, which has no workspace
+ * slot; processes whose device memory is wholly owned by another allocator;
+ * paths on which a device allocation must not happen.  The partial tiles and
+ * counters live in one fixed WAVE_CUDA_STATIC_WORKSPACE_BYTES area inside the
+ * library's device image (held by every GPU that loads the library until the
+ * process exits); nothing is allocated or freed.  A descriptor that needs more
+ * than the area holds is refused with WAVE_E_INVALID.  The first call on a
+ * device looks the area's address up and should be made before any stream
+ * capture.  Every call shares the area: calls whose kernels overlap on the GPU
+ * race and must be serialised by the caller.  Same arguments and results as
+ * wave_cuda_gemm with a caller workspace. */
+#define WAVE_CUDA_STATIC_WORKSPACE_BYTES (8 * 1024 * 1024)
+int wave_cuda_gemm_streamk_static(const wave_gemm_desc *desc, const void *A, const void *B, void *C, void *stream);
+
 /* Launch geometry the backend chose (tile rows, tile columns, grid size,
  * Stream-K workers or 0, operands swapped or not) -- the counterpart of the
  * runner's `grid:` / `shape:` lines (runner.cpp:1881-1908). */
