@@ -26,22 +26,59 @@
 #include "fa_sm100.h"
 #include "sm100_ptx.cuh"
 
+#include <cstdlib>
+#include <type_traits>
+
 namespace wave {
 
+void set_last_error(const char *message); // wave_cuda_backend.cu
+
 __device__ int g_fa_status[4]; // [0] code, [1] linear block, [2] role, [3] detail
+
+// Optional stage stamps (clock64) for one CTA, compiled in with -DWAVE_FA_TRACE:
+// [role][block][stamp].  Role 0 = UMMA thread, 1 = softmax tile 0 (row 0),
+// 2 = softmax tile 1 (row 0).
+#ifdef WAVE_FA_TRACE
+__device__ long long g_fa_trace[3][64][8];
+#define FA_STAMP(role, blk, idx)                                                                   \
+  do {                                                                                             \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && (blk) < 64)                                          \
+      g_fa_trace[role][blk][idx] = clock64();                                                      \
+  } while (0)
+#else
+#define FA_STAMP(role, blk, idx)                                                                   \
+  do {                                                                                             \
+  } while (0)
+#endif
 
 namespace {
 
 constexpr int kBlockM = 128; // rows per Q tile = UMMA M = TMEM lanes
 constexpr int kBlockN = 128; // keys per K/V block
 constexpr int kD = 128;      // head dimension
-constexpr int kThreads = 384;
+constexpr int kThreads = 384;            // warpgroup 0: loader + UMMA warps; warpgroups 1, 2: softmax
 constexpr int kSubTile = 128 * 64 * 2;  // [128 rows][64 elements], 128-byte swizzled rows
 constexpr int kTile = 2 * kSubTile;     // 128 x 128 16-bit elements
 constexpr int kSmemTiles = 2 * kTile /*Q*/ + 2 * kTile /*K ring*/ + 2 * kTile /*V ring*/;
 constexpr int kSmemBytes = kSmemTiles + 1024 + 256;
 constexpr int kTmemCols = 512;
-constexpr float kRescaleThreshold = 8.0f; // log2 units (wave_flash_attention.py:563-569)
+// Of every 8 column pairs, how many evaluate 2^x with exp2_poly2 instead of the
+// special-function unit.  Measured on B200 (causal, B=16 H=32 S=4096): 0 -> 1014,
+// 1 -> 1011, 2 -> 966, 3 -> 958, 4 -> 975 TFLOP/s: the kernel is paced by the
+// S/P hand-offs between the softmax warps and the tensor core, not by the
+// special-function unit, so the default keeps every exponential on it.
+constexpr int kDefaultPoly = 0;
+constexpr float kRescaleThreshold = 8.0f;
+// setmaxnreg budget.  The kernel starts with kLaunchRegs per thread (12 warps,
+// one CTA per SM); warpgroup 0 shrinks to kIssueRegs and the two softmax
+// warpgroups grow to kSoftmaxRegs.  The grow request blocks until the registers
+// exist, so what warpgroup 0 releases must cover what the other two ask for.
+constexpr int kLaunchRegs = 168;
+constexpr int kIssueRegs = 72;
+constexpr int kSoftmaxRegs = 216;
+static_assert((kLaunchRegs - kIssueRegs) * 128 >= (kSoftmaxRegs - kLaunchRegs) * 256,
+              "setmaxnreg.inc would wait forever: warpgroup 0 does not release enough registers");
+static_assert(kIssueRegs % 8 == 0 && kSoftmaxRegs % 8 == 0, "setmaxnreg takes multiples of 8"); // log2 units (wave_flash_attention.py:563-569)
 
 struct FaShared {
   uint64_t q_full;
@@ -65,6 +102,40 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// 2^x for a pair of values on the FMA pipe instead of the special-function
+// unit: round-to-nearest split x = n + f with |f| <= 0.5 (adding 1.5*2^23 leaves
+// n in the low mantissa bits), a degree-3 minimax polynomial for 2^f (maximum
+// relative error 7.6e-5, far below the 2^-9 of the 16-bit rounding that
+// follows), then n is added to the exponent field.  Arguments below -125 are
+// clamped (the result is then ~2^-125, which rounds away in every use here).
+__device__ __forceinline__ float2 exp2_poly2(float2 x) {
+  x.x = fmaxf(x.x, -125.0f);
+  x.y = fmaxf(x.y, -125.0f);
+  const float2 t = __fadd2_rn(x, make_float2(12582912.0f, 12582912.0f));
+  const float2 n = __fadd2_rn(t, make_float2(-12582912.0f, -12582912.0f));
+  const float2 f = __ffma2_rn(n, make_float2(-1.0f, -1.0f), x);
+  float2 q = __ffma2_rn(f, make_float2(0.05520550534129143f, 0.05520550534129143f),
+                        make_float2(0.24261397123336792f, 0.24261397123336792f));
+  q = __ffma2_rn(q, f, make_float2(0.6932547688484192f, 0.6932547688484192f));
+  q = __ffma2_rn(q, f, make_float2(0.9999276995658875f, 0.9999276995658875f));
+  float2 r;
+  r.x = __int_as_float(__float_as_int(q.x) + (__float_as_int(t.x) << 23));
+  r.y = __int_as_float(__float_as_int(q.y) + (__float_as_int(t.y) << 23));
+  return r;
+}
+
+// Which of the 64 column pairs of a row take the polynomial path: kPoly of
+// every 8, spread evenly so that FMA-pipe and special-function work interleave.
+template <int kPoly> __device__ __forceinline__ constexpr bool pair_uses_poly(int i) {
+  return ((i + 1) * kPoly) / 8 > (i * kPoly) / 8;
+}
+
 __device__ __forceinline__ uint32_t pack2(float lo, float hi, bool bf16) {
   if (bf16) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -74,6 +145,7 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi, bool bf16) {
   return *reinterpret_cast<uint32_t *>(&v);
 }
 
+template <int kPoly, bool kBf16>
 __global__ void __launch_bounds__(kThreads, 1)
 fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
               const __grid_constant__ CUtensorMap tm_v, const FaParams p) {
@@ -130,6 +202,11 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   tc_fence_after_sync();
   const uint32_t tmem_base = sh->tmem_base;
 
+  // Register budget (setmaxnreg must be the first thing each warpgroup does on
+  // its own path): warpgroup 0 (loader, UMMA issuer, two idle warps) gives
+  // registers up, the softmax warpgroups hold a 128-column score row per thread.
+  if (warp < 4)
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kIssueRegs));
   if (warp == 0) {
     // ---------------------------------------------------------------- loads
     if (lane == 0) {
@@ -235,11 +312,13 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             }
             have_v = true;
           }
+          FA_STAMP(0, j, t * 4 + 0);
           if (!mbar_wait(&sh->p_full[t], j & 1, abort_flag)) {
             fa_report(kStatusWaitTimeout, 1, 40 + t);
             ok = false;
             break;
           }
+          FA_STAMP(0, j, t * 4 + 1);
           tc_fence_after_sync();
           issue_pv(t, s, j > 0);
           if (j + 1 < n_blocks[t]) {
@@ -253,6 +332,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
               have_k_next = true;
             }
             issue_s(t, s_next);
+            FA_STAMP(0, j, t * 4 + 2);
           } else {
             umma_commit(&sh->o_full[t]);
           }
@@ -266,6 +346,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     }
   } else if (warp >= 4) {
     // --------------------------------------------------------------- softmax
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
     const int t = (warp - 4) >> 2;
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
@@ -275,12 +356,14 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t s_addr = tmem_base + lane_base + static_cast<uint32_t>(t * kBlockN);
     const uint32_t o_addr = tmem_base + lane_base + static_cast<uint32_t>(2 * kBlockN + t * kD);
-    const bool bf16 = p.is_bf16 != 0;
+    constexpr bool bf16 = kBf16;
     float m_used = -INFINITY; // running maximum the exponentials are taken against (raw score units)
     float l = 0.0f;           // running sum of unrounded probabilities
     bool ok = true;
 
     for (int j = 0; j < nb; ++j) {
+      if (row == 0)
+        FA_STAMP(1 + t, j, 0);
       if (!mbar_wait(&sh->s_full[t], j & 1, abort_flag)) {
         if (lane == 0)
           fa_report(kStatusWaitTimeout, 2 + t, 60);
@@ -288,12 +371,16 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         break;
       }
       tc_fence_after_sync();
+      if (row == 0)
+        FA_STAMP(1 + t, j, 1);
       uint32_t s[128];
       tmem_ld_32x32b_x32(s_addr + 0, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
       tmem_ld_32x32b_x32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
       tmem_ld_32x32b_x32(s_addr + 64, *reinterpret_cast<uint32_t(*)[32]>(&s[64]));
       tmem_ld_32x32b_x32(s_addr + 96, *reinterpret_cast<uint32_t(*)[32]>(&s[96]));
       tmem_ld_wait();
+      if (row == 0)
+        FA_STAMP(1 + t, j, 2);
 
       const int key0 = j * kBlockN;
       const bool need_mask = (p.causal && key0 + kBlockN - 1 > q_row - row) || (key0 + kBlockN > p.seq_k);
@@ -304,14 +391,13 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           if (key0 + i > limit)
             s[i] = 0xFF800000u; // -inf
       }
-      float mx0 = __uint_as_float(s[0]), mx1 = __uint_as_float(s[1]);
-      float mx2 = __uint_as_float(s[2]), mx3 = __uint_as_float(s[3]);
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-      for (int i = 4; i < 128; i += 4) {
-        mx0 = fmaxf(mx0, __uint_as_float(s[i]));
-        mx1 = fmaxf(mx1, __uint_as_float(s[i + 1]));
-        mx2 = fmaxf(mx2, __uint_as_float(s[i + 2]));
-        mx3 = fmaxf(mx3, __uint_as_float(s[i + 3]));
+      for (int i = 0; i < 128; i += 8) {
+        mx0 = max3(mx0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+        mx1 = max3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+        mx2 = max3(mx2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
+        mx3 = max3(mx3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
       }
       const float m_new = fmaxf(m_used, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
       // Lazy rescale: only when some row of this warp moved its maximum by more
@@ -334,28 +420,37 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         }
         m_used = m_new;
       }
+      if (row == 0)
+        FA_STAMP(1 + t, j, 3);
       const float neg_mc = -m_used * c;
-      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+      const float2 c2 = make_float2(c, c), nm2 = make_float2(neg_mc, neg_mc);
+      float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
       uint32_t pk[64];
 #pragma unroll
-      for (int i = 0; i < 128; i += 4) {
-        const float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), c, neg_mc));
-        const float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), c, neg_mc));
-        const float p2 = fast_exp2(fmaf(__uint_as_float(s[i + 2]), c, neg_mc));
-        const float p3 = fast_exp2(fmaf(__uint_as_float(s[i + 3]), c, neg_mc));
-        l0 += p0;
-        l1 += p1;
-        l2 += p2;
-        l3 += p3;
-        pk[i / 2] = pack2(p0, p1, bf16);
-        pk[i / 2 + 1] = pack2(p2, p3, bf16);
+      for (int i = 0; i < 64; ++i) {
+        const float2 x =
+            __ffma2_rn(make_float2(__uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1])), c2, nm2);
+        float2 pr;
+        if (pair_uses_poly<kPoly>(i))
+          pr = exp2_poly2(x);
+        else
+          pr = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+        if (i & 1)
+          lb = __fadd2_rn(lb, pr);
+        else
+          la = __fadd2_rn(la, pr);
+        pk[i] = pack2(pr.x, pr.y, bf16);
       }
-      l += (l0 + l1) + (l2 + l3);
+      l += (la.x + la.y) + (lb.x + lb.y);
+      if (row == 0)
+        FA_STAMP(1 + t, j, 4);
       tmem_st_32x32b_x32(s_addr + 0, *reinterpret_cast<uint32_t(*)[32]>(&pk[0]));
       tmem_st_32x32b_x32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&pk[32]));
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(&sh->p_full[t]);
+      if (row == 0)
+        FA_STAMP(1 + t, j, 5);
     }
 
     if (ok && nb > 0) {
@@ -426,14 +521,68 @@ int launch_flash_attention(const FaParams &p, const void *Q, const void *K, cons
     if (rc != WAVE_OK)
       return rc;
   }
-  cudaError_t err = cudaFuncSetAttribute(fa_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-  if (err != cudaSuccess)
-    return WAVE_E_CUDA;
+  // Share of the exponentials evaluated on the FMA pipe, in eighths (a tuning
+  // knob for measurements; the default is the measured best).
+  int poly = kDefaultPoly;
+  if (const char *env = getenv("WAVE_CUDA_FA_POLY"))
+    poly = atoi(env);
   dim3 grid(static_cast<unsigned>((p.seq_q + 2 * kBlockM - 1) / (2 * kBlockM)), static_cast<unsigned>(p.batch_heads));
-  fa_fwd_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tq, tk, tv, p);
-  err = cudaGetLastError();
-  return err == cudaSuccess ? WAVE_OK : WAVE_E_CUDA;
+  cudaError_t err = cudaSuccess;
+  bool unsafe_budget = false;
+  auto launch = [&](auto kernel) {
+    // The setmaxnreg arithmetic in the kernel assumes the register count the
+    // compiler actually gave it; refuse to launch rather than risk a grow
+    // request that can never be satisfied.
+    cudaFuncAttributes attr;
+    err = cudaFuncGetAttributes(&attr, kernel);
+    if (err != cudaSuccess)
+      return;
+    if ((attr.numRegs - kIssueRegs) * 128 < (kSoftmaxRegs - attr.numRegs) * 256 || attr.numRegs * kThreads > 65536) {
+      unsafe_budget = true;
+      return;
+    }
+    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (err != cudaSuccess)
+      return;
+    kernel<<<grid, kThreads, kSmemBytes, stream>>>(tq, tk, tv, p);
+    err = cudaGetLastError();
+  };
+  auto dispatch = [&](auto bf16_tag) {
+    constexpr bool B = decltype(bf16_tag)::value;
+    switch (poly) {
+    case 0: launch(fa_fwd_kernel<0, B>); break;
+    case 1: launch(fa_fwd_kernel<1, B>); break;
+    case 2: launch(fa_fwd_kernel<2, B>); break;
+    case 3: launch(fa_fwd_kernel<3, B>); break;
+    case 4: launch(fa_fwd_kernel<4, B>); break;
+    default: launch(fa_fwd_kernel<kDefaultPoly, B>); break;
+    }
+  };
+  if (p.is_bf16)
+    dispatch(std::true_type{});
+  else
+    dispatch(std::false_type{});
+  if (unsafe_budget) {
+    set_last_error("attention kernel was built with a register count its setmaxnreg budget does not cover");
+    return WAVE_E_CUDA;
+  }
+  if (err != cudaSuccess) {
+    set_last_error(cudaGetErrorString(err));
+    return WAVE_E_CUDA;
+  }
+  return WAVE_OK;
 }
+
+#ifdef WAVE_FA_TRACE
+extern "C" int wave_cuda_fa_trace_read(long long *out, int clear) {
+  cudaError_t err = cudaMemcpyFromSymbol(out, g_fa_trace, sizeof(long long) * 3 * 64 * 8);
+  if (err == cudaSuccess && clear) {
+    static long long zero[3 * 64 * 8];
+    err = cudaMemcpyToSymbol(g_fa_trace, zero, sizeof(zero));
+  }
+  return err == cudaSuccess ? 0 : -3;
+}
+#endif
 
 cudaError_t fa_read_status(int out[4], bool clear) {
   cudaError_t err = cudaMemcpyFromSymbol(out, g_fa_status, sizeof(int) * 4);
