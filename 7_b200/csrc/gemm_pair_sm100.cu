@@ -32,7 +32,10 @@ constexpr int kPairM = 256;    // UMMA M across the pair
 constexpr int kPairN = 256;    // UMMA N
 constexpr int kBRows = 128;    // B rows held by one CTA
 constexpr int kBK = 64;
-constexpr int kStages = 6;
+#ifndef WAVE_PAIR_STAGES
+#define WAVE_PAIR_STAGES 6
+#endif
+constexpr int kStages = WAVE_PAIR_STAGES;
 constexpr int kABytes = kRows * kBK * 2;
 constexpr int kBBytes = kBRows * kBK * 2;
 constexpr int kStageBytes = kABytes + kBBytes;
