@@ -37,9 +37,11 @@ sys.path.insert(0, ROOT)
 
 METRIC = "TFLOP/s + % tensor roofline: GEMM 8192^3 bf16, FA-fwd S=4096 d=128 @1/2/4/8 B200"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
-# DRAM bytes per launch from an ncu capture of the same kernel (see the file
-# named in profiles/); None until a capture for that workload has been read.
-NCU_TRAFFIC_BYTES = {"gemm": None, "fa": None, "skinny": None}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from one ncu capture of
+# the same kernel (summaries under profiles/): gemm and skinny at full size; fa
+# captured at B=2 (250.58 MB) and scaled by the 8x heads of the B=16 workload,
+# since every head moves the same bytes.
+NCU_TRAFFIC_BYTES = {"gemm": 1172.98e6, "fa": 8 * 250.58e6, "skinny": 477.11e6}
 
 WORKLOADS = {
     "gemm": dict(name="gemm_bf16_8192x8192x8192_f32acc_bf16out", M=8192, N=8192, K=8192),

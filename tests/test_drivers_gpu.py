@@ -1,0 +1,77 @@
+"""The command-line checkers in tests/drivers, run the way the reference's
+integration tests run its tools: a child process whose stdout must contain
+`CPU comparison passed` / `output_check: passed`
+(test/Integration/wave_mfma_per_wave_tiles.mlir:3-11,
+wave_flash_attention_gfx950_runtime.mlir:3-22,
+wave_gfx950_streamk_f16_runtime.mlir:3-88)."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+DRIVERS = os.path.join(os.path.dirname(os.path.abspath(__file__)), "drivers")
+
+
+def run(tool, *args, expect=0):
+    proc = subprocess.run([sys.executable, os.path.join(DRIVERS, tool), *map(str, args)], capture_output=True,
+                          text=True, timeout=600)
+    assert proc.returncode == expect, proc.stdout + proc.stderr
+    return proc.stdout, proc.stderr
+
+
+def test_example_driver_compare_cpu_reference_case(cuda):
+    # README / wave_mfma_per_wave_tiles.mlir: 32x32x64, bm=bn=2, wave-k-tiles=2, seed 7
+    out, _ = run("wmma_matmul_tiled.py", "--m=32", "--n=32", "--k=64", "--bm=2", "--bn=2", "--wave-k-tiles=2",
+                 "--compare-cpu", "--seed=7", "--matrix-intrinsic=mfma", "--chip=gfx942")
+    assert "CPU comparison passed: elements=1024" in out
+
+
+@pytest.mark.parametrize("extra", [
+    ["--input-type=bf16", "--output-type=f16"],
+    ["--output-layout=column-major", "--wave-m-tiles=2", "--wave-n-tiles=2"],
+])
+def test_example_driver_variants(cuda, extra):
+    out, _ = run("wmma_matmul_tiled.py", "--m=64", "--n=128", "--k=96", "--compare-cpu", "--seed=3", *extra)
+    assert "CPU comparison passed" in out
+
+
+def test_example_driver_prints_data_and_rejects_bad_shape(cuda):
+    out, _ = run("wmma_matmul_tiled.py", "--m=16", "--n=16", "--k=16", "--run")
+    assert out.startswith("data = ") and out.count(",") == 255
+    _, err = run("wmma_matmul_tiled.py", "--m=24", "--n=16", "--k=16", "--run", expect=2)
+    assert "M must be a positive multiple of 16; got 24" in err
+
+
+def test_gemm_calibrate_runner_contract(cuda):
+    out, _ = run("wave_matmul_calibrate.py", "--m=256", "--n=512", "--k=1024", "--bm=4", "--bn=4", "--wave-m-tiles=2",
+                 "--wave-n-tiles=4", "--rand-int", "--iters=5", "--warmup=2", "--c-type=f16")
+    for key in ("kernel: wmma_f16_matmul_tiled", "shape: m=256 n=512 k=1024", "iters: 5", "per_launch_us: ",
+                "total_ms: ", "tflops: ", "output_check: passed mode=strict layout=row-major elements=131072"):
+        assert key in out, out
+    assert "input_mode=rand_int" in out
+
+
+def test_gemm_calibrate_runner_streamk(cuda):
+    out, _ = run("wave_matmul_calibrate.py", "--m=512", "--n=512", "--k=2048", "--bm=4", "--bn=4", "--wave-m-tiles=2",
+                 "--wave-n-tiles=4", "--hpl", "--input-type=bf16", "--kernel-abi=streamk", "--streamk-workers=5",
+                 "--iters=50", "--warmup=2")
+    assert "output_check: passed" in out and "streamk_counter_check: passed" in out
+    assert "kernel: gfx950_f16_streamk_gemm" in out
+
+
+def test_gemm_calibrate_runner_bad_arguments(cuda):
+    _, err = run("wave_matmul_calibrate.py", "--m=64", "--n=64", "--k=64", "--bn=3", expect=2)
+    assert "BN must be a positive power of two" in err
+
+
+def test_attention_calibrate_runner(cuda):
+    out, _ = run("wave_fa_gfx950.py", "--batch=1", "--heads=2", "--sequence=512", "--iters=3", "--warmup=1", "--check")
+    assert "shape: B=1 H=2 N=512 D=128" in out and "output_check: passed max_abs_diff=" in out
+    assert "median_tflops: " in out
+    out, _ = run("wave_fa_gfx950.py", "--batch=2", "--heads=3", "--sequence=1024", "--iters=3", "--warmup=1", "--check",
+                 "--causal", "--seed=5")
+    assert "output_check: passed" in out
+    _, err = run("wave_fa_gfx950.py", "--sequence=300", expect=2)
+    assert "multiple of 256" in err
