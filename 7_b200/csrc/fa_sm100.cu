@@ -461,22 +461,39 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         tc_fence_after_sync();
         const float inv = 1.0f / l;
         const bool live = q_row < p.seq_q;
+        // Head dimensions below 128 ran zero-padded (TMA fills the missing
+        // columns of Q, K and V with zeros); only the first head_dim columns of
+        // O exist in memory.  Output is the I/O type, or f32 on request.
+        const int esize = p.out_f32 ? 4 : 2;
         uint8_t *out_row = static_cast<uint8_t *>(p.O) +
-                           (static_cast<size_t>(bh) * p.seq_q + static_cast<size_t>(live ? q_row : 0)) * kD * 2;
+                           (static_cast<size_t>(bh) * p.seq_q + static_cast<size_t>(live ? q_row : 0)) *
+                               static_cast<size_t>(p.head_dim) * esize;
 #pragma unroll 1
-        for (int cc = 0; cc < kD; cc += 32) {
+        for (int cc = 0; cc < p.head_dim; cc += 32) {
           uint32_t o[32];
           tmem_ld_32x32b_x32(o_addr + cc, o);
           tmem_ld_wait();
-          uint32_t w[16];
+          if (p.out_f32) {
+            if (live) {
+              float4 *dst = reinterpret_cast<float4 *>(out_row + cc * 4);
 #pragma unroll
-          for (int i = 0; i < 16; ++i)
-            w[i] = pack2(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv, bf16);
-          if (live) {
-            uint4 *dst = reinterpret_cast<uint4 *>(out_row + cc * 2);
+              for (int v = 0; v < 8; ++v)
+                if (cc + 4 * v < p.head_dim) // head_dim is a multiple of 16
+                  dst[v] = make_float4(__uint_as_float(o[4 * v]) * inv, __uint_as_float(o[4 * v + 1]) * inv,
+                                       __uint_as_float(o[4 * v + 2]) * inv, __uint_as_float(o[4 * v + 3]) * inv);
+            }
+          } else {
+            uint32_t w[16];
 #pragma unroll
-            for (int v = 0; v < 4; ++v)
-              dst[v] = make_uint4(w[4 * v], w[4 * v + 1], w[4 * v + 2], w[4 * v + 3]);
+            for (int i = 0; i < 16; ++i)
+              w[i] = pack2(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv, bf16);
+            if (live) {
+              uint4 *dst = reinterpret_cast<uint4 *>(out_row + cc * 2);
+#pragma unroll
+              for (int v = 0; v < 4; ++v)
+                if (cc + 8 * v < p.head_dim)
+                  dst[v] = make_uint4(w[4 * v], w[4 * v + 1], w[4 * v + 2], w[4 * v + 3]);
+            }
           }
         }
         if (p.lse && live)
@@ -499,20 +516,21 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 int launch_flash_attention(const FaParams &p, const void *Q, const void *K, const void *V, int sm_count,
                            cudaStream_t stream) {
   (void)sm_count;
-  if (p.head_dim != kD)
+  if (p.head_dim < 16 || p.head_dim > kD || p.head_dim % 16)
     return WAVE_E_UNSUPPORTED;
   CUtensorMap tq, tk, tv;
   const uint32_t box[3] = {64, 128, 1};
-  const uint64_t row_bytes = static_cast<uint64_t>(kD) * 2;
+  const uint64_t hd = static_cast<uint64_t>(p.head_dim);
+  const uint64_t row_bytes = hd * 2;
   {
-    const uint64_t dims[3] = {kD, static_cast<uint64_t>(p.seq_q), static_cast<uint64_t>(p.batch_heads)};
+    const uint64_t dims[3] = {hd, static_cast<uint64_t>(p.seq_q), static_cast<uint64_t>(p.batch_heads)};
     const uint64_t strides[2] = {row_bytes, row_bytes * static_cast<uint64_t>(p.seq_q)};
     int rc = make_tensor_map_16bit(&tq, p.is_bf16, Q, 3, dims, strides, box);
     if (rc != WAVE_OK)
       return rc;
   }
   {
-    const uint64_t dims[3] = {kD, static_cast<uint64_t>(p.seq_k), static_cast<uint64_t>(p.batch_heads)};
+    const uint64_t dims[3] = {hd, static_cast<uint64_t>(p.seq_k), static_cast<uint64_t>(p.batch_heads)};
     const uint64_t strides[2] = {row_bytes, row_bytes * static_cast<uint64_t>(p.seq_k)};
     int rc = make_tensor_map_16bit(&tk, p.is_bf16, K, 3, dims, strides, box);
     if (rc != WAVE_OK)

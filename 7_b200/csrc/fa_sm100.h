@@ -10,9 +10,10 @@ namespace wave {
 struct FaParams {
   int batch_heads, seq_q, seq_k, head_dim;
   int causal, is_bf16;
+  int out_f32;       // O is f32 instead of the 16-bit I/O type
   float scale;       // softmax scale applied to q.k
   float scale_log2e; // scale * log2(e): scores enter exp2 as fma(s, scale_log2e, -max)
-  void *O;           // [batch_heads][seq_q][head_dim], same 16-bit type as the inputs
+  void *O;           // [batch_heads][seq_q][head_dim], the I/O type or f32
   float *lse;        // optional [batch_heads][seq_q] natural-log sum-exp, or null
 };
 

@@ -522,8 +522,8 @@ int wave_cuda_fa_validate(const wave_fa_desc *d) {
   if (d->seq_q <= 0 || d->seq_k <= 0 || d->seq_q % 16 != 0 || d->seq_k % 16 != 0)
     return fail(WAVE_E_INVALID, "sequence lengths must be positive multiples of 16; got seq_q=%d, seq_k=%d",
                 d->seq_q, d->seq_k);
-  if (d->head_dim != 128)
-    return fail(WAVE_E_UNSUPPORTED, "head_dim must be 128; got %d", d->head_dim);
+  if (d->head_dim < 16 || d->head_dim > 128 || d->head_dim % 16 != 0)
+    return fail(WAVE_E_UNSUPPORTED, "head_dim must be a multiple of 16 between 16 and 128; got %d", d->head_dim);
   if (d->io_type != WAVE_BF16 && d->io_type != WAVE_F16)
     return fail(WAVE_E_UNSUPPORTED, "io_type must be bf16 or f16; got %d", d->io_type);
   if (d->causal && d->seq_q != d->seq_k)
@@ -550,6 +550,7 @@ int wave_cuda_flash_attention_fwd(const wave_fa_desc *d, const void *Q, const vo
   p.head_dim = d->head_dim;
   p.causal = d->causal ? 1 : 0;
   p.is_bf16 = d->io_type == WAVE_BF16;
+  p.out_f32 = d->out_f32 ? 1 : 0;
   const double scale = d->scale > 0.0f ? static_cast<double>(d->scale) : 1.0 / std::sqrt(static_cast<double>(d->head_dim));
   p.scale = static_cast<float>(scale);
   p.scale_log2e = static_cast<float>(scale * 1.4426950408889634);
@@ -572,7 +573,8 @@ int wave_cuda_flash_attention_fwd_host(const wave_fa_desc *d, const void *Q_host
   const size_t bh = static_cast<size_t>(d->batch) * d->heads;
   const size_t q_bytes = bh * d->seq_q * d->head_dim * 2, kv_bytes = bh * d->seq_k * d->head_dim * 2;
   const size_t off_k = align_up(q_bytes, 256), off_v = off_k + align_up(kv_bytes, 256);
-  const size_t off_o = off_v + align_up(kv_bytes, 256), total = off_o + align_up(q_bytes, 256);
+  const size_t o_bytes = d->out_f32 ? 2 * q_bytes : q_bytes;
+  const size_t off_o = off_v + align_up(kv_bytes, 256), total = off_o + align_up(o_bytes, 256);
   std::lock_guard<std::mutex> lock(g_arena_mu);
   void *base = nullptr;
   if ((rc = arena_reserve(total, &base)) != WAVE_OK)
@@ -588,7 +590,7 @@ int wave_cuda_flash_attention_fwd_host(const wave_fa_desc *d, const void *Q_host
     return cuda_fail(err, "copy V to device");
   if ((rc = wave_cuda_flash_attention_fwd(d, dev, dev + off_k, dev + off_v, dev + off_o, nullptr, stream)) != WAVE_OK)
     return rc;
-  if ((err = cudaMemcpyAsync(O_host, dev + off_o, q_bytes, cudaMemcpyDeviceToHost, s)) != cudaSuccess)
+  if ((err = cudaMemcpyAsync(O_host, dev + off_o, o_bytes, cudaMemcpyDeviceToHost, s)) != cudaSuccess)
     return cuda_fail(err, "copy O to host");
   if ((err = cudaStreamSynchronize(s)) != cudaSuccess)
     return cuda_fail(err, "synchronise after attention");

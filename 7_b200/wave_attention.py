@@ -17,7 +17,7 @@ import numpy as np
 from . import wave_cuda as wc
 from .wave_matmul import deterministic_random_values, input_bits
 
-HEAD_DIM = 128   # wave_flash_attention.py: the production kernel's only head dimension
+HEAD_DIM = 128   # wave_flash_attention.py: the production kernel's only head dimension (others run zero-padded)
 BLOCK_M = 256    # query rows per workgroup (wave_flash_attention.py:23)
 
 
@@ -70,6 +70,20 @@ def attention(q, k, v, sm_scale: float | None = None, causal: bool = False, *, o
         raise ValueError(err.message) from None
     wc.flash_attention_fwd(desc, q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
                            lse.data_ptr() if lse is not None else 0, torch.cuda.current_stream().cuda_stream)
+    return out
+
+
+def run_toy_attention_f32(q_bits: np.ndarray, k_bits: np.ndarray, v_bits: np.ndarray) -> np.ndarray:
+    """The reference's toy kernel `flash_attention_f32`
+    (python/mlir/dialects/wave_attention.py:18, 225-278): one [block_m, d] f16
+    Q tile already multiplied by log2(e)/sqrt(d), [seq_n, d] f16 K and V, f32
+    output, probabilities 2^(s - max).  A softmax scale of ln 2 turns the
+    backend's exp2(scale*log2(e)*s) into exactly that."""
+    q, k, v = (np.ascontiguousarray(x, np.uint16) for x in (q_bits, k_bits, v_bits))
+    desc = wc.fa_desc(1, 1, q.shape[-2], k.shape[-2], q.shape[-1], scale=math.log(2.0), io_type=wc.F16, out_f32=True)
+    out = np.zeros(q.shape[-2:], np.float32)
+    wc.flash_attention_fwd_host(desc, q.ctypes.data, k.ctypes.data, v.ctypes.data, out.ctypes.data)
+    wc.check_device_status()
     return out
 
 

@@ -35,7 +35,8 @@ class GemmDesc(C.Structure):
 
 class FaDesc(C.Structure):
     _fields_ = [("batch", C.c_int), ("heads", C.c_int), ("seq_q", C.c_int), ("seq_k", C.c_int),
-                ("head_dim", C.c_int), ("scale", C.c_float), ("causal", C.c_int), ("io_type", C.c_int)]
+                ("head_dim", C.c_int), ("scale", C.c_float), ("causal", C.c_int), ("io_type", C.c_int),
+                ("out_f32", C.c_int)]
 
 
 EXPORTS = [
@@ -135,8 +136,8 @@ def gemm_host(desc: GemmDesc, a_ptr: int, b_ptr: int, c_ptr: int, stream: int = 
 
 
 def fa_desc(batch: int, heads: int, seq_q: int, seq_k: int, head_dim: int = 128, *, scale: float = 0.0,
-            causal: bool = False, io_type: int = BF16) -> FaDesc:
-    return FaDesc(batch, heads, seq_q, seq_k, head_dim, scale, int(causal), io_type)
+            causal: bool = False, io_type: int = BF16, out_f32: bool = False) -> FaDesc:
+    return FaDesc(batch, heads, seq_q, seq_k, head_dim, scale, int(causal), io_type, int(out_f32))
 
 
 def fa_validate(desc: FaDesc) -> None:

@@ -145,10 +145,15 @@ int wave_cuda_gemm_plan(const wave_gemm_desc *desc, int *tile_m, int *tile_n, in
 typedef struct wave_fa_desc {
   int batch, heads;
   int seq_q, seq_k; /* multiples of 16 */
-  int head_dim;     /* 128, the reference kernel's only value (wave_flash_attention.py:43-60) */
+  int head_dim;     /* 128 is the reference production kernel's only value
+                       (wave_flash_attention.py:43-60) and the tuned one; multiples of 16
+                       up to 128 (the toy kernel's 16/32/64, wave_attention.py) run
+                       zero-padded to 128 */
   float scale;      /* 0 = 1/sqrt(head_dim) */
   int causal;
   int io_type;      /* WAVE_BF16 | WAVE_F16 */
+  int out_f32;      /* non-zero: O is f32 (the toy kernel `flash_attention_f32`, f16 in /
+                       f32 out, wave_attention.py:18); zero: O has io_type */
 } wave_fa_desc;
 
 int wave_cuda_fa_validate(const wave_fa_desc *desc);

@@ -90,7 +90,8 @@ def test_streamk_workspace_sizes(wc, oracle):
 @pytest.mark.parametrize("kwargs,message", [
     (dict(batch=0), "batch and heads must be positive"),
     (dict(seq_q=100), "sequence lengths must be positive multiples of 16"),
-    (dict(head_dim=96), "head_dim must be 128"),
+    (dict(head_dim=72), "head_dim must be a multiple of 16 between 16 and 128"),
+    (dict(head_dim=256), "head_dim must be a multiple of 16 between 16 and 128"),
     (dict(io_type=2), "io_type must be bf16 or f16"),
     (dict(causal=True, seq_k=512), "causal attention requires seq_q == seq_k"),
     (dict(scale=-1.0), "scale must be finite"),

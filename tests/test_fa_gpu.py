@@ -18,13 +18,15 @@ pytestmark = pytest.mark.gpu
 REFERENCE_MAX_ABS = 3.0e-2  # wave-fa-gfx950-runner.cpp:388
 
 
-def run_fa(torch, wc, q_bits, k_bits, v_bits, io_name, batch, heads, causal, scale=0.0, want_lse=False):
+def run_fa(torch, wc, q_bits, k_bits, v_bits, io_name, batch, heads, causal, scale=0.0, want_lse=False,
+           out_f32=False):
     BH, Sq, D = q_bits.shape
     Sk = k_bits.shape[1]
     assert BH == batch * heads
-    desc = wc.fa_desc(batch, heads, Sq, Sk, D, scale=scale, causal=causal, io_type=wc.TYPE_BY_NAME[io_name])
+    desc = wc.fa_desc(batch, heads, Sq, Sk, D, scale=scale, causal=causal, io_type=wc.TYPE_BY_NAME[io_name],
+                      out_f32=out_f32)
     q, k, v = (to_device_bits(torch, x) for x in (q_bits, k_bits, v_bits))
-    dt = torch.bfloat16 if io_name == "bf16" else torch.float16
+    dt = torch.float32 if out_f32 else torch.bfloat16 if io_name == "bf16" else torch.float16
     o = torch.full((BH, Sq, D), float("nan"), dtype=dt, device="cuda")
     lse = torch.full((BH, Sq), float("nan"), dtype=torch.float32, device="cuda") if want_lse else None
     wc.flash_attention_fwd(desc, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
@@ -131,3 +133,31 @@ def test_rows_are_convex_combinations(cuda, wc, oracle):
     got = run_fa(cuda, wc, q, k, v, "bf16", 1, BH, True)
     want = np.broadcast_to(oracle.from_bits(vrow, t), (BH, S, 128))
     assert np.abs(got - want).max() <= 1e-2 * np.abs(want).max()
+
+
+@pytest.mark.parametrize("D,causal", [(64, True), (64, False), (32, False), (96, True), (16, False)])
+def test_smaller_head_dims_run_zero_padded(cuda, wc, oracle, D, causal):
+    t = oracle.BF16
+    q, k, v = normal_qkv(oracle, 2, 384, 384, D, t, seed=D)
+    got = run_fa(cuda, wc, q, k, v, "bf16", 1, 2, causal)
+    want = oracle.fa_ref(q, k, v, t, 1.0 / np.sqrt(float(D)), causal=causal)
+    check(got, want, f"D={D} causal={causal}")
+
+
+def test_toy_kernel_surface_matches_reference_golden(cuda, wc, oracle):
+    """The reference's toy kernel `flash_attention_f32` (16 query rows, f16 in,
+    f32 out, Q pre-multiplied by log2(e)/sqrt(d), exp2 of the bare scores;
+    python/mlir/dialects/wave_attention.py:225-278) against the outputs recorded
+    from the reference's own Python reference, at the toy runner's tolerance
+    3e-3 (tools/wave-fa-calibrate/wave-fa-calibrate-runner.cpp:263)."""
+    import json
+    import os
+    from test_oracle import toy_fa_inputs
+    with open(os.path.join(os.path.dirname(__file__), "golden", "fa_toy_golden.json")) as f:
+        cases = json.load(f)["cases"]
+    for entry in cases:
+        c = entry["case"]
+        q, k, v = toy_fa_inputs(oracle, c["block_m"], c["head_dim"], c["seq_n"], c["random_seed"])
+        got = run_fa(cuda, wc, q, k, v, "f16", 1, 1, False, scale=float(np.log(2.0)), out_f32=True)
+        want = np.asarray(entry["out"], np.float64).reshape(got.shape)
+        assert np.abs(got - want).max() <= 3.0e-3, c
