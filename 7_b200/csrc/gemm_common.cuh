@@ -37,6 +37,45 @@ template <typename T, int W>
 __device__ __forceinline__ void store_row_chunk(const GemmParams &p, int m, int n0, const float (&v)[W]) {
   if (m >= p.M)
     return;
+  if (p.tile_packed) {
+    // Tile-packed output: 16 x 16 tiles stored one after another, row-major
+    // inside a tile, in the reference's workgroup -> wave -> per-wave-tile
+    // order (python/mlir/dialects/wave_matmul.py:1025-1041, 1106-1139).
+    constexpr int per_vec = 16 / sizeof(T);
+    const int m_tile = m >> 4;
+    const int tm = p.tp_bm * p.tp_wmt, tn = p.tp_bn * p.tp_wnt;
+    const int wg_m = m_tile / tm, rm = m_tile % tm;
+    const int m_wave = rm / p.tp_wmt, ti = rm % p.tp_wmt;
+#pragma unroll
+    for (int g = 0; g < W; g += 16) {
+      const int n = n0 + g;
+      if (n >= p.N)
+        break;
+      const int n_tile = n >> 4;
+      const int wg_n = n_tile / tn, rn = n_tile % tn;
+      const int n_wave = rn / p.tp_wnt, tj = rn % p.tp_wnt;
+      const long long tile =
+          (((static_cast<long long>(wg_m) * p.tp_n_blocks + wg_n) * (p.tp_bm * p.tp_bn) + (m_wave * p.tp_bn + n_wave)) *
+               p.tp_wmt +
+           ti) *
+              p.tp_wnt +
+          tj;
+      T *dst = reinterpret_cast<T *>(p.C) + tile * 256 + (m & 15) * 16;
+#pragma unroll
+      for (int j = 0; j < 16; j += per_vec) {
+        if constexpr (sizeof(T) == 4) {
+          *reinterpret_cast<float4 *>(dst + j) = make_float4(v[g + j], v[g + j + 1], v[g + j + 2], v[g + j + 3]);
+        } else {
+          T tmp[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e)
+            store_elem(&tmp[e], v[g + j + e]);
+          *reinterpret_cast<uint4 *>(dst + j) = *reinterpret_cast<uint4 *>(tmp);
+        }
+      }
+    }
+    return;
+  }
   T *base = reinterpret_cast<T *>(p.C) + static_cast<long long>(m) * p.stride_m +
             static_cast<long long>(n0) * p.stride_n;
   if (p.stride_n == 1) {

@@ -24,6 +24,8 @@ struct GemmParams {
   int streamk_workers; // 0: persistent data-parallel tiles; >0: Stream-K with that grid
   float *scratch;      // Stream-K: [workers][2][128 x tile_n] f32 partial tiles
   int *counters;       // Stream-K: one arrival counter per output tile, zero on entry and exit
+  // tile-packed output (16 x 16 tiles in workgroup -> wave -> per-wave-tile order)
+  int tile_packed, tp_bm, tp_bn, tp_wmt, tp_wnt, tp_n_blocks;
 };
 
 int gemm_tile_m();

@@ -140,7 +140,7 @@ int make_plan(const wave_gemm_desc &d, int sms, bool have_workspace, GemmPlan *p
   GemmPlan p{};
   // A 128-row UMMA wastes most of its rows on a skinny M; put N on the rows
   // instead and M on the (narrow) column tile.
-  p.swapped = d.M < tile_m && d.N > d.M;
+  p.swapped = d.M < tile_m && d.N > d.M && d.out_layout != WAVE_TILE_PACKED;
   p.Mk = p.swapped ? d.N : d.M;
   p.Nk = p.swapped ? d.M : d.N;
   const int want = p.swapped ? want_m : want_n;
@@ -309,9 +309,8 @@ int wave_cuda_gemm_validate(const wave_gemm_desc *d) {
                 d->wave_m_tiles, d->wave_n_tiles, d->wave_k_tiles);
   if (d->out_type != WAVE_F32 && d->out_type != WAVE_F16 && d->out_type != WAVE_BF16)
     return fail(WAVE_E_INVALID, "output_type must be one of f32, f16, bf16; got %d", d->out_type);
-  if (d->out_layout != WAVE_ROW_MAJOR && d->out_layout != WAVE_COL_MAJOR)
-    return fail(WAVE_E_UNSUPPORTED, "output_layout must be one of row-major, column-major; got %d "
-                                    "(tile-packed output is not implemented by this backend)",
+  if (d->out_layout != WAVE_ROW_MAJOR && d->out_layout != WAVE_COL_MAJOR && d->out_layout != WAVE_TILE_PACKED)
+    return fail(WAVE_E_INVALID, "output_layout must be one of row-major, column-major, tile-packed; got %d",
                 d->out_layout);
   if (d->in_type != WAVE_F16 && d->in_type != WAVE_BF16)
     return fail(WAVE_E_UNSUPPORTED, "input_type must be one of f16, bf16; got %d (mxfp4 is outside this backend)",
@@ -341,6 +340,8 @@ int wave_cuda_gemm_validate(const wave_gemm_desc *d) {
                 m_blocks, d->cta_group_m);
   if (d->streamk_workers < 0)
     return fail(WAVE_E_INVALID, "streamk_workers must be >= 0; got %d", d->streamk_workers);
+  if (d->out_layout == WAVE_TILE_PACKED && d->ldc != 0)
+    return fail(WAVE_E_INVALID, "ldc must be 0 with tile-packed output; got %d", d->ldc);
   const int min_ld = d->out_layout == WAVE_ROW_MAJOR ? d->N : d->M;
   if (d->ldc != 0 && (d->ldc < min_ld || d->ldc % 16 != 0))
     return fail(WAVE_E_INVALID, "ldc must be 0 or a multiple of 16 that is >= %d; got %d", min_ld, d->ldc);
@@ -459,6 +460,14 @@ int wave_cuda_gemm(const wave_gemm_desc *d, const void *A, const void *B, void *
     if (g > plan.num_m)
       g = plan.num_m;
     p.group_m = g;
+  }
+  if (d->out_layout == WAVE_TILE_PACKED) {
+    p.tile_packed = 1;
+    p.tp_bm = d->bm;
+    p.tp_bn = d->bn;
+    p.tp_wmt = d->wave_m_tiles;
+    p.tp_wnt = d->wave_n_tiles;
+    p.tp_n_blocks = (d->N / 16) / (d->bn * d->wave_n_tiles);
   }
   p.streamk_workers = plan.streamk_workers;
   p.scratch = static_cast<float *>(workspace);

@@ -13,11 +13,11 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libwave_cuda.so")
 
 F16, BF16, F32 = 0, 1, 2
-ROW_MAJOR, COL_MAJOR = 0, 1
+ROW_MAJOR, COL_MAJOR, TILE_PACKED = 0, 1, 2
 OK, E_INVALID, E_UNSUPPORTED, E_CUDA, E_DEVICE_STATUS, E_NOT_FOUND = 0, -1, -2, -3, -4, -5
 
 TYPE_BY_NAME = {"f16": F16, "bf16": BF16, "f32": F32}
-LAYOUT_BY_NAME = {"row-major": ROW_MAJOR, "column-major": COL_MAJOR}
+LAYOUT_BY_NAME = {"row-major": ROW_MAJOR, "column-major": COL_MAJOR, "tile-packed": TILE_PACKED}
 
 
 class WaveCudaError(RuntimeError):

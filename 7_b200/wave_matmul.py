@@ -156,7 +156,7 @@ class MatmulConfig:
 
     def __post_init__(self):
         for name, table in (("input_type", ("f16", "bf16")), ("output_type", ("f32", "f16", "bf16")),
-                            ("output_layout", ("row-major", "column-major"))):
+                            ("output_layout", ("row-major", "column-major", "tile-packed"))):
             if getattr(self, name) not in table:
                 raise ValueError(f"{name} must be one of {', '.join(table)}; got {getattr(self, name)}")
         try:
@@ -213,8 +213,8 @@ def run_matmul(cfg: MatmulConfig, a_bits: np.ndarray, b_bits: np.ndarray) -> np.
     b = np.ascontiguousarray(b_bits, np.uint16)
     if a.shape != (cfg.M, cfg.K) or b.shape != (cfg.N, cfg.K):
         raise ValueError(f"A must be {cfg.M}x{cfg.K} and B {cfg.N}x{cfg.K} (B is stored transposed)")
-    ld = cfg.ldc or (cfg.N if cfg.output_layout == "row-major" else cfg.M)
-    outer = cfg.M if cfg.output_layout == "row-major" else cfg.N
+    ld = cfg.ldc or (cfg.M if cfg.output_layout == "column-major" else cfg.N)
+    outer = cfg.N if cfg.output_layout == "column-major" else cfg.M
     out = np.zeros(ld * outer, _OUT_DTYPES[cfg.output_type])
     wc.gemm_host(cfg.desc(), a.ctypes.data, b.ctypes.data, out.ctypes.data)
     wc.check_device_status()

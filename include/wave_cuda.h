@@ -37,6 +37,10 @@ extern "C" {
 #define WAVE_F32 2
 #define WAVE_ROW_MAJOR 0 /* C[m*ldc + n]   (wave_matmul.py:1040) */
 #define WAVE_COL_MAJOR 1 /* C[n*ldc + m]   (wave_matmul.py:1040) */
+#define WAVE_TILE_PACKED 2 /* 16x16 tiles one after another, row-major inside a tile, in
+                              workgroup -> wave -> per-wave-tile order: the order in which
+                              compute_wmma_f16_matmul_reference_buffer emits them
+                              (wave_matmul.py:1025-1028, 1106-1139) */
 
 const char *wave_cuda_last_error(void);
 const char *wave_cuda_version(void);
@@ -72,7 +76,7 @@ typedef struct wave_gemm_desc {
   int wave_m_tiles, wave_n_tiles, wave_k_tiles; /* 16x16 tiles per wave, K slices per step */
   int in_type;                 /* WAVE_F16 | WAVE_BF16                                      */
   int out_type;                /* WAVE_F32 | WAVE_F16 | WAVE_BF16                           */
-  int out_layout;              /* WAVE_ROW_MAJOR | WAVE_COL_MAJOR                           */
+  int out_layout;              /* WAVE_ROW_MAJOR | WAVE_COL_MAJOR | WAVE_TILE_PACKED        */
   int cta_group_m;             /* grouped-M rasterisation (wave_matmul.py:1267-1272); >= 1 */
   int streamk_workers;         /* 0 auto, 1 plain tiles, >1 persistent Stream-K grid
                                   (--streamk-workers, wave-matmul-calibrate.py:1170)      */

@@ -222,12 +222,32 @@ def np_gemm_ref(a_bits, b_bits, dtype: int) -> np.ndarray:
     return acc
 
 
-def layout_output(c_rowmajor: np.ndarray, layout: str) -> np.ndarray:
-    """Logical [M,N] -> the flat physical buffer (wave_matmul.py:1025-1041)."""
+def layout_output(c_rowmajor: np.ndarray, layout: str, BM: int = 1, BN: int = 1, wave_m_tiles: int = 1,
+                  wave_n_tiles: int = 1) -> np.ndarray:
+    """Logical [M,N] -> the flat physical buffer (wave_matmul.py:1025-1041).
+    Tile-packed: 16x16 tiles appended in the loop order of
+    compute_wmma_f16_matmul_reference_buffer (wave_matmul.py:1106-1139):
+    workgroup rows, workgroup columns, waves (m_wave = id // BN, n_wave = id % BN),
+    per-wave tile rows, per-wave tile columns; row-major inside a tile."""
     if layout == "row-major":
         return np.ascontiguousarray(c_rowmajor).reshape(-1)
     if layout == "column-major":
         return np.ascontiguousarray(c_rowmajor.T).reshape(-1)
+    if layout == "tile-packed":
+        M, N = c_rowmajor.shape
+        m_blocks = (M // 16) // (BM * wave_m_tiles)
+        n_blocks = (N // 16) // (BN * wave_n_tiles)
+        out = []
+        for wg_m in range(m_blocks):
+            for wg_n in range(n_blocks):
+                for wave in range(BM * BN):
+                    m_wave, n_wave = wave // BN, wave % BN
+                    for i in range(wave_m_tiles):
+                        for j in range(wave_n_tiles):
+                            mt = wg_m * BM * wave_m_tiles + m_wave * wave_m_tiles + i
+                            nt = wg_n * BN * wave_n_tiles + n_wave * wave_n_tiles + j
+                            out.append(c_rowmajor[mt * 16:(mt + 1) * 16, nt * 16:(nt + 1) * 16].reshape(-1))
+        return np.concatenate(out)
     raise ValueError(layout)
 
 

@@ -78,6 +78,10 @@ GEMM_CASES = [
     dict(M=64, N=32, K=128, BM=2, BN=2, random_data=True, random_seed=3, output_type="f16"),
     dict(M=48, N=80, K=96, random_data=True, random_seed=12345, input_type="bf16",
          matrix_intrinsic="mfma_gfx950"),
+    dict(M=64, N=96, K=32, BM=2, BN=2, wave_m_tiles=2, wave_n_tiles=3, random_data=True, random_seed=21,
+         output_layout="tile-packed"),
+    dict(M=32, N=32, K=64, BM=2, BN=2, wave_k_tiles=2, random_data=True, random_seed=7,
+         output_layout="tile-packed", output_type="f16"),
 ]
 
 FA_CASES = [

@@ -31,6 +31,7 @@ def test_example_driver_compare_cpu_reference_case(cuda):
 @pytest.mark.parametrize("extra", [
     ["--input-type=bf16", "--output-type=f16"],
     ["--output-layout=column-major", "--wave-m-tiles=2", "--wave-n-tiles=2"],
+    ["--output-layout=tile-packed", "--bm=2", "--bn=2", "--wave-n-tiles=2"],
 ])
 def test_example_driver_variants(cuda, extra):
     out, _ = run("wmma_matmul_tiled.py", "--m=64", "--n=128", "--k=96", "--compare-cpu", "--seed=3", *extra)

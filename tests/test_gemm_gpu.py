@@ -175,6 +175,35 @@ def test_pair_kernel_random_inputs(cuda, wc, oracle):
     assert ok, f"{nbad} elements out of tolerance, worst abs diff {worst}"
 
 
+@pytest.mark.parametrize("M,N,K,out_name,streamk,knobs", [
+    (64, 96, 32, "f32", 1, dict(bm=2, bn=2, wave_m_tiles=2, wave_n_tiles=3)),
+    (32, 32, 64, "f16", 1, dict(bm=2, bn=2, wave_k_tiles=2)),
+    (256, 512, 128, "bf16", 1, dict(bm=4, bn=4, wave_m_tiles=4, wave_n_tiles=4)),   # CTA-pair kernel
+    (384, 256, 1024, "f32", 7, dict(bm=2, bn=4, wave_m_tiles=3, wave_n_tiles=4)),   # Stream-K
+    (16, 256, 64, "f32", 1, dict(bn=1, wave_n_tiles=2)),                            # skinny M, not swapped
+])
+def test_tile_packed_output(cuda, wc, oracle, M, N, K, out_name, streamk, knobs):
+    """Tile-packed C in the order the reference's Python reference emits it
+    (wave_matmul.py:1025-1028, 1106-1139); LCG inputs, bit-exact."""
+    a_bits, b_bits = lcg_inputs(oracle, M, N, K, "f16", seed=K)
+    desc = wc.gemm_desc(M, N, K, out_type=wc.TYPE_BY_NAME[out_name], out_layout=wc.TILE_PACKED,
+                        streamk_workers=streamk, **knobs)
+    a, b = to_device_bits(cuda, a_bits), to_device_bits(cuda, b_bits)
+    c = device_out(cuda, M * N, out_name)
+    scratch, counters = wc.gemm_workspace_bytes(desc)
+    ws = cuda.zeros(scratch + counters, dtype=cuda.uint8, device="cuda") if scratch + counters else None
+    os.environ["WAVE_CUDA_GEMM_KERNEL"] = "pair"
+    try:
+        wc.gemm(desc, a.data_ptr(), b.data_ptr(), c.data_ptr(), ws.data_ptr() if ws is not None else 0,
+                cuda.cuda.current_stream().cuda_stream)
+    finally:
+        del os.environ["WAVE_CUDA_GEMM_KERNEL"]
+    wc.check_device_status()
+    want = oracle.layout_output(expected(oracle, a_bits, b_bits, "f16", out_name), "tile-packed", knobs.get("bm", 1),
+                                knobs.get("bn", 2), knobs.get("wave_m_tiles", 1), knobs.get("wave_n_tiles", 1))
+    assert np.array_equal(out_to_f32(cuda, c), want)
+
+
 def test_ldc_writes_column_shard_in_place(cuda, wc, oracle):
     """A rank's N-column shard written straight into a wider row-major C."""
     M, N, K, ldc = 128, 64, 128, 256

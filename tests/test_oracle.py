@@ -137,7 +137,8 @@ def test_gemm_golden_vectors(oracle):
         assert _sha(af) == entry["a_sha256"] and _sha(bf) == entry["b_sha256"]
         c = oracle.round_output(oracle.gemm_ref(a, b, t), case.get("output_type", "f32"))
         layout = case.get("output_layout", "row-major")
-        got = oracle.layout_output(c, layout)
+        got = oracle.layout_output(c, layout, case.get("BM", 1), case.get("BN", 1), case.get("wave_m_tiles", 1),
+                                   case.get("wave_n_tiles", 1))
         want = np.asarray(entry["out"], np.float64)
         assert np.array_equal(got.astype(np.float64), want), case
         # the NumPy restatement agrees too
