@@ -100,32 +100,35 @@ struct Segment {
 // of (tile, k range) segments without talking to each other.
 struct WorkIter {
   const GemmParams &p;
-  long long cur, end; // data-parallel: tile ids (strided); Stream-K: iterations
+  long long dp_cur;   // next whole tile of the data-parallel part (strided by the grid)
+  long long cur, end; // Stream-K part: this worker's interval of (tile, k) iterations
   __device__ WorkIter(const GemmParams &params) : p(params) {
-    if (p.streamk_workers > 0) {
-      streamk_interval(static_cast<long long>(p.num_tiles) * p.k_iters, p.streamk_workers, blockIdx.x, cur, end);
-    } else {
-      cur = blockIdx.x;
-      end = p.num_tiles;
-    }
+    // Tiles [0, dp_tiles) are whole tiles dealt round-robin; tiles
+    // [dp_tiles, num_tiles) are split Stream-K style over all workers.  Pure
+    // data-parallel launches have dp_tiles == num_tiles, pure Stream-K 0.
+    dp_cur = blockIdx.x;
+    cur = end = 0;
+    if (p.streamk_workers > 0)
+      streamk_interval(static_cast<long long>(p.num_tiles - p.dp_tiles) * p.k_iters, p.streamk_workers, blockIdx.x,
+                       cur, end);
   }
   __device__ bool next(Segment &s) {
-    if (cur >= end)
-      return false;
-    if (p.streamk_workers > 0) {
-      const long long tile = cur / p.k_iters;
-      const long long tile_begin = tile * p.k_iters;
-      const long long seg_end = min(end, tile_begin + p.k_iters);
-      s.tile = static_cast<int>(tile);
-      s.k_begin = static_cast<int>(cur - tile_begin);
-      s.k_end = static_cast<int>(seg_end - tile_begin);
-      cur = seg_end;
-    } else {
-      s.tile = static_cast<int>(cur);
+    if (dp_cur < p.dp_tiles) {
+      s.tile = static_cast<int>(dp_cur);
       s.k_begin = 0;
       s.k_end = p.k_iters;
-      cur += gridDim.x;
+      dp_cur += gridDim.x;
+      return true;
     }
+    if (cur >= end)
+      return false;
+    const long long tile = cur / p.k_iters; // index within the Stream-K part
+    const long long tile_begin = tile * p.k_iters;
+    const long long seg_end = min(end, tile_begin + p.k_iters);
+    s.tile = static_cast<int>(tile) + p.dp_tiles;
+    s.k_begin = static_cast<int>(cur - tile_begin);
+    s.k_end = static_cast<int>(seg_end - tile_begin);
+    cur = seg_end;
     return true;
   }
 };
@@ -262,7 +265,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     Segment seg;
     int acc = 0;
     uint32_t acc_phase = 0;
-    const long long total_iters = static_cast<long long>(p.num_tiles) * p.k_iters;
+    const long long total_iters = static_cast<long long>(p.num_tiles - p.dp_tiles) * p.k_iters; // Stream-K part
     while (work.next(seg)) {
       int mb, nb;
       tile_coords(seg.tile, p.num_m_blocks, p.num_n_blocks, p.group_m, mb, nb);
@@ -299,7 +302,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         // Stream-K partial: raw f32 accumulator -> this worker's scratch slot,
         // element (row, col) at col*128 + row so a warp writes 128 contiguous
         // bytes.  Then count the arrival; the last arriver reduces.
-        const int slot = streamk_slot(total_iters, p.streamk_workers, p.k_iters, blockIdx.x, seg.tile);
+        const int sk_tile = seg.tile - p.dp_tiles; // index within the Stream-K part
+        const int slot = streamk_slot(total_iters, p.streamk_workers, p.k_iters, blockIdx.x, sk_tile);
         float *mine = p.scratch + (static_cast<size_t>(blockIdx.x) * 2 + slot) * (kBM * BN);
 #pragma unroll 1
         for (int c = 0; c < BN; c += CW) {
@@ -319,12 +323,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           mbar_arrive(&sh->tempty[acc]); // TMEM buffer is free; the rest is global memory only
         __threadfence();
         asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
-        const long long tile_begin = static_cast<long long>(seg.tile) * p.k_iters;
+        const long long tile_begin = static_cast<long long>(sk_tile) * p.k_iters;
         const int first_owner = streamk_owner(total_iters, p.streamk_workers, tile_begin);
         const int last_owner = streamk_owner(total_iters, p.streamk_workers, tile_begin + p.k_iters - 1);
         const int parts = last_owner - first_owner + 1;
         if (epi_tid == 0) {
-          const int old = atomicAdd(&p.counters[seg.tile], 1);
+          const int old = atomicAdd(&p.counters[sk_tile], 1);
           sh->last_arriver = (old + 1 == parts) ? 1 : 0;
         }
         asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
@@ -340,7 +344,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             for (int j = 0; j < CW; ++j)
               v[j] = 0.0f;
             for (int owner = first_owner; owner <= last_owner; ++owner) {
-              const int oslot = streamk_slot(total_iters, p.streamk_workers, p.k_iters, owner, seg.tile);
+              const int oslot = streamk_slot(total_iters, p.streamk_workers, p.k_iters, owner, sk_tile);
               const float *src = p.scratch + (static_cast<size_t>(owner) * 2 + oslot) * (kBM * BN);
 #pragma unroll
               for (int j = 0; j < CW; ++j)
@@ -349,7 +353,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             store_row_chunk<T, CW>(p, m, nb * BN + c, v);
           }
           if (epi_tid == 0)
-            atomicAdd(&p.counters[seg.tile], -parts); // back to zero for the next launch
+            atomicAdd(&p.counters[sk_tile], -parts); // back to zero for the next launch
         }
         asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory"); // sh->last_arriver may be rewritten
       }

@@ -21,7 +21,8 @@ struct GemmParams {
   int in_type, out_type;
   int num_m_blocks, num_n_blocks, num_tiles, k_iters;
   int group_m;
-  int streamk_workers; // 0: persistent data-parallel tiles; >0: Stream-K with that grid
+  int dp_tiles;        // tiles [0, dp_tiles) are whole tiles dealt round-robin over the grid
+  int streamk_workers; // >0: tiles [dp_tiles, num_tiles) are split Stream-K style over that many workers (= grid)
   float *scratch;      // Stream-K: [workers][2][128 x tile_n] f32 partial tiles
   int *counters;       // Stream-K: one arrival counter per output tile, zero on entry and exit
   // tile-packed output (16 x 16 tiles in workgroup -> wave -> per-wave-tile order)

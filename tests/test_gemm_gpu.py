@@ -135,6 +135,9 @@ def test_random_inputs_within_runner_tolerance(cuda, wc, oracle, M, N, K, in_nam
     (384, 640, 1536, 37, dict(bm=4, bn=4, wave_m_tiles=2, wave_n_tiles=2)),
     (16, 4096, 4096, 148, dict(bn=1)),
     (16, 28672, 8192, 0, dict(bn=1)),
+    # auto mode, several full rounds of tiles plus a thin last one: whole tiles, then a Stream-K tail
+    (2560, 4096, 512, 0, dict(bm=4, bn=4, wave_m_tiles=2, wave_n_tiles=4)),
+    (2688, 1920, 1024, 0, dict(bm=4, bn=4, wave_m_tiles=1, wave_n_tiles=2)),
 ])
 def test_streamk_matches_oracle_and_resets_counters(cuda, wc, oracle, M, N, K, workers, knobs):
     """Stream-K: fixed-order reduction makes two launches bit-identical, and the
