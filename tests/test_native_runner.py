@@ -1,0 +1,66 @@
+"""The CUDA C++ calibrate runner (tests/drivers/wave_matmul_calibrate_runner.cpp):
+its host logic as a plain g++ program without a GPU (the reference tests its HIP
+runner the same way, test/Integration/Inputs/wave_matmul_rand_int_test.cpp), and
+on a GPU the runner itself through the reference's stdout contract
+(test/Integration/wave_gfx950_streamk_f16_runtime.mlir:3-88)."""
+import os
+import shutil
+import subprocess
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+DRIVERS = os.path.join(ROOT, "tests", "drivers")
+LINK = ["-I" + os.path.join(ROOT, "include"), "-L" + os.path.join(ROOT, "7_b200"), "-lwave_cuda",
+        "-L" + os.path.join(ROOT, "oracle"), "-lwave_oracle",
+        "-Wl,-rpath," + os.path.join(ROOT, "7_b200"), "-Wl,-rpath," + os.path.join(ROOT, "oracle")]
+
+
+def test_runner_host_logic_without_gpu(wc, oracle, tmp_path):
+    wc.lib()  # builds libwave_cuda.so if needed
+    exe = str(tmp_path / "runner_host_test")
+    subprocess.run(["g++", "-std=c++17", "-O1", os.path.join(DRIVERS, "runner_host_test.cpp"), "-o", exe, *LINK],
+                   check=True, cwd=DRIVERS)
+    proc = subprocess.run([exe], capture_output=True, text=True)
+    assert proc.returncode == 0 and "runner_host_test: ok" in proc.stdout, proc.stdout + proc.stderr
+
+
+@pytest.fixture(scope="module")
+def runner_exe(tmp_path_factory):
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    exe = str(tmp_path_factory.mktemp("runner") / "wave_matmul_calibrate_runner")
+    link = [a.replace("-Wl,-rpath,", "-Xlinker=-rpath=") for a in LINK]
+    subprocess.run([nvcc, "-std=c++17", "-O2", "-x", "cu", os.path.join(DRIVERS, "wave_matmul_calibrate_runner.cpp"),
+                    "-o", exe, *link], check=True, cwd=DRIVERS)
+    return exe
+
+
+def _run(exe, *args, expect=0):
+    proc = subprocess.run([exe, *map(str, args)], capture_output=True, text=True, timeout=600)
+    assert proc.returncode == expect, proc.stdout + proc.stderr
+    return proc.stdout, proc.stderr
+
+
+@pytest.mark.gpu
+def test_runner_plain_abi(cuda, oracle, runner_exe):
+    out, _ = _run(runner_exe, "--m=256", "--n=512", "--k=1024", "--bm=4", "--bn=4", "--wave-m-tiles=2",
+                  "--wave-n-tiles=4", "--rand-int", "--iters=5", "--warmup=2", "--c-type=f16", "--hsaco", "unused.hsaco")
+    for key in ("kernel: wmma_f16_matmul_tiled", "shape: m=256 n=512 k=1024", "loop_trip_count: 63", "iters: 5",
+                "per_launch_us: ", "output_check: passed mode=strict layout=row-major elements=131072"):
+        assert key in out, out
+
+
+@pytest.mark.gpu
+def test_runner_streamk_abi_and_counter_reset(cuda, oracle, runner_exe):
+    out, _ = _run(runner_exe, "--m=512", "--n=512", "--k=2048", "--bm=4", "--bn=4", "--wave-m-tiles=2",
+                  "--wave-n-tiles=4", "--hpl", "--input-type=bf16", "--kernel-abi=streamk", "--streamk-workers=5",
+                  "--iters=1000", "--warmup=2", "--output-layout=column-major")
+    assert "output_check: passed mode=strict layout=column-major" in out and "streamk_counter_check: passed" in out
+
+
+@pytest.mark.gpu
+def test_runner_exit_codes(cuda, oracle, runner_exe):
+    _, err = _run(runner_exe, "--m=64", "--n=64", "--k=64", "--bn=3", expect=2)
+    assert "BN must be a positive power of two" in err
+    _, err = _run(runner_exe, "--rand-int", "--hpl", expect=2)
+    assert "mutually exclusive" in err
