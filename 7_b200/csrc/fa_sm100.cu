@@ -7,7 +7,9 @@
 // unrounded probabilities with 16-bit probabilities feeding P*V (:706-722),
 // and the lazy accumulator rescale with threshold 8 in log2 units (:557-583).
 //
-// Structure (one CTA per 256 query rows of one head, 384 threads):
+// Structure (persistent CTAs, one per SM, 384 threads; a work item is 256 query
+// rows of one head, drawn from a ticket counter so that the causal triangle
+// balances itself and the prologue/epilogue of one item overlaps the next):
 //   warp 0        TMA producer: two 128-row Q tiles once, then K and V blocks
 //                 of 128 keys through two-stage rings (128B-swizzled smem)
 //   warp 1        UMMA issuer (one thread): S_t = Q_t K^T (both operands from
@@ -26,6 +28,7 @@
 #include "fa_sm100.h"
 #include "sm100_ptx.cuh"
 
+#include <atomic>
 #include <cstdlib>
 #include <type_traits>
 
@@ -34,6 +37,11 @@ namespace wave {
 void set_last_error(const char *message); // wave_cuda_backend.cu
 
 __device__ int g_fa_status[4]; // [0] code, [1] linear block, [2] role, [3] detail
+
+// Work-item ticket counters: one per launch in flight (ring), cleared by the
+// launcher on the launch's stream.
+constexpr unsigned kTicketSlots = 64;
+__device__ unsigned int g_fa_tickets[kTicketSlots];
 
 // Optional stage stamps (clock64) for one CTA, compiled in with -DWAVE_FA_TRACE:
 // [role][block][stamp].  Role 0 = UMMA thread, 1 = softmax tile 0 (row 0),
@@ -81,12 +89,43 @@ static_assert((kLaunchRegs - kIssueRegs) * 128 >= (kSoftmaxRegs - kLaunchRegs) *
 static_assert(kIssueRegs % 8 == 0 && kSoftmaxRegs % 8 == 0, "setmaxnreg takes multiples of 8"); // log2 units (wave_flash_attention.py:563-569)
 
 struct FaShared {
-  uint64_t q_full;
+  uint64_t item_full[2], item_empty[2]; // work-item hand-off from the loader to the other roles
+  uint64_t q_full, q_empty;
   uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
-  uint64_t s_full[2], p_full[2], o_full[2];
+  uint64_t s_full[2], p_full[2], o_full[2], o_free[2];
   uint32_t tmem_base;
   int abort_flag;
+  int item_idx[2];
 };
+
+// One work item = 256 query rows (two tiles) of one (batch, head).  Items are
+// numbered head-major with the heaviest causal query block of a head first, so
+// that CTAs running at the same time share a head's K/V through L2.
+struct WorkItem {
+  int q_blk, bh;
+  int n_blocks[2]; // K/V blocks each Q tile visits (0: tile is past the end of Q)
+  int n_max;
+};
+__device__ __forceinline__ WorkItem decode_item(int idx, const FaParams &p) {
+  WorkItem w;
+  const int nq = (p.seq_q + 2 * kBlockM - 1) / (2 * kBlockM);
+  w.bh = idx / nq;
+  w.q_blk = nq - 1 - idx % nq;
+  const int n_kv_blocks = (p.seq_k + kBlockN - 1) / kBlockN;
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int q0 = w.q_blk * 2 * kBlockM + t * kBlockM;
+    int n = 0;
+    if (q0 < p.seq_q) {
+      n = n_kv_blocks;
+      if (p.causal)
+        n = min(n, q0 / kBlockN + 1);
+    }
+    w.n_blocks[t] = n;
+  }
+  w.n_max = max(w.n_blocks[0], w.n_blocks[1]);
+  return w;
+}
 
 __device__ __forceinline__ void fa_report(int code, int role, int detail) {
   if (atomicCAS(&g_fa_status[0], 0, code) == 0) {
@@ -159,29 +198,14 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  // Heaviest causal tiles first: the last query block of a head has the most keys.
-  const int q_blk = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
-  const int bh = blockIdx.y;
-  const int n_kv_blocks = (p.seq_k + kBlockN - 1) / kBlockN;
-
-  // Number of K/V blocks each Q tile visits (0: tile is past the end of Q).
-  int n_blocks[2];
-#pragma unroll
-  for (int t = 0; t < 2; ++t) {
-    const int q0 = q_blk * 2 * kBlockM + t * kBlockM;
-    int n = 0;
-    if (q0 < p.seq_q) {
-      n = n_kv_blocks;
-      if (p.causal)
-        n = min(n, q0 / kBlockN + 1);
-    }
-    n_blocks[t] = n;
-  }
-  const int n_max = max(n_blocks[0], n_blocks[1]);
+  const int total_items = p.batch_heads * ((p.seq_q + 2 * kBlockM - 1) / (2 * kBlockM));
 
   if (threadIdx.x == 0) {
     mbar_init(&sh->q_full, 1);
+    mbar_init(&sh->q_empty, 1);
     for (int s = 0; s < 2; ++s) {
+      mbar_init(&sh->item_full[s], 1);
+      mbar_init(&sh->item_empty[s], 9); // the UMMA thread and one lane of each softmax warp
       mbar_init(&sh->k_full[s], 1);
       mbar_init(&sh->k_empty[s], 1);
       mbar_init(&sh->v_full[s], 1);
@@ -189,6 +213,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       mbar_init(&sh->s_full[s], 1);
       mbar_init(&sh->p_full[s], kBlockM); // every softmax thread of the tile arrives
       mbar_init(&sh->o_full[s], 1);
+      mbar_init(&sh->o_free[s], 4);       // one lane of each softmax warp of the tile
     }
     sh->abort_flag = 0;
     fence_barrier_init();
@@ -209,46 +234,66 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kIssueRegs));
   if (warp == 0) {
     // ---------------------------------------------------------------- loads
+    // The loader also hands out work: it draws the next item from a global
+    // ticket counter (CTAs are persistent, one per SM, so the draw balances
+    // the causal triangle by itself) and publishes it to the other roles.
     if (lane == 0) {
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_v);
-      const int q_tiles = (n_blocks[0] > 0) + (n_blocks[1] > 0);
-      if (q_tiles > 0) {
+      bool ok = true;
+      uint32_t kv_n = 0; // K/V blocks loaded so far: ring stage and phase carry over from item to item
+      for (uint32_t n = 0; ok; ++n) {
+        const int slot = n & 1;
+        if (!mbar_wait(&sh->item_empty[slot], ((n >> 1) & 1) ^ 1, abort_flag)) {
+          fa_report(kStatusWaitTimeout, 0, 1);
+          break;
+        }
+        const int idx = static_cast<int>(atomicAdd(p.ticket, 1u));
+        sh->item_idx[slot] = idx;
+        mbar_arrive(&sh->item_full[slot]);
+        if (idx >= total_items)
+          break;
+        const WorkItem w = decode_item(idx, p);
+        // Q of the previous item may be overwritten once its last Q*K^T has run.
+        if (n > 0 && !mbar_wait(&sh->q_empty, (n - 1) & 1, abort_flag)) {
+          fa_report(kStatusWaitTimeout, 0, 2);
+          break;
+        }
+        const int q_tiles = (w.n_blocks[0] > 0) + (w.n_blocks[1] > 0);
         mbar_arrive_expect_tx(&sh->q_full, static_cast<uint32_t>(q_tiles * kTile));
         for (int t = 0; t < 2; ++t)
-          if (n_blocks[t] > 0)
+          if (w.n_blocks[t] > 0)
             for (int c = 0; c < 2; ++c)
               tma_load_3d(q_smem + t * kTile + c * kSubTile, &tm_q, &sh->q_full, c * 64,
-                          q_blk * 2 * kBlockM + t * kBlockM, bh);
-      }
-      bool ok = true;
-      for (int j = 0; j < n_max && ok; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&sh->k_empty[s], ph ^ 1, abort_flag)) {
-          fa_report(kStatusWaitTimeout, 0, 10 + s);
-          ok = false;
-          break;
+                          w.q_blk * 2 * kBlockM + t * kBlockM, w.bh);
+        for (int j = 0; j < w.n_max && ok; ++j, ++kv_n) {
+          const int s = kv_n & 1;
+          const uint32_t ph = (kv_n >> 1) & 1;
+          if (!mbar_wait(&sh->k_empty[s], ph ^ 1, abort_flag)) {
+            fa_report(kStatusWaitTimeout, 0, 10 + s);
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(&sh->k_full[s], kTile);
+          for (int c = 0; c < 2; ++c)
+            tma_load_3d(k_smem + s * kTile + c * kSubTile, &tm_k, &sh->k_full[s], c * 64, j * kBlockN, w.bh);
+          if (!mbar_wait(&sh->v_empty[s], ph ^ 1, abort_flag)) {
+            fa_report(kStatusWaitTimeout, 0, 20 + s);
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(&sh->v_full[s], kTile);
+          for (int c = 0; c < 2; ++c)
+            tma_load_3d(v_smem + s * kTile + c * kSubTile, &tm_v, &sh->v_full[s], c * 64, j * kBlockN, w.bh);
         }
-        mbar_arrive_expect_tx(&sh->k_full[s], kTile);
-        for (int c = 0; c < 2; ++c)
-          tma_load_3d(k_smem + s * kTile + c * kSubTile, &tm_k, &sh->k_full[s], c * 64, j * kBlockN, bh);
-        if (!mbar_wait(&sh->v_empty[s], ph ^ 1, abort_flag)) {
-          fa_report(kStatusWaitTimeout, 0, 20 + s);
-          ok = false;
-          break;
-        }
-        mbar_arrive_expect_tx(&sh->v_full[s], kTile);
-        for (int c = 0; c < 2; ++c)
-          tma_load_3d(v_smem + s * kTile + c * kSubTile, &tm_v, &sh->v_full[s], c * 64, j * kBlockN, bh);
       }
       if (!ok)
         bounded_delay(1 << 21);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ UMMA issue
-    if (lane == 0 && n_max > 0) {
+    if (lane == 0) {
       const uint32_t idesc_s = umma_idesc_f16(kBlockM, kBlockN, p.is_bf16, 0, 0);
       const uint32_t idesc_o = umma_idesc_f16(kBlockM, kD, p.is_bf16, 0, 1); // V is MN-major
       const uint32_t q_addr = smem_u32(q_smem), k_addr = smem_u32(k_smem), v_addr = smem_u32(v_smem);
@@ -280,68 +325,102 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         }
       };
 
-      if (!mbar_wait(&sh->q_full, 0, abort_flag)) {
-        fa_report(kStatusWaitTimeout, 1, 1);
-        ok = false;
-      }
-      if (ok && !mbar_wait(&sh->k_full[0], 0, abort_flag)) {
-        fa_report(kStatusWaitTimeout, 1, 2);
-        ok = false;
-      }
-      if (ok) {
-        tc_fence_after_sync();
-        for (int t = 0; t < 2; ++t)
-          if (n_blocks[t] > 0)
-            issue_s(t, 0);
-        umma_commit(&sh->k_empty[0]);
-      }
-      for (int j = 0; j < n_max && ok; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        const int s_next = (j + 1) & 1;
-        const uint32_t ph_next = ((j + 1) >> 1) & 1;
-        bool have_v = false, have_k_next = false;
-        for (int t = 0; t < 2 && ok; ++t) {
-          if (j >= n_blocks[t])
-            continue;
-          if (!have_v) {
-            if (!mbar_wait(&sh->v_full[s], ph, abort_flag)) {
-              fa_report(kStatusWaitTimeout, 1, 30 + s);
-              ok = false;
-              break;
-            }
-            have_v = true;
-          }
-          FA_STAMP(0, j, t * 4 + 0);
-          if (!mbar_wait(&sh->p_full[t], j & 1, abort_flag)) {
-            fa_report(kStatusWaitTimeout, 1, 40 + t);
-            ok = false;
+      // Running counts that carry barrier phases from item to item.
+      uint32_t kv_n = 0;              // K/V blocks consumed so far
+      uint32_t p_n[2] = {0, 0};       // P hand-offs waited for, per tile
+      uint32_t tile_items[2] = {0, 0}; // items in which the tile had work (o_full / o_free phases)
+      for (uint32_t n = 0; ok; ++n) {
+        const int slot = n & 1;
+        if (!mbar_wait(&sh->item_full[slot], (n >> 1) & 1, abort_flag)) {
+          fa_report(kStatusWaitTimeout, 1, 3);
+          break;
+        }
+        const int idx = sh->item_idx[slot];
+        mbar_arrive(&sh->item_empty[slot]);
+        if (idx >= total_items)
+          break;
+        const WorkItem w = decode_item(idx, p);
+        const int n_max = w.n_max;
+        if (!mbar_wait(&sh->q_full, n & 1, abort_flag)) {
+          fa_report(kStatusWaitTimeout, 1, 1);
+          break;
+        }
+        {
+          const int s0 = kv_n & 1;
+          if (!mbar_wait(&sh->k_full[s0], (kv_n >> 1) & 1, abort_flag)) {
+            fa_report(kStatusWaitTimeout, 1, 2);
             break;
           }
-          FA_STAMP(0, j, t * 4 + 1);
           tc_fence_after_sync();
-          issue_pv(t, s, j > 0);
-          if (j + 1 < n_blocks[t]) {
-            if (!have_k_next) {
-              if (!mbar_wait(&sh->k_full[s_next], ph_next, abort_flag)) {
-                fa_report(kStatusWaitTimeout, 1, 50 + s_next);
+          for (int t = 0; t < 2; ++t)
+            if (w.n_blocks[t] > 0)
+              issue_s(t, s0);
+          umma_commit(&sh->k_empty[s0]);
+          if (n_max == 1)
+            umma_commit(&sh->q_empty); // no further Q*K^T in this item
+        }
+        for (int j = 0; j < n_max && ok; ++j, ++kv_n) {
+          const int s = kv_n & 1;
+          const uint32_t ph = (kv_n >> 1) & 1;
+          const int s_next = (kv_n + 1) & 1;
+          const uint32_t ph_next = ((kv_n + 1) >> 1) & 1;
+          bool have_v = false, have_k_next = false;
+          for (int t = 0; t < 2 && ok; ++t) {
+            if (j >= w.n_blocks[t])
+              continue;
+            if (!have_v) {
+              if (!mbar_wait(&sh->v_full[s], ph, abort_flag)) {
+                fa_report(kStatusWaitTimeout, 1, 30 + s);
                 ok = false;
                 break;
               }
-              tc_fence_after_sync();
-              have_k_next = true;
+              have_v = true;
             }
-            issue_s(t, s_next);
-            FA_STAMP(0, j, t * 4 + 2);
-          } else {
-            umma_commit(&sh->o_full[t]);
+            if (n == 0)
+              FA_STAMP(0, j, t * 4 + 0);
+            if (!mbar_wait(&sh->p_full[t], p_n[t] & 1, abort_flag)) {
+              fa_report(kStatusWaitTimeout, 1, 40 + t);
+              ok = false;
+              break;
+            }
+            ++p_n[t];
+            if (n == 0)
+              FA_STAMP(0, j, t * 4 + 1);
+            // The first P*V of an item overwrites O_t: the previous item's
+            // epilogue must have read it out.
+            if (j == 0 && tile_items[t] > 0 && !mbar_wait(&sh->o_free[t], (tile_items[t] - 1) & 1, abort_flag)) {
+              fa_report(kStatusWaitTimeout, 1, 45 + t);
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+            issue_pv(t, s, j > 0);
+            if (j + 1 < w.n_blocks[t]) {
+              if (!have_k_next) {
+                if (!mbar_wait(&sh->k_full[s_next], ph_next, abort_flag)) {
+                  fa_report(kStatusWaitTimeout, 1, 50 + s_next);
+                  ok = false;
+                  break;
+                }
+                tc_fence_after_sync();
+                have_k_next = true;
+              }
+              issue_s(t, s_next);
+              if (n == 0)
+                FA_STAMP(0, j, t * 4 + 2);
+            } else {
+              umma_commit(&sh->o_full[t]);
+              ++tile_items[t];
+            }
           }
+          if (!ok)
+            break;
+          umma_commit(&sh->v_empty[s]);
+          if (have_k_next)
+            umma_commit(&sh->k_empty[s_next]);
+          if (j + 2 == n_max)
+            umma_commit(&sh->q_empty); // the last Q*K^T of the item has been issued
         }
-        if (!ok)
-          break;
-        umma_commit(&sh->v_empty[s]);
-        if (have_k_next)
-          umma_commit(&sh->k_empty[s_next]);
       }
     }
   } else if (warp >= 4) {
@@ -350,26 +429,45 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     const int t = (warp - 4) >> 2;
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
-    const int q_row = q_blk * 2 * kBlockM + t * kBlockM + row;
-    const int nb = n_blocks[t];
     const float c = p.scale_log2e;
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t s_addr = tmem_base + lane_base + static_cast<uint32_t>(t * kBlockN);
     const uint32_t o_addr = tmem_base + lane_base + static_cast<uint32_t>(2 * kBlockN + t * kD);
     constexpr bool bf16 = kBf16;
+    uint32_t s_n = 0;        // score blocks consumed so far by this tile (s_full phase)
+    uint32_t tile_items = 0; // items in which this tile had work (o_full phase)
+    bool ok = true;
+
+    for (uint32_t item_n = 0; ok; ++item_n) {
+    const int slot = item_n & 1;
+    if (!mbar_wait(&sh->item_full[slot], (item_n >> 1) & 1, abort_flag)) {
+      if (lane == 0)
+        fa_report(kStatusWaitTimeout, 2 + t, 59);
+      break;
+    }
+    const int idx = sh->item_idx[slot];
+    __syncwarp();
+    if (lane == 0)
+      mbar_arrive(&sh->item_empty[slot]);
+    if (idx >= total_items)
+      break;
+    const WorkItem w = decode_item(idx, p);
+    const int bh = w.bh;
+    const int q_row = w.q_blk * 2 * kBlockM + t * kBlockM + row;
+    const int nb = w.n_blocks[t];
     float m_used = -INFINITY; // running maximum the exponentials are taken against (raw score units)
     float l = 0.0f;           // running sum of unrounded probabilities
-    bool ok = true;
 
     for (int j = 0; j < nb; ++j) {
       if (row == 0)
         FA_STAMP(1 + t, j, 0);
-      if (!mbar_wait(&sh->s_full[t], j & 1, abort_flag)) {
+      if (!mbar_wait(&sh->s_full[t], s_n & 1, abort_flag)) {
         if (lane == 0)
           fa_report(kStatusWaitTimeout, 2 + t, 60);
         ok = false;
         break;
       }
+      ++s_n;
       tc_fence_after_sync();
       if (row == 0)
         FA_STAMP(1 + t, j, 1);
@@ -454,10 +552,12 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     }
 
     if (ok && nb > 0) {
-      if (!mbar_wait(&sh->o_full[t], 0, abort_flag)) {
+      if (!mbar_wait(&sh->o_full[t], tile_items & 1, abort_flag)) {
         if (lane == 0)
           fa_report(kStatusWaitTimeout, 2 + t, 70);
+        ok = false;
       } else {
+        ++tile_items;
         tc_fence_after_sync();
         const float inv = 1.0f / l;
         const bool live = q_row < p.seq_q;
@@ -498,8 +598,14 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         }
         if (p.lse && live)
           p.lse[static_cast<size_t>(bh) * p.seq_q + q_row] = m_used * p.scale + logf(l);
+        // O_t has been read out: the next item's first P*V may overwrite it.
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0)
+          mbar_arrive(&sh->o_free[t]);
       }
     }
+    } // work items
   }
 
   tc_fence_before_sync();
@@ -515,7 +621,6 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 
 int launch_flash_attention(const FaParams &p, const void *Q, const void *K, const void *V, int sm_count,
                            cudaStream_t stream) {
-  (void)sm_count;
   if (p.head_dim < 16 || p.head_dim > kD || p.head_dim % 16)
     return WAVE_E_UNSUPPORTED;
   CUtensorMap tq, tk, tv;
@@ -544,8 +649,30 @@ int launch_flash_attention(const FaParams &p, const void *Q, const void *K, cons
   int poly = kDefaultPoly;
   if (const char *env = getenv("WAVE_CUDA_FA_POLY"))
     poly = atoi(env);
-  dim3 grid(static_cast<unsigned>((p.seq_q + 2 * kBlockM - 1) / (2 * kBlockM)), static_cast<unsigned>(p.batch_heads));
+  // Persistent CTAs, one per SM, draw work items (256 query rows of one head)
+  // from a ticket counter.  Each launch takes the next of a ring of counters
+  // and clears it on its stream, so launches that overlap on the GPU do not
+  // share one.
+  const long long total_items =
+      static_cast<long long>(p.batch_heads) * ((p.seq_q + 2 * kBlockM - 1) / (2 * kBlockM));
+  const unsigned grid = static_cast<unsigned>(total_items < sm_count ? total_items : sm_count);
   cudaError_t err = cudaSuccess;
+  FaParams params = p;
+  {
+    static std::atomic<unsigned> next_slot{0};
+    void *base = nullptr;
+    err = cudaGetSymbolAddress(&base, g_fa_tickets);
+    if (err != cudaSuccess) {
+      set_last_error(cudaGetErrorString(err));
+      return WAVE_E_CUDA;
+    }
+    params.ticket = static_cast<unsigned int *>(base) + (next_slot.fetch_add(1) % kTicketSlots);
+    err = cudaMemsetAsync(params.ticket, 0, sizeof(unsigned int), stream);
+    if (err != cudaSuccess) {
+      set_last_error(cudaGetErrorString(err));
+      return WAVE_E_CUDA;
+    }
+  }
   bool unsafe_budget = false;
   auto launch = [&](auto kernel) {
     // The setmaxnreg arithmetic in the kernel assumes the register count the
@@ -562,7 +689,7 @@ int launch_flash_attention(const FaParams &p, const void *Q, const void *K, cons
     err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (err != cudaSuccess)
       return;
-    kernel<<<grid, kThreads, kSmemBytes, stream>>>(tq, tk, tv, p);
+    kernel<<<grid, kThreads, kSmemBytes, stream>>>(tq, tk, tv, params);
     err = cudaGetLastError();
   };
   auto dispatch = [&](auto bf16_tag) {

@@ -15,6 +15,7 @@ struct FaParams {
   float scale_log2e; // scale * log2(e): scores enter exp2 as fma(s, scale_log2e, -max)
   void *O;           // [batch_heads][seq_q][head_dim], the I/O type or f32
   float *lse;        // optional [batch_heads][seq_q] natural-log sum-exp, or null
+  unsigned int *ticket; // device counter, zero at launch: the persistent CTAs draw work items from it
 };
 
 // Builds the tensor maps and launches.  Returns a WAVE_* code (0 = ok).
