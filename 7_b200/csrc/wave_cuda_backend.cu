@@ -16,7 +16,9 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <initializer_list>
 #include <string>
+#include <vector>
 
 namespace {
 
@@ -251,6 +253,46 @@ int arena_reserve(size_t bytes, void **out) {
 }
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Streams of the host-buffer pipeline (per device, created on first use).
+struct HostPipeline {
+  cudaStream_t h2d = nullptr, compute = nullptr, d2h = nullptr;
+  int device = -1;
+};
+HostPipeline g_host_pipeline;
+HostPipeline *host_pipeline() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess)
+    return nullptr;
+  if (g_host_pipeline.device != dev) {
+    HostPipeline hp;
+    if (cudaStreamCreateWithFlags(&hp.h2d, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaStreamCreateWithFlags(&hp.compute, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaStreamCreateWithFlags(&hp.d2h, cudaStreamNonBlocking) != cudaSuccess)
+      return nullptr;
+    hp.device = dev;
+    g_host_pipeline = hp;
+  }
+  return &g_host_pipeline;
+}
+
+// Columns of C per pipeline step of the host-buffer GEMM, or 0 to copy, compute
+// and copy back in one piece: worth it only when the copies are large, and the
+// block must keep the descriptor's tiling rules valid (a multiple of
+// 16*bn*wave_n_tiles) and fill whole 256-column tiles.
+int host_pipeline_chunk(const wave_gemm_desc &d, size_t copy_bytes) {
+  if (copy_bytes < (64u << 20) || d.out_layout == WAVE_TILE_PACKED || d.ldc != 0 || d.streamk_workers > 1)
+    return 0;
+  const int unit = 16 * d.bn * d.wave_n_tiles;
+  for (int parts : {8, 6, 4, 3, 2}) {
+    if (d.N % parts)
+      continue;
+    const int chunk = d.N / parts;
+    if (chunk % unit == 0 && chunk % 256 == 0 && chunk >= 512)
+      return chunk;
+  }
+  return 0;
+}
 
 struct FnHandle {
   int kind; // 0 gemm, 1 stream-K gemm, 2 flash attention
@@ -520,6 +562,72 @@ int wave_cuda_gemm_host(const wave_gemm_desc *d, const void *A_host, const void 
   char *dev = static_cast<char *>(base);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaError_t err;
+
+  // Large problems are pipelined by column blocks of C: while block i is
+  // being computed, block i+1 of B is on its way to the device and block i-1
+  // of C on its way back (PCIe is full duplex), so the call costs about
+  // "copy A + copy B" instead of "copy A + copy B + compute + copy C".
+  const int chunk = host_pipeline_chunk(*d, b_bytes + c_bytes);
+  if (chunk > 0) {
+    HostPipeline *hp = host_pipeline();
+    if (!hp)
+      return fail(WAVE_E_CUDA, "could not create the streams of the host-call pipeline");
+    const int nchunks = d->N / chunk;
+    const size_t es = elem_size(d->out_type);
+    std::vector<cudaEvent_t> ev(2 * nchunks + 2, nullptr);
+    bool failed = false;
+    auto check = [&](cudaError_t e, const char *what) {
+      if (e != cudaSuccess && !failed) {
+        failed = true;
+        cuda_fail(e, what);
+      }
+    };
+    for (cudaEvent_t &e : ev)
+      check(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "create event");
+    cudaEvent_t ev_start = ev[2 * nchunks], ev_a = ev[2 * nchunks + 1];
+    if (!failed) {
+      check(cudaEventRecord(ev_start, s), "record");
+      for (cudaStream_t q : {hp->h2d, hp->compute, hp->d2h})
+        check(cudaStreamWaitEvent(q, ev_start, 0), "order after the caller's stream");
+      check(cudaMemcpyAsync(dev, A_host, a_bytes, cudaMemcpyHostToDevice, hp->h2d), "copy A to device");
+      check(cudaEventRecord(ev_a, hp->h2d), "record");
+      check(cudaStreamWaitEvent(hp->compute, ev_a, 0), "wait for A");
+      wave_gemm_desc sub = *d;
+      sub.N = chunk;
+      sub.streamk_workers = 1;
+      sub.ldc = d->out_layout == WAVE_ROW_MAJOR ? d->N : d->M;
+      for (int i = 0; i < nchunks && !failed; ++i) {
+        const size_t b_off = static_cast<size_t>(i) * chunk * d->K * 2;
+        check(cudaMemcpyAsync(dev + off_b + b_off, static_cast<const char *>(B_host) + b_off,
+                              static_cast<size_t>(chunk) * d->K * 2, cudaMemcpyHostToDevice, hp->h2d),
+              "copy a block of B to device");
+        check(cudaEventRecord(ev[2 * i], hp->h2d), "record");
+        check(cudaStreamWaitEvent(hp->compute, ev[2 * i], 0), "wait for a block of B");
+        const size_t c_off = d->out_layout == WAVE_ROW_MAJOR ? static_cast<size_t>(i) * chunk * es
+                                                             : static_cast<size_t>(i) * chunk * d->M * es;
+        if (!failed && wave_cuda_gemm(&sub, dev, dev + off_b + b_off, dev + off_c + c_off, nullptr, hp->compute) != WAVE_OK)
+          failed = true; // message already recorded
+        check(cudaEventRecord(ev[2 * i + 1], hp->compute), "record");
+        check(cudaStreamWaitEvent(hp->d2h, ev[2 * i + 1], 0), "wait for a block of C");
+        if (d->out_layout == WAVE_ROW_MAJOR)
+          check(cudaMemcpy2DAsync(static_cast<char *>(C_host) + c_off, static_cast<size_t>(d->N) * es,
+                                  dev + off_c + c_off, static_cast<size_t>(d->N) * es, static_cast<size_t>(chunk) * es,
+                                  static_cast<size_t>(d->M), cudaMemcpyDeviceToHost, hp->d2h),
+                "copy a block of C to host");
+        else
+          check(cudaMemcpyAsync(static_cast<char *>(C_host) + c_off, dev + off_c + c_off,
+                                static_cast<size_t>(chunk) * d->M * es, cudaMemcpyDeviceToHost, hp->d2h),
+                "copy a block of C to host");
+      }
+    }
+    for (cudaStream_t q : {hp->h2d, hp->compute, hp->d2h})
+      check(cudaStreamSynchronize(q), "synchronise the host-call pipeline");
+    for (cudaEvent_t e : ev)
+      if (e)
+        cudaEventDestroy(e);
+    return failed ? WAVE_E_CUDA : WAVE_OK;
+  }
+
   if ((err = cudaMemcpyAsync(dev, A_host, a_bytes, cudaMemcpyHostToDevice, s)) != cudaSuccess)
     return cuda_fail(err, "copy A to device");
   if ((err = cudaMemcpyAsync(dev + off_b, B_host, b_bytes, cudaMemcpyHostToDevice, s)) != cudaSuccess)
@@ -608,6 +716,68 @@ int wave_cuda_flash_attention_fwd_host(const wave_fa_desc *d, const void *Q_host
   char *dev = static_cast<char *>(base);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaError_t err;
+
+  // Large calls are pipelined by groups of heads (contiguous slabs of Q, K, V
+  // and O): the next group's inputs and the previous group's output travel
+  // while the current group is computed.
+  int parts = 0;
+  if (q_bytes + 2 * kv_bytes >= (64u << 20))
+    for (int cand : {8, 4, 2})
+      if (bh % cand == 0 && bh / cand >= 8) {
+        parts = cand;
+        break;
+      }
+  if (parts > 0) {
+    HostPipeline *hp = host_pipeline();
+    if (!hp)
+      return fail(WAVE_E_CUDA, "could not create the streams of the host-call pipeline");
+    const size_t group = bh / parts;
+    const size_t q_step = q_bytes / parts, kv_step = kv_bytes / parts, o_step = o_bytes / parts;
+    std::vector<cudaEvent_t> ev(2 * parts + 1, nullptr);
+    bool failed = false;
+    auto check = [&](cudaError_t e, const char *what) {
+      if (e != cudaSuccess && !failed) {
+        failed = true;
+        cuda_fail(e, what);
+      }
+    };
+    for (cudaEvent_t &e : ev)
+      check(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "create event");
+    if (!failed) {
+      check(cudaEventRecord(ev[2 * parts], s), "record");
+      for (cudaStream_t q : {hp->h2d, hp->compute, hp->d2h})
+        check(cudaStreamWaitEvent(q, ev[2 * parts], 0), "order after the caller's stream");
+      wave_fa_desc sub = *d;
+      sub.batch = 1;
+      sub.heads = static_cast<int>(group);
+      for (int i = 0; i < parts && !failed; ++i) {
+        const char *qh = static_cast<const char *>(Q_host) + i * q_step;
+        const char *kh = static_cast<const char *>(K_host) + i * kv_step;
+        const char *vh = static_cast<const char *>(V_host) + i * kv_step;
+        check(cudaMemcpyAsync(dev + i * q_step, qh, q_step, cudaMemcpyHostToDevice, hp->h2d), "copy Q to device");
+        check(cudaMemcpyAsync(dev + off_k + i * kv_step, kh, kv_step, cudaMemcpyHostToDevice, hp->h2d), "copy K to device");
+        check(cudaMemcpyAsync(dev + off_v + i * kv_step, vh, kv_step, cudaMemcpyHostToDevice, hp->h2d), "copy V to device");
+        check(cudaEventRecord(ev[2 * i], hp->h2d), "record");
+        check(cudaStreamWaitEvent(hp->compute, ev[2 * i], 0), "wait for a group of heads");
+        if (!failed && wave_cuda_flash_attention_fwd(&sub, dev + i * q_step, dev + off_k + i * kv_step,
+                                                     dev + off_v + i * kv_step, dev + off_o + i * o_step, nullptr,
+                                                     hp->compute) != WAVE_OK)
+          failed = true; // message already recorded
+        check(cudaEventRecord(ev[2 * i + 1], hp->compute), "record");
+        check(cudaStreamWaitEvent(hp->d2h, ev[2 * i + 1], 0), "wait for a group's output");
+        check(cudaMemcpyAsync(static_cast<char *>(O_host) + i * o_step, dev + off_o + i * o_step, o_step,
+                              cudaMemcpyDeviceToHost, hp->d2h),
+              "copy O to host");
+      }
+    }
+    for (cudaStream_t q : {hp->h2d, hp->compute, hp->d2h})
+      check(cudaStreamSynchronize(q), "synchronise the host-call pipeline");
+    for (cudaEvent_t e : ev)
+      if (e)
+        cudaEventDestroy(e);
+    return failed ? WAVE_E_CUDA : WAVE_OK;
+  }
+
   if ((err = cudaMemcpyAsync(dev, Q_host, q_bytes, cudaMemcpyHostToDevice, s)) != cudaSuccess)
     return cuda_fail(err, "copy Q to device");
   if ((err = cudaMemcpyAsync(dev + off_k, K_host, kv_bytes, cudaMemcpyHostToDevice, s)) != cudaSuccess)

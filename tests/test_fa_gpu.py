@@ -161,3 +161,19 @@ def test_toy_kernel_surface_matches_reference_golden(cuda, wc, oracle):
         got = run_fa(cuda, wc, q, k, v, "f16", 1, 1, False, scale=float(np.log(2.0)), out_f32=True)
         want = np.asarray(entry["out"], np.float64).reshape(got.shape)
         assert np.abs(got - want).max() <= 3.0e-3, c
+
+
+def test_host_buffer_call_pipelined_by_head_groups(cuda, wc, oracle):
+    """Large host-buffer calls run group of heads by group of heads, copies
+    overlapped with compute; the result must equal the one-piece call's."""
+    import importlib
+    wa = importlib.import_module("7_b200.wave_attention")
+    t = oracle.BF16
+    BH, S = 64, 1024  # 3 x 16 MiB of inputs: above the pipelining threshold
+    q, k, v = normal_qkv(oracle, BH, S, S, 128, t, seed=31)
+    got = oracle.from_bits(wa.run_attention_host(q, k, v, 4, 16, causal=True), t)
+    hs, rs = oracle.fa_sample_heads(BH), oracle.fa_sample_rows(S)
+    want = oracle.fa_ref(q, k, v, t, 1.0 / np.sqrt(128.0), causal=True, heads=hs, rows=rs)
+    check(got[np.ix_(hs, rs)], want, "host pipelined")
+    dev = run_fa(cuda, wc, q, k, v, "bf16", 4, 16, True)
+    assert np.array_equal(got, dev)

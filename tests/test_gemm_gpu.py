@@ -225,6 +225,23 @@ def test_host_buffer_call(cuda, wc, oracle):
     assert np.array_equal(c, expected(oracle, a, b, "bf16", "f32"))
 
 
+@pytest.mark.parametrize("layout,out_name", [("row-major", "f32"), ("column-major", "bf16")])
+def test_host_buffer_call_pipelined(cuda, wc, oracle, layout, out_name):
+    """Large host-buffer calls are pipelined by column blocks of C (B blocks in,
+    C blocks out, overlapped with compute); the result must not depend on it."""
+    M, N, K = 2048, 8192, 2048 if out_name == "f32" else 4096
+    a, b = lcg_inputs(oracle, M, N, K, "bf16", seed=17)
+    dt = np.float32 if out_name == "f32" else np.uint16
+    c = np.zeros(M * N, dt)
+    desc = wc.gemm_desc(M, N, K, bm=4, bn=4, wave_m_tiles=2, wave_n_tiles=4, in_type=wc.BF16,
+                        out_type=wc.TYPE_BY_NAME[out_name], out_layout=wc.LAYOUT_BY_NAME[layout])
+    wc.gemm_host(desc, a.ctypes.data, b.ctypes.data, c.ctypes.data)
+    wc.check_device_status()
+    got = c if out_name == "f32" else oracle.from_bits(c, oracle.BF16)
+    got = got.reshape(M, N) if layout == "row-major" else got.reshape(N, M).T
+    assert np.array_equal(got, expected(oracle, a, b, "bf16", out_name))
+
+
 def test_name_based_launch_facade(cuda, wc, oracle):
     """Same call shape as the reference runner: look a kernel up by name, then
     launch with an array of pointers to the argument values
