@@ -1,12 +1,15 @@
 // CTA-pair variant of the tiled f16/bf16 GEMM for large problems: two CTAs of a
-// 2-CTA cluster compute one 256 x 256 output tile with tcgen05.mma
-// cta_group::2 (UMMA 256 x 256 x 16).  Each CTA loads its own 128 rows of A and
-// its own 128 of the tile's 256 B rows (no multicast: every load targets the
-// loading CTA's shared memory) and receives its 128 accumulator rows in its
-// own TMEM; the even CTA issues the MMAs, which read both CTAs' shared memory.
-// Per CTA a K step moves 32 KB instead of the one-CTA kernel's 48 KB for the
-// same 128 x 256 outputs, which both deepens the ring (6 stages) and cuts
-// shared-memory and L2 traffic per flop.
+// 2-CTA cluster compute one 256 x PN output tile (PN = 256 or 128) with
+// tcgen05.mma cta_group::2 (UMMA 256 x PN x 16).  Each CTA loads its own 128
+// rows of A and its own half of the tile's PN B rows (no multicast: every load
+// targets the loading CTA's shared memory) and receives its 128 accumulator
+// rows in its own TMEM; the even CTA issues the MMAs, which read both CTAs'
+// shared memory.  With PN = 256 a K step moves 32 KB per CTA instead of the
+// one-CTA kernel's 48 KB for the same 128 x 256 outputs, which both deepens the
+// ring (6 stages) and cuts shared-memory and L2 traffic per flop.  PN = 128
+// (24 KB per step, 8 stages) halves the tile; its 256 x 128 x 16 MMAs reach
+// only 0.69 of the wide tile's rate (1035 against 1507 TFLOP/s at 8192^3), so
+// the host never picks it by itself.
 //
 // Same numerics and operator surface as gemm_sm100.cu (the reference's
 // `wmma_f16_matmul_tiled`, python/mlir/dialects/wave_matmul.py:11163-11241).
@@ -29,23 +32,25 @@ using namespace gemm_detail;
 
 constexpr int kRows = 128;     // rows of A / of the accumulator per CTA
 constexpr int kPairM = 256;    // UMMA M across the pair
-constexpr int kPairN = 256;    // UMMA N
-constexpr int kBRows = 128;    // B rows held by one CTA
 constexpr int kBK = 64;
-#ifndef WAVE_PAIR_STAGES
-#define WAVE_PAIR_STAGES 6
-#endif
-constexpr int kStages = WAVE_PAIR_STAGES;
 constexpr int kABytes = kRows * kBK * 2;
-constexpr int kBBytes = kBRows * kBK * 2;
-constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kThreads = 192;
-constexpr int kTmemCols = 512; // two 256-column accumulators
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+constexpr int kMaxStages = 8;
+
+// Per tile width PN: B rows held by one CTA, ring depth (192 KB of stages) and
+// TMEM columns (two PN-column accumulators).
+template <int PN> struct PairCfg {
+  static constexpr int kBRows = PN / 2;
+  static constexpr int kBBytes = kBRows * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = PN == 256 ? 6 : 8;
+  static constexpr int kTmemCols = 2 * PN;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+};
 
 struct PairShared {
-  uint64_t full[kStages];
-  uint64_t empty[kStages];
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
   uint64_t tfull[2];
   uint64_t tempty[2];
   uint32_t tmem_base;
@@ -60,11 +65,17 @@ __device__ __forceinline__ void pair_report(int code, int role, int detail) {
   }
 }
 
-template <int OUT>
+template <int OUT, int PN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const GemmParams p) {
+                 const __grid_constant__ CUtensorMap tmap_b_half, const GemmParams p) {
   using T = typename OutT<OUT>::type;
+  using Cfg = PairCfg<PN>;
+  constexpr int kPairN = PN;
+  constexpr int kBRows = Cfg::kBRows;
+  constexpr int kStageBytes = Cfg::kStageBytes;
+  constexpr int kStages = Cfg::kStages;
+  constexpr int kTmemCols = Cfg::kTmemCols;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *tiles = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   PairShared *sh = reinterpret_cast<PairShared *>(tiles + kStages * kStageBytes);
@@ -76,6 +87,23 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const bool leader = rank == 0;
   const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
+  // Work items: tiles [0, split_from) whole, then every later tile as two
+  // half-width items (columns [0,128) and [128,256) of the tile), so that a
+  // sparsely filled last round of tiles spreads over twice as many CTA pairs.
+  const int split_from = PN == 256 ? p.split_from : p.num_tiles;
+  const int num_items = split_from + 2 * (p.num_tiles - split_from);
+  auto decode = [&](int item, int &mb, int &nb, int &n_off, int &width) {
+    int tile = item;
+    n_off = 0;
+    width = PN;
+    if (item >= split_from) {
+      const int r = item - split_from;
+      tile = split_from + (r >> 1);
+      n_off = (r & 1) * (PN / 2);
+      width = PN / 2;
+    }
+    tile_coords(tile, p.num_m_blocks, p.num_n_blocks, p.group_m, mb, nb);
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -108,11 +136,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = pair_id; tile < p.num_tiles && ok; tile += num_pairs) {
-        int mb, nb;
-        tile_coords(tile, p.num_m_blocks, p.num_n_blocks, p.group_m, mb, nb);
+      for (int item = pair_id; item < num_items && ok; item += num_pairs) {
+        int mb, nb, n_off, width;
+        decode(item, mb, nb, n_off, width);
+        const bool half = width != PN;
         const int m0 = mb * kPairM + static_cast<int>(rank) * kRows;
-        const int n0 = nb * kPairN + static_cast<int>(rank) * kBRows;
+        const int n0 = nb * kPairN + n_off + static_cast<int>(rank) * (width / 2);
+        const uint32_t stage_tx = 2 * (kABytes + (width / 2) * kBK * 2);
         for (int kb = 0; kb < p.k_iters; ++kb) {
           if (!mbar_wait(&sh->empty[stage], phase ^ 1, abort_flag)) {
             pair_report(kStatusWaitTimeout, 0, stage);
@@ -122,9 +152,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           uint8_t *a_dst = tiles + stage * kStageBytes;
           uint8_t *b_dst = a_dst + kABytes;
           if (leader)
-            mbar_arrive_expect_tx(&sh->full[stage], 2 * kStageBytes);
+            mbar_arrive_expect_tx(&sh->full[stage], stage_tx);
           tma_load_2d_pair(a_dst, &tmap_a, &sh->full[stage], kb * kBK, m0);
-          tma_load_2d_pair(b_dst, &tmap_b, &sh->full[stage], kb * kBK, n0);
+          tma_load_2d_pair(b_dst, half ? &tmap_b_half : &tmap_b, &sh->full[stage], kb * kBK, n0);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1;
@@ -137,13 +167,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   } else if (warp == 1) {
     // ------------------------------------------- UMMA issuer (leader only)
     if (lane == 0 && leader) {
-      const uint32_t idesc = umma_idesc_f16(kPairM, kPairN, p.in_type == WAVE_GEMM_IN_BF16 ? 1 : 0);
+      const uint32_t idesc_whole = umma_idesc_f16(kPairM, kPairN, p.in_type == WAVE_GEMM_IN_BF16 ? 1 : 0);
+      const uint32_t idesc_half = umma_idesc_f16(kPairM, kPairN / 2, p.in_type == WAVE_GEMM_IN_BF16 ? 1 : 0);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = pair_id; tile < p.num_tiles && ok; tile += num_pairs) {
+      for (int item = pair_id; item < num_items && ok; item += num_pairs) {
+        const uint32_t idesc = item >= split_from ? idesc_half : idesc_whole;
         if (!mbar_wait(&sh->tempty[acc], acc_phase ^ 1, abort_flag)) {
           pair_report(kStatusWaitTimeout, 1, 100 + acc);
           break;
@@ -186,9 +218,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     int acc = 0;
     uint32_t acc_phase = 0;
     const uint32_t tempty_leader[2] = {map_to_cta(&sh->tempty[0], 0), map_to_cta(&sh->tempty[1], 0)};
-    for (int tile = pair_id; tile < p.num_tiles; tile += num_pairs) {
-      int mb, nb;
-      tile_coords(tile, p.num_m_blocks, p.num_n_blocks, p.group_m, mb, nb);
+    for (int item = pair_id; item < num_items; item += num_pairs) {
+      int mb, nb, n_off, width;
+      decode(item, mb, nb, n_off, width);
       if (!mbar_wait(&sh->tfull[acc], acc_phase, abort_flag)) {
         if (lane == 0)
           pair_report(kStatusWaitTimeout, 2, 200 + acc);
@@ -199,7 +231,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * kPairN);
       const int m = mb * kPairM + static_cast<int>(rank) * kRows + row_in_tile;
 #pragma unroll 1
-      for (int c = 0; c < kPairN; c += 32) {
+      for (int c = 0; c < width; c += 32) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(taddr + c, r);
         tmem_ld_wait();
@@ -207,7 +239,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
         for (int j = 0; j < 32; ++j)
           v[j] = __uint_as_float(r[j]);
-        store_row_chunk<T, 32>(p, m, nb * kPairN + c, v);
+        store_row_chunk<T, 32>(p, m, nb * kPairN + n_off + c, v);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -233,34 +265,46 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   }
 }
 
-template <int OUT>
-cudaError_t launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const GemmParams &p, int grid,
-                        cudaStream_t stream) {
-  cudaError_t err =
-      cudaFuncSetAttribute(gemm_pair_kernel<OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+template <int OUT, int PN>
+cudaError_t launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tbh, const GemmParams &p,
+                        int grid, cudaStream_t stream) {
+  constexpr int smem = PairCfg<PN>::kSmemBytes;
+  cudaError_t err = cudaFuncSetAttribute(gemm_pair_kernel<OUT, PN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (err != cudaSuccess)
     return err;
-  gemm_pair_kernel<OUT><<<grid, kThreads, kSmemBytes, stream>>>(ta, tb, p);
+  gemm_pair_kernel<OUT, PN><<<grid, kThreads, smem, stream>>>(ta, tb, tbh, p);
   return cudaGetLastError();
+}
+
+template <int PN>
+cudaError_t launch_pair_out(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tbh, const GemmParams &p,
+                            int grid, cudaStream_t stream) {
+  switch (p.out_type) {
+  case WAVE_GEMM_OUT_F32:
+    return launch_pair<WAVE_GEMM_OUT_F32, PN>(ta, tb, tbh, p, grid, stream);
+  case WAVE_GEMM_OUT_F16:
+    return launch_pair<WAVE_GEMM_OUT_F16, PN>(ta, tb, tbh, p, grid, stream);
+  case WAVE_GEMM_OUT_BF16:
+    return launch_pair<WAVE_GEMM_OUT_BF16, PN>(ta, tb, tbh, p, grid, stream);
+  }
+  return cudaErrorInvalidValue;
 }
 
 } // namespace
 
 int gemm_pair_tile_m() { return kPairM; }
-int gemm_pair_tile_n() { return kPairN; }
+int gemm_pair_tile_n() { return 256; }
 int gemm_pair_box_rows() { return kRows; }
 
-// `grid` must be even: consecutive CTAs form the pairs.
-cudaError_t launch_gemm_pair(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, const GemmParams &p, int grid,
-                             cudaStream_t stream) {
-  switch (p.out_type) {
-  case WAVE_GEMM_OUT_F32:
-    return launch_pair<WAVE_GEMM_OUT_F32>(tmap_a, tmap_b, p, grid, stream);
-  case WAVE_GEMM_OUT_F16:
-    return launch_pair<WAVE_GEMM_OUT_F16>(tmap_a, tmap_b, p, grid, stream);
-  case WAVE_GEMM_OUT_BF16:
-    return launch_pair<WAVE_GEMM_OUT_BF16>(tmap_a, tmap_b, p, grid, stream);
-  }
+// `grid` must be even: consecutive CTAs form the pairs.  `tile_n` is 256 or
+// 128; the tensor map of B must have a box of tile_n / 2 rows, `tmap_b_half`
+// (read only when tile_n is 256 and p.split_from < p.num_tiles) one of 64 rows.
+cudaError_t launch_gemm_pair(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, const CUtensorMap &tmap_b_half,
+                             const GemmParams &p, int tile_n, int grid, cudaStream_t stream) {
+  if (tile_n == 256)
+    return launch_pair_out<256>(tmap_a, tmap_b, tmap_b_half, p, grid, stream);
+  if (tile_n == 128)
+    return launch_pair_out<128>(tmap_a, tmap_b, tmap_b_half, p, grid, stream);
   return cudaErrorInvalidValue;
 }
 

@@ -21,6 +21,7 @@ struct GemmParams {
   int in_type, out_type;
   int num_m_blocks, num_n_blocks, num_tiles, k_iters;
   int group_m;
+  int split_from;      // CTA-pair kernel: tiles [split_from, num_tiles) run as two half-width work items each
   int dp_tiles;        // tiles [0, dp_tiles) are whole tiles dealt round-robin over the grid
   int streamk_workers; // >0: tiles [dp_tiles, num_tiles) are split Stream-K style over that many workers (= grid)
   float *scratch;      // Stream-K: [workers][2][128 x tile_n] f32 partial tiles
@@ -35,12 +36,13 @@ cudaError_t launch_gemm(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, co
                         int grid, cudaStream_t stream);
 cudaError_t gemm_read_status(int out[4], bool clear);
 
-// CTA-pair kernel (256 x 256 tiles, tcgen05 cta_group::2); data-parallel only.
+// CTA-pair kernel (256 x 256 or 256 x 128 tiles, tcgen05 cta_group::2);
+// data-parallel only.  gemm_pair_tile_n() is the wide tile.
 int gemm_pair_tile_m();
 int gemm_pair_tile_n();
 int gemm_pair_box_rows();
-cudaError_t launch_gemm_pair(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, const GemmParams &p, int grid,
-                             cudaStream_t stream);
+cudaError_t launch_gemm_pair(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, const CUtensorMap &tmap_b_half,
+                             const GemmParams &p, int tile_n, int grid, cudaStream_t stream);
 cudaError_t gemm_pair_read_status(int out[4], bool clear);
 
 } // namespace wave

@@ -115,7 +115,7 @@ int elem_size(int type) { return type == WAVE_F32 ? 4 : 2; }
 
 // ---------------------------------------------------------------- GEMM plan
 struct GemmPlan {
-  bool pair;          // CTA-pair kernel: 256 x 256 tiles, two CTAs per tile
+  bool pair;          // CTA-pair kernel: 256 x 256 or 256 x 128 tiles, two CTAs per tile
   int tile_m;         // kernel-space tile rows
   bool swapped;       // kernel computes C^T = B * A^T (skinny M)
   int Mk, Nk;         // kernel-space extents
@@ -124,8 +124,27 @@ struct GemmPlan {
   int grid;
   int streamk_workers; // 0 = data-parallel
   int dp_tiles;        // whole tiles dealt round-robin before the Stream-K part (all of them if no Stream-K)
+  int split_from;      // CTA-pair kernel: tiles from this one on run as two half-width work items
   size_t scratch_bytes, counter_bytes;
 };
+
+// Steady-state rate of the one-CTA kernel relative to the 256 x 256 pair tile
+// (8192^3 bf16, measured: 1381 against 1507 TFLOP/s).
+constexpr double kSingleRate = 0.915;
+
+// Duration of a round of half-width (256 x 128) work items of the CTA-pair
+// kernel relative to a round of whole tiles: half the work at 0.69 of the rate.
+constexpr double kHalfItemCost = 0.72;
+
+// Whether the last, partly filled round of `tail` whole tiles on `pairs` CTA
+// pairs is better run as 2 * tail half-width items: only if those still fit
+// one round.  WAVE_CUDA_GEMM_SPLIT_TAIL=0 turns the split off.
+bool pair_tail_splits(long long tail, long long pairs) {
+  const char *env = getenv("WAVE_CUDA_GEMM_SPLIT_TAIL");
+  if (env && strcmp(env, "0") == 0)
+    return false;
+  return tail > 0 && 2 * tail <= pairs;
+}
 
 int snap_tile_n(int want) {
   const int options[5] = {16, 32, 64, 128, 256};
@@ -160,17 +179,37 @@ int make_plan(const wave_gemm_desc &d, int sms, bool have_workspace, GemmPlan *p
   const char *force = getenv("WAVE_CUDA_GEMM_KERNEL");
   if (force && strcmp(force, "single") == 0)
     p.pair = false;
-  if (p.pair && sms > 0 && !(force && strcmp(force, "pair") == 0)) {
-    // With few 256 x 256 tiles per CTA pair the last, partly filled round of
-    // tiles costs more than the pair kernel saves; the one-CTA kernel's
-    // 128 x 256 tiles fill the machine better there (measured at 4096^3).
-    const long long pair_tiles = static_cast<long long>((d.M + 255) / 256) * ((d.N + 255) / 256);
-    if (pair_tiles < 6ll * (sms / 2))
-      p.pair = false;
-  }
   if (p.pair) {
     p.tile_m = wave::gemm_pair_tile_m();
     p.tile_n = wave::gemm_pair_tile_n();
+    // WAVE_CUDA_GEMM_KERNEL=pair128 forces the narrow pair tile (never chosen
+    // automatically: its 256 x 128 x 16 MMAs run at 0.69 of the wide tile's rate).
+    if (force && strcmp(force, "pair128") == 0)
+      p.tile_n = 128;
+    else if (sms > 0 && !(force && strcmp(force, "pair") == 0)) {
+      // Choose between 256 x 256 pair tiles and the one-CTA kernel's 128 x 256
+      // tiles by how well each fills its last round of tiles, weighted by the
+      // one-CTA kernel's measured steady-state rate relative to the pair's.
+      const long long wide = static_cast<long long>((d.M + 255) / 256) * ((d.N + 255) / 256);
+      const long long single = static_cast<long long>((d.M + 127) / 128) * ((d.N + 255) / 256);
+      const long long pairs = sms / 2;
+      const long long r_wide = (wide + pairs - 1) / pairs, r_single = (single + sms - 1) / sms;
+      const long long tail = wide % pairs;
+      // a last round that fills at most half of the pairs runs as half-width items (see pair_tail_splits)
+      const double rounds = static_cast<double>(wide / pairs) +
+                            (tail == 0 ? 0.0 : (pair_tail_splits(tail, pairs) ? kHalfItemCost : 1.0));
+      const double f_wide = static_cast<double>(wide) / (rounds * static_cast<double>(pairs));
+      const double f_single = kSingleRate * static_cast<double>(single) / static_cast<double>(r_single * sms);
+      // A single round is all prologue and epilogue: the smaller tile's shorter tail wins there.
+      if (f_single > f_wide || (r_wide == 1 && r_single == 1))
+        p.pair = false;
+    }
+  }
+  if (!p.pair) {
+    p.tile_m = tile_m;
+    p.tile_n = snap_tile_n(want);
+    if (p.tile_n > cap)
+      p.tile_n = cap;
   }
   p.num_m = (p.Mk + p.tile_m - 1) / p.tile_m;
   p.num_n = (p.Nk + p.tile_n - 1) / p.tile_n;
@@ -208,6 +247,7 @@ int make_plan(const wave_gemm_desc &d, int sms, bool have_workspace, GemmPlan *p
                   workers, sk_iters);
     p.streamk_workers = workers;
     p.dp_tiles = static_cast<int>(dp_tiles);
+    p.split_from = static_cast<int>(tiles);
     p.grid = workers;
     p.scratch_bytes = static_cast<size_t>(workers) * 2 * tile_m * p.tile_n * sizeof(float);
     p.counter_bytes = static_cast<size_t>(tiles - dp_tiles) * sizeof(int);
@@ -215,8 +255,14 @@ int make_plan(const wave_gemm_desc &d, int sms, bool have_workspace, GemmPlan *p
     p.streamk_workers = 0;
     p.dp_tiles = static_cast<int>(tiles);
     p.grid = sms > 0 ? static_cast<int>(tiles < sms ? tiles : sms) : static_cast<int>(tiles);
+    p.split_from = static_cast<int>(tiles);
     if (p.pair) {
-      const long long pairs = sms > 0 ? (tiles < sms / 2 ? tiles : sms / 2) : tiles;
+      long long items = tiles;
+      if (sms > 0 && p.tile_n == wave::gemm_pair_tile_n() && pair_tail_splits(tiles % (sms / 2), sms / 2)) {
+        p.split_from = static_cast<int>(tiles - tiles % (sms / 2));
+        items += tiles % (sms / 2);
+      }
+      const long long pairs = sms > 0 ? (items < sms / 2 ? items : sms / 2) : items;
       p.grid = static_cast<int>(2 * pairs);
     }
   }
@@ -469,7 +515,7 @@ int wave_cuda_gemm(const wave_gemm_desc *d, const void *A, const void *B, void *
   const int tile_m = wave::gemm_tile_m(), tile_k = wave::gemm_tile_k();
   const void *Ak = plan.swapped ? B : A;
   const void *Bk = plan.swapped ? A : B;
-  CUtensorMap ta, tb;
+  CUtensorMap ta, tb, tbh;
   const int bf16 = d->in_type == WAVE_BF16;
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(d->K), static_cast<uint64_t>(plan.Mk)};
@@ -483,9 +529,15 @@ int wave_cuda_gemm(const wave_gemm_desc *d, const void *A, const void *B, void *
     const uint64_t dims[2] = {static_cast<uint64_t>(d->K), static_cast<uint64_t>(plan.Nk)};
     const uint64_t strides[1] = {static_cast<uint64_t>(d->K) * 2};
     const uint32_t box[2] = {static_cast<uint32_t>(tile_k),
-                             static_cast<uint32_t>(plan.pair ? wave::gemm_pair_box_rows() : plan.tile_n)};
+                             static_cast<uint32_t>(plan.pair ? plan.tile_n / 2 : plan.tile_n)};
     if ((rc = wave::make_tensor_map_16bit(&tb, bf16, Bk, 2, dims, strides, box)) != WAVE_OK)
       return rc;
+    tbh = tb;
+    if (plan.pair && plan.split_from < plan.num_m * plan.num_n) {
+      const uint32_t half_box[2] = {static_cast<uint32_t>(tile_k), static_cast<uint32_t>(plan.tile_n / 4)};
+      if ((rc = wave::make_tensor_map_16bit(&tbh, bf16, Bk, 2, dims, strides, half_box)) != WAVE_OK)
+        return rc;
+    }
   }
 
   wave::GemmParams p{};
@@ -506,6 +558,7 @@ int wave_cuda_gemm(const wave_gemm_desc *d, const void *A, const void *B, void *
   p.num_n_blocks = plan.num_n;
   p.num_tiles = plan.num_m * plan.num_n;
   p.k_iters = plan.k_iters;
+  p.split_from = plan.split_from;
   // The descriptor's cta_group_m counts the reference's (smaller) workgroup
   // tiles; keep the same number of rows per group, at least one 128-row block.
   {
@@ -532,7 +585,7 @@ int wave_cuda_gemm(const wave_gemm_desc *d, const void *A, const void *B, void *
   p.scratch = static_cast<float *>(workspace);
   p.counters = workspace ? reinterpret_cast<int *>(static_cast<char *>(workspace) + plan.scratch_bytes) : nullptr;
 
-  cudaError_t err = plan.pair ? wave::launch_gemm_pair(ta, tb, p, plan.grid, static_cast<cudaStream_t>(stream))
+  cudaError_t err = plan.pair ? wave::launch_gemm_pair(ta, tb, tbh, p, plan.tile_n, plan.grid, static_cast<cudaStream_t>(stream))
                               : wave::launch_gemm(ta, tb, p, plan.tile_n, plan.grid, static_cast<cudaStream_t>(stream));
   if (err != cudaSuccess)
     return cuda_fail(err, "gemm launch");

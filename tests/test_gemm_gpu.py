@@ -17,9 +17,10 @@ pytestmark = pytest.mark.gpu
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
 
 
-def run_gemm(torch, wc, a_bits, b_bits, in_name, out_name, layout="row-major", streamk=1, ldc=0, **knobs):
+def run_gemm(torch, wc, a_bits, b_bits, in_name, out_name, layout="row-major", streamk=1, ldc=0, kernel="pair",
+             **knobs):
     # small shapes must still exercise the CTA-pair kernel when their knobs ask for 256 x 256 tiles
-    os.environ["WAVE_CUDA_GEMM_KERNEL"] = "pair"
+    os.environ["WAVE_CUDA_GEMM_KERNEL"] = kernel
     try:
         return _run_gemm(torch, wc, a_bits, b_bits, in_name, out_name, layout, streamk, ldc, **knobs)
     finally:
@@ -163,9 +164,53 @@ def test_pair_kernel_is_selected_for_large_tiles(cuda, wc):
     assert (plan["tile_m"], plan["tile_n"]) == (256, 256) and plan["grid"] % 2 == 0
     plan = wc.gemm_plan(wc.gemm_desc(8192, 8192, 8192, bm=4, bn=4, wave_m_tiles=2, wave_n_tiles=4, in_type=wc.BF16))
     assert (plan["tile_m"], plan["tile_n"]) == (128, 256)
-    # too few 256 x 256 tiles to fill the CTA pairs several times over: one-CTA kernel
+    # equal fill of the last round either way (3.46 rounds): the pair kernel's higher rate wins
     plan = wc.gemm_plan(wc.gemm_desc(4096, 4096, 4096, bm=4, bn=4, wave_m_tiles=4, wave_n_tiles=4))
+    assert (plan["tile_m"], plan["tile_n"]) == (256, 256) and plan["grid"] % 2 == 0
+    # one round of tiles either way: the one-CTA kernel
+    plan = wc.gemm_plan(wc.gemm_desc(2048, 2048, 4096, bm=4, bn=4, wave_m_tiles=4, wave_n_tiles=4))
     assert (plan["tile_m"], plan["tile_n"]) == (128, 256)
+
+
+@pytest.mark.parametrize("M,N,K,in_name,out_name,layout", [
+    (256, 256, 64, "f16", "f32", "row-major"),
+    (512, 768, 256, "bf16", "bf16", "row-major"),
+    (1024, 1152, 1040, "bf16", "f32", "column-major"),
+    (400, 272, 208, "f16", "f16", "row-major"),
+    (2304, 2048, 512, "f16", "f32", "row-major"),
+])
+def test_narrow_pair_tile_bit_exact(cuda, wc, oracle, M, N, K, in_name, out_name, layout):
+    """The 256 x 128 tile of the CTA-pair kernel (only on request: WAVE_CUDA_GEMM_KERNEL=pair128)."""
+    a, b = lcg_inputs(oracle, M, N, K, in_name, seed=M + N + K)
+    knobs = dict(bm=4, bn=4, wave_m_tiles=4, wave_n_tiles=4) if M % 256 == 0 and N % 256 == 0 else \
+        dict(bm=1, bn=1, wave_m_tiles=M // 16, wave_n_tiles=N // 16)
+    if N == 1152:  # ragged against the wide tile, whole against the narrow one
+        knobs = dict(bm=1, bn=1, wave_m_tiles=16, wave_n_tiles=72)
+    got, _ = run_gemm(cuda, wc, a, b, in_name, out_name, layout, kernel="pair128", **knobs)
+    want = expected(oracle, a, b, in_name, out_name)
+    assert np.array_equal(got, want), f"max abs diff {np.nanmax(np.abs(got - want))}"
+
+
+@pytest.mark.parametrize("split", ["1", "0"])
+@pytest.mark.parametrize("M,N,K,layout", [
+    (2560, 2560, 128, "row-major"),     # 100 tiles on 74 CTA pairs: the last 26 run as 52 half-width items
+    (768, 1024, 192, "column-major"),   # 12 tiles: all of them split
+    (2304, 2048, 64, "row-major"),      # 72 tiles: one well-filled round, nothing to split
+    (2576, 2448, 80, "row-major"),      # ragged edges in both directions on split tiles
+])
+def test_pair_kernel_split_tail(cuda, wc, oracle, M, N, K, layout, split):
+    """A sparsely filled last round of 256 x 256 tiles runs as half-width work
+    items; the result must be the oracle's bits with the split on and off."""
+    a, b = lcg_inputs(oracle, M, N, K, "bf16", seed=M + K)
+    knobs = dict(bm=4, bn=4, wave_m_tiles=4, wave_n_tiles=4) if M % 256 == 0 and N % 256 == 0 else \
+        dict(bm=1, bn=1, wave_m_tiles=23 if M == 2576 else 16, wave_n_tiles=17 if N == 2448 else 16)
+    os.environ["WAVE_CUDA_GEMM_SPLIT_TAIL"] = split
+    try:
+        got, _ = run_gemm(cuda, wc, a, b, "bf16", "f32", layout, **knobs)
+    finally:
+        del os.environ["WAVE_CUDA_GEMM_SPLIT_TAIL"]
+    want = expected(oracle, a, b, "bf16", "f32")
+    assert np.array_equal(got, want), f"max abs diff {np.nanmax(np.abs(got - want))}"
 
 
 def test_pair_kernel_random_inputs(cuda, wc, oracle):
