@@ -47,16 +47,27 @@ __device__ unsigned int g_fa_tickets[kTicketSlots];
 // [role][block][stamp].  Role 0 = UMMA thread, 1 = softmax tile 0 (row 0),
 // 2 = softmax tile 1 (row 0).
 #ifdef WAVE_FA_TRACE
-__device__ long long g_fa_trace[3][64][8];
+__device__ long long g_fa_trace[3][64][16];
+#ifdef WAVE_FA_TRACE_CLOCK_ONLY // only the start/end clock probe
+#define FA_STAMP(role, blk, idx)
+#else
+// Stamps go to shared memory (a 32-bit clock read and one shared store) and
+// are copied out when the CTA ends.
 #define FA_STAMP(role, blk, idx)                                                                   \
   do {                                                                                             \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && (blk) < 64)                                          \
-      g_fa_trace[role][blk][idx] = clock64();                                                      \
+    if (blockIdx.x == 0 && (blk) < 64) {                                                           \
+      unsigned int fa_stamp_clk;                                                                   \
+      asm volatile("mov.u32 %0, %%clock;" : "=r"(fa_stamp_clk));                                   \
+      fa_trace_smem[((role)*64 + (blk)) * 16 + (idx)] = fa_stamp_clk;                              \
+    }                                                                                              \
   } while (0)
+#endif
+#define FA_TRACE_SMEM_BYTES (3 * 64 * 16 * 4)
 #else
 #define FA_STAMP(role, blk, idx)                                                                   \
   do {                                                                                             \
   } while (0)
+#define FA_TRACE_SMEM_BYTES 0
 #endif
 
 namespace {
@@ -68,7 +79,7 @@ constexpr int kThreads = 384;            // warpgroup 0: loader + UMMA warps; wa
 constexpr int kSubTile = 128 * 64 * 2;  // [128 rows][64 elements], 128-byte swizzled rows
 constexpr int kTile = 2 * kSubTile;     // 128 x 128 16-bit elements
 constexpr int kSmemTiles = 2 * kTile /*Q*/ + 2 * kTile /*K ring*/ + 2 * kTile /*V ring*/;
-constexpr int kSmemBytes = kSmemTiles + 1024 + 256;
+constexpr int kSmemBytes = kSmemTiles + 1024 + 256 + FA_TRACE_SMEM_BYTES;
 constexpr int kTmemCols = 512;
 // Of every 8 column pairs, how many evaluate 2^x with exp2_poly2 instead of the
 // special-function unit.  Measured on B200 (causal, B=16 H=32 S=4096): 0 -> 1014,
@@ -127,7 +138,8 @@ __device__ __forceinline__ WorkItem decode_item(int idx, const FaParams &p) {
   return w;
 }
 
-__device__ __forceinline__ void fa_report(int code, int role, int detail) {
+// Out of line: the report sits on many cold paths and would otherwise bloat the hot loops.
+__device__ __noinline__ void fa_report(int code, int role, int detail) {
   if (atomicCAS(&g_fa_status[0], 0, code) == 0) {
     g_fa_status[1] = static_cast<int>(blockIdx.y * gridDim.x + blockIdx.x);
     g_fa_status[2] = role;
@@ -195,6 +207,11 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   uint8_t *v_smem = tiles + 4 * kTile;  // 2 stages
   FaShared *sh = reinterpret_cast<FaShared *>(tiles + kSmemTiles);
   volatile int *abort_flag = &sh->abort_flag;
+#ifdef WAVE_FA_TRACE
+  volatile unsigned int *fa_trace_smem = reinterpret_cast<volatile unsigned int *>(tiles + kSmemTiles + 256);
+  for (int i = threadIdx.x; i < 3 * 64 * 16; i += kThreads)
+    fa_trace_smem[i] = 0;
+#endif
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -226,6 +243,14 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = sh->tmem_base;
+#ifdef WAVE_FA_TRACE
+  if (threadIdx.x == 64 && blockIdx.x == 0) { // SM clock against wall time over the CTA's life
+    unsigned long long ns;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(ns));
+    g_fa_trace[1][63][0] = clock64();
+    g_fa_trace[1][63][1] = static_cast<long long>(ns);
+  }
+#endif
 
   // Register budget (setmaxnreg must be the first thing each warpgroup does on
   // its own path): warpgroup 0 (loader, UMMA issuer, two idle warps) gives
@@ -293,23 +318,35 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ UMMA issue
+    // One thread feeds the tensor core.  It can queue only about two
+    // instructions (128 cycles of work at 128 x 128 x 16), so every cycle it
+    // spends between two issues beyond that leaves the tensor core idle: the
+    // descriptors are stepped with one 32-bit add per operand, and the common
+    // case (both tiles have a P*V for this block and a Q*K^T for the next) runs
+    // in a loop of its own without the bookkeeping of the ragged cases.
     if (lane == 0) {
       const uint32_t idesc_s = umma_idesc_f16(kBlockM, kBlockN, p.is_bf16, 0, 0);
       const uint32_t idesc_o = umma_idesc_f16(kBlockM, kD, p.is_bf16, 0, 1); // V is MN-major
-      const uint32_t q_addr = smem_u32(q_smem), k_addr = smem_u32(k_smem), v_addr = smem_u32(v_smem);
+      // Descriptor halves (see umma_desc_kmajor_sw128 / umma_desc_mnmajor_sw128):
+      // the high half is the same for Q, K (K-major) and V (MN-major): stride
+      // 1024 bytes, version 1, 128-byte swizzle.
+      constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+      constexpr uint32_t kTile16 = kTile >> 4, kSub16 = kSubTile >> 4;
+      const uint32_t q_lo = ((smem_u32(q_smem) & 0x3FFFFu) >> 4) | (1u << 16);
+      const uint32_t k_lo = ((smem_u32(k_smem) & 0x3FFFFu) >> 4) | (1u << 16);
+      const uint32_t v_lo = ((smem_u32(v_smem) & 0x3FFFFu) >> 4) | ((kSub16 & 0x3FFFu) << 16);
       bool ok = true;
 
       // S_t = Q_t K_j^T : K = head dim, two 64-element swizzle chunks x four UMMA K steps
       auto issue_s = [&](int t, int stage) {
         const uint32_t d = tmem_base + static_cast<uint32_t>(t * kBlockN);
+        const uint32_t a = q_lo + static_cast<uint32_t>(t) * kTile16;
+        const uint32_t b = k_lo + static_cast<uint32_t>(stage) * kTile16;
+        umma_ss_halves<0>(d, a, b, kDescHi, idesc_s);
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          const uint64_t a = umma_desc_kmajor_sw128(q_addr + t * kTile + c * kSubTile);
-          const uint64_t b = umma_desc_kmajor_sw128(k_addr + stage * kTile + c * kSubTile);
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_ss(d, a + static_cast<uint64_t>(2 * k), b + static_cast<uint64_t>(2 * k), idesc_s,
-                    (c | k) ? 1u : 0u);
+        for (int i = 1; i < 8; ++i) {
+          const uint32_t off = static_cast<uint32_t>((i >> 2) * kSub16 + (i & 3) * 2);
+          umma_ss_halves<1>(d, a + off, b + off, kDescHi, idesc_s);
         }
         umma_commit(&sh->s_full[t]);
       };
@@ -318,11 +355,12 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       auto issue_pv = [&](int t, int stage, bool accumulate) {
         const uint32_t d = tmem_base + static_cast<uint32_t>(2 * kBlockN + t * kD);
         const uint32_t a = tmem_base + static_cast<uint32_t>(t * kBlockN);
+        const uint32_t b = v_lo + static_cast<uint32_t>(stage) * kTile16;
+        umma_ts_halves<-1>(d, a, b, kDescHi, idesc_o, accumulate ? 1u : 0u);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint64_t b = umma_desc_mnmajor_sw128(v_addr + stage * kTile + kk * 2048, kSubTile, 1024);
-          umma_ts(d, a + static_cast<uint32_t>(kk * 8), b, idesc_o, (accumulate || kk) ? 1u : 0u);
-        }
+        for (int kk = 1; kk < 8; ++kk)
+          umma_ts_halves<1>(d, a + static_cast<uint32_t>(kk * 8), b + static_cast<uint32_t>(kk * (2048 >> 4)), kDescHi,
+                            idesc_o);
       };
 
       // Running counts that carry barrier phases from item to item.
@@ -340,7 +378,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         if (idx >= total_items)
           break;
         const WorkItem w = decode_item(idx, p);
-        const int n_max = w.n_max;
+        const int n_max = w.n_max, nb0 = w.n_blocks[0], nb1 = w.n_blocks[1];
         if (!mbar_wait(&sh->q_full, n & 1, abort_flag)) {
           fa_report(kStatusWaitTimeout, 1, 1);
           break;
@@ -352,14 +390,86 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             break;
           }
           tc_fence_after_sync();
-          for (int t = 0; t < 2; ++t)
-            if (w.n_blocks[t] > 0)
-              issue_s(t, s0);
+          if (nb0 > 0)
+            issue_s(0, s0);
+          if (nb1 > 0)
+            issue_s(1, s0);
           umma_commit(&sh->k_empty[s0]);
           if (n_max == 1)
             umma_commit(&sh->q_empty); // no further Q*K^T in this item
         }
-        for (int j = 0; j < n_max && ok; ++j, ++kv_n) {
+        int j = 0;
+        // ---- common case: both tiles have P*V(j) and Q*K^T(j+1)
+        const int n_fast = min(nb0, nb1) - 1;
+        for (; j < n_fast; ++j, ++kv_n) {
+          const int s = kv_n & 1, s_next = s ^ 1;
+          const uint32_t ph = (kv_n >> 1) & 1, ph_next = ((kv_n + 1) >> 1) & 1;
+          if (n == 0)
+            FA_STAMP(0, j, 9);
+          if (!mbar_wait(&sh->v_full[s], ph, abort_flag)) {
+            fa_report(kStatusWaitTimeout, 1, 30 + s);
+            ok = false;
+            break;
+          }
+          if (n == 0)
+            FA_STAMP(0, j, 0);
+          if (!mbar_wait(&sh->p_full[0], p_n[0] & 1, abort_flag)) {
+            fa_report(kStatusWaitTimeout, 1, 40);
+            ok = false;
+            break;
+          }
+          ++p_n[0];
+          if (n == 0)
+            FA_STAMP(0, j, 1);
+          // The first P*V of an item overwrites O_t: the previous item's
+          // epilogue must have read it out.
+          if (j == 0 && tile_items[0] > 0 && !mbar_wait(&sh->o_free[0], (tile_items[0] - 1) & 1, abort_flag)) {
+            fa_report(kStatusWaitTimeout, 1, 45);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          issue_pv(0, s, j > 0);
+          if (n == 0)
+            FA_STAMP(0, j, 3);
+          if (!mbar_wait(&sh->k_full[s_next], ph_next, abort_flag)) {
+            fa_report(kStatusWaitTimeout, 1, 50 + s_next);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          issue_s(0, s_next);
+          if (n == 0)
+            FA_STAMP(0, j, 2);
+          if (!mbar_wait(&sh->p_full[1], p_n[1] & 1, abort_flag)) {
+            fa_report(kStatusWaitTimeout, 1, 41);
+            ok = false;
+            break;
+          }
+          ++p_n[1];
+          if (n == 0)
+            FA_STAMP(0, j, 5);
+          if (j == 0 && tile_items[1] > 0 && !mbar_wait(&sh->o_free[1], (tile_items[1] - 1) & 1, abort_flag)) {
+            fa_report(kStatusWaitTimeout, 1, 46);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          issue_pv(1, s, j > 0);
+          if (n == 0)
+            FA_STAMP(0, j, 7);
+          issue_s(1, s_next);
+          if (n == 0)
+            FA_STAMP(0, j, 6);
+          umma_commit(&sh->v_empty[s]);
+          umma_commit(&sh->k_empty[s_next]);
+          if (j + 2 == n_max)
+            umma_commit(&sh->q_empty); // the last Q*K^T of the item has been issued
+          if (n == 0)
+            FA_STAMP(0, j, 8);
+        }
+        // ---- ragged tail: a tile without work, or the last block(s) of the item
+        for (; j < n_max && ok; ++j, ++kv_n) {
           const int s = kv_n & 1;
           const uint32_t ph = (kv_n >> 1) & 1;
           const int s_next = (kv_n + 1) & 1;
@@ -376,18 +486,12 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
               }
               have_v = true;
             }
-            if (n == 0)
-              FA_STAMP(0, j, t * 4 + 0);
             if (!mbar_wait(&sh->p_full[t], p_n[t] & 1, abort_flag)) {
               fa_report(kStatusWaitTimeout, 1, 40 + t);
               ok = false;
               break;
             }
             ++p_n[t];
-            if (n == 0)
-              FA_STAMP(0, j, t * 4 + 1);
-            // The first P*V of an item overwrites O_t: the previous item's
-            // epilogue must have read it out.
             if (j == 0 && tile_items[t] > 0 && !mbar_wait(&sh->o_free[t], (tile_items[t] - 1) & 1, abort_flag)) {
               fa_report(kStatusWaitTimeout, 1, 45 + t);
               ok = false;
@@ -406,8 +510,6 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                 have_k_next = true;
               }
               issue_s(t, s_next);
-              if (n == 0)
-                FA_STAMP(0, j, t * 4 + 2);
             } else {
               umma_commit(&sh->o_full[t]);
               ++tile_items[t];
@@ -459,7 +561,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     float l = 0.0f;           // running sum of unrounded probabilities
 
     for (int j = 0; j < nb; ++j) {
-      if (row == 0)
+      if (row == 0 && item_n == 0)
         FA_STAMP(1 + t, j, 0);
       if (!mbar_wait(&sh->s_full[t], s_n & 1, abort_flag)) {
         if (lane == 0)
@@ -469,7 +571,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       }
       ++s_n;
       tc_fence_after_sync();
-      if (row == 0)
+      if (row == 0 && item_n == 0)
         FA_STAMP(1 + t, j, 1);
       uint32_t s[128];
       tmem_ld_32x32b_x32(s_addr + 0, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
@@ -477,7 +579,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       tmem_ld_32x32b_x32(s_addr + 64, *reinterpret_cast<uint32_t(*)[32]>(&s[64]));
       tmem_ld_32x32b_x32(s_addr + 96, *reinterpret_cast<uint32_t(*)[32]>(&s[96]));
       tmem_ld_wait();
-      if (row == 0)
+      if (row == 0 && item_n == 0)
         FA_STAMP(1 + t, j, 2);
 
       const int key0 = j * kBlockN;
@@ -518,7 +620,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         }
         m_used = m_new;
       }
-      if (row == 0)
+      if (row == 0 && item_n == 0)
         FA_STAMP(1 + t, j, 3);
       const float neg_mc = -m_used * c;
       const float2 c2 = make_float2(c, c), nm2 = make_float2(neg_mc, neg_mc);
@@ -540,14 +642,14 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         pk[i] = pack2(pr.x, pr.y, bf16);
       }
       l += (la.x + la.y) + (lb.x + lb.y);
-      if (row == 0)
+      if (row == 0 && item_n == 0)
         FA_STAMP(1 + t, j, 4);
       tmem_st_32x32b_x32(s_addr + 0, *reinterpret_cast<uint32_t(*)[32]>(&pk[0]));
       tmem_st_32x32b_x32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&pk[32]));
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(&sh->p_full[t]);
-      if (row == 0)
+      if (row == 0 && item_n == 0)
         FA_STAMP(1 + t, j, 5);
     }
 
@@ -610,6 +712,19 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 
   tc_fence_before_sync();
   __syncthreads();
+#ifdef WAVE_FA_TRACE
+  if (blockIdx.x == 0) {
+    for (int i = threadIdx.x; i < 3 * 64 * 16; i += kThreads)
+      if (i / 16 != 64 + 63) // [1][63][*] holds the clock probe
+        (&g_fa_trace[0][0][0])[i] = fa_trace_smem[i];
+  }
+  if (threadIdx.x == 64 && blockIdx.x == 0) {
+    unsigned long long ns;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(ns));
+    g_fa_trace[1][63][2] = clock64();
+    g_fa_trace[1][63][3] = static_cast<long long>(ns);
+  }
+#endif
   if (warp == 1) {
     __syncwarp();
     tc_fence_after_sync();
@@ -720,9 +835,9 @@ int launch_flash_attention(const FaParams &p, const void *Q, const void *K, cons
 
 #ifdef WAVE_FA_TRACE
 extern "C" int wave_cuda_fa_trace_read(long long *out, int clear) {
-  cudaError_t err = cudaMemcpyFromSymbol(out, g_fa_trace, sizeof(long long) * 3 * 64 * 8);
+  cudaError_t err = cudaMemcpyFromSymbol(out, g_fa_trace, sizeof(long long) * 3 * 64 * 16);
   if (err == cudaSuccess && clear) {
-    static long long zero[3 * 64 * 8];
+    static long long zero[3 * 64 * 16];
     err = cudaMemcpyToSymbol(g_fa_trace, zero, sizeof(zero));
   }
   return err == cudaSuccess ? 0 : -3;

@@ -210,6 +210,46 @@ __device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64
                : "memory");
 }
 
+// The same two instructions with each 64-bit shared-memory descriptor given as
+// its two 32-bit halves, so that the issuing thread steps through a tile with
+// one 32-bit add per operand (the start-address field is the low 14 bits of
+// the low half and never carries out of it for addresses below 256 KB).
+// kAccumulate < 0: take the runtime flag; 0 / 1: compile-time constant.
+template <int kAccumulate>
+__device__ __forceinline__ void umma_ss_halves(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi,
+                                               uint32_t idesc, uint32_t accumulate = 1) {
+  if constexpr (kAccumulate < 0) {
+    asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+                 "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}" ::"r"(tmem_d),
+                 "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
+                 : "memory");
+  } else {
+    asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+                 "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}" ::"r"(tmem_d),
+                 "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "n"(kAccumulate)
+                 : "memory");
+  }
+}
+template <int kAccumulate>
+__device__ __forceinline__ void umma_ts_halves(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint32_t desc_hi,
+                                               uint32_t idesc, uint32_t accumulate = 1) {
+  if constexpr (kAccumulate < 0) {
+    asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 db;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+                 "mov.b64 db, {%2, %3};\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}" ::"r"(tmem_d),
+                 "r"(tmem_a), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
+                 : "memory");
+  } else {
+    asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 db;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+                 "mov.b64 db, {%2, %3};\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}" ::"r"(tmem_d),
+                 "r"(tmem_a), "r"(b_lo), "r"(desc_hi), "r"(idesc), "n"(kAccumulate)
+                 : "memory");
+  }
+}
+
 // TMEM -> registers, 32 lanes x 32-bit, N consecutive columns per thread.
 // Warp w of a warpgroup may only touch lanes [32*(w%4), 32*(w%4)+32).
 __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
