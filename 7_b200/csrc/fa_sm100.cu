@@ -411,6 +411,14 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             ok = false;
             break;
           }
+          // K of the next block was requested a whole block ago; looking at
+          // its barrier here, ahead of the wait for P, keeps that look out of
+          // the tile's softmax -> P*V -> Q*K^T -> softmax chain.
+          if (!mbar_wait(&sh->k_full[s_next], ph_next, abort_flag)) {
+            fa_report(kStatusWaitTimeout, 1, 50 + s_next);
+            ok = false;
+            break;
+          }
           if (n == 0)
             FA_STAMP(0, j, 0);
           if (!mbar_wait(&sh->p_full[0], p_n[0] & 1, abort_flag)) {
@@ -432,12 +440,6 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           issue_pv(0, s, j > 0);
           if (n == 0)
             FA_STAMP(0, j, 3);
-          if (!mbar_wait(&sh->k_full[s_next], ph_next, abort_flag)) {
-            fa_report(kStatusWaitTimeout, 1, 50 + s_next);
-            ok = false;
-            break;
-          }
-          tc_fence_after_sync();
           issue_s(0, s_next);
           if (n == 0)
             FA_STAMP(0, j, 2);
