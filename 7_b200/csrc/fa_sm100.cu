@@ -26,10 +26,12 @@
 // extension: the reference's Wave kernel is non-causal.
 #include "../../include/wave_cuda.h"
 #include "fa_sm100.h"
+#include "fa_common.cuh"
 #include "sm100_ptx.cuh"
 
 #include <atomic>
 #include <cstdlib>
+#include <cstring>
 #include <type_traits>
 
 namespace wave {
@@ -72,6 +74,8 @@ __device__ long long g_fa_trace[3][64][16];
 
 namespace {
 
+using namespace fa_detail;
+
 constexpr int kBlockM = 128; // rows per Q tile = UMMA M = TMEM lanes
 constexpr int kBlockN = 128; // keys per K/V block
 constexpr int kD = 128;      // head dimension
@@ -87,6 +91,7 @@ constexpr int kTmemCols = 512;
 // S/P hand-offs between the softmax warps and the tensor core, not by the
 // special-function unit, so the default keeps every exponential on it.
 constexpr int kDefaultPoly = 0;
+constexpr bool kDefaultStreamKernel = false;
 constexpr float kRescaleThreshold = 8.0f;
 // setmaxnreg budget.  The kernel starts with kLaunchRegs per thread (12 warps,
 // one CTA per SM); warpgroup 0 shrinks to kIssueRegs and the two softmax
@@ -145,55 +150,6 @@ __device__ __noinline__ void fa_report(int code, int role, int detail) {
     g_fa_status[2] = role;
     g_fa_status[3] = detail;
   }
-}
-
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
-__device__ __forceinline__ float max3(float a, float b, float c) {
-  float d;
-  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-  return d;
-}
-
-// 2^x for a pair of values on the FMA pipe instead of the special-function
-// unit: round-to-nearest split x = n + f with |f| <= 0.5 (adding 1.5*2^23 leaves
-// n in the low mantissa bits), a degree-3 minimax polynomial for 2^f (maximum
-// relative error 7.6e-5, far below the 2^-9 of the 16-bit rounding that
-// follows), then n is added to the exponent field.  Arguments below -125 are
-// clamped (the result is then ~2^-125, which rounds away in every use here).
-__device__ __forceinline__ float2 exp2_poly2(float2 x) {
-  x.x = fmaxf(x.x, -125.0f);
-  x.y = fmaxf(x.y, -125.0f);
-  const float2 t = __fadd2_rn(x, make_float2(12582912.0f, 12582912.0f));
-  const float2 n = __fadd2_rn(t, make_float2(-12582912.0f, -12582912.0f));
-  const float2 f = __ffma2_rn(n, make_float2(-1.0f, -1.0f), x);
-  float2 q = __ffma2_rn(f, make_float2(0.05520550534129143f, 0.05520550534129143f),
-                        make_float2(0.24261397123336792f, 0.24261397123336792f));
-  q = __ffma2_rn(q, f, make_float2(0.6932547688484192f, 0.6932547688484192f));
-  q = __ffma2_rn(q, f, make_float2(0.9999276995658875f, 0.9999276995658875f));
-  float2 r;
-  r.x = __int_as_float(__float_as_int(q.x) + (__float_as_int(t.x) << 23));
-  r.y = __int_as_float(__float_as_int(q.y) + (__float_as_int(t.y) << 23));
-  return r;
-}
-
-// Which of the 64 column pairs of a row take the polynomial path: kPoly of
-// every 8, spread evenly so that FMA-pipe and special-function work interleave.
-template <int kPoly> __device__ __forceinline__ constexpr bool pair_uses_poly(int i) {
-  return ((i + 1) * kPoly) / 8 > (i * kPoly) / 8;
-}
-
-__device__ __forceinline__ uint32_t pack2(float lo, float hi, bool bf16) {
-  if (bf16) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t *>(&v);
-  }
-  __half2 v = __floats2half2_rn(lo, hi);
-  return *reinterpret_cast<uint32_t *>(&v);
 }
 
 template <int kPoly, bool kBf16>
@@ -593,15 +549,23 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           if (key0 + i > limit)
             s[i] = 0xFF800000u; // -inf
       }
-      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+      // Sixteen independent chains: a three-input maximum has a long latency
+      // (a chain of 16 took ~245 cycles), so the depth is kept at four.
+      float mx[16];
 #pragma unroll
-      for (int i = 0; i < 128; i += 8) {
-        mx0 = max3(mx0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
-        mx1 = max3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
-        mx2 = max3(mx2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
-        mx3 = max3(mx3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
-      }
-      const float m_new = fmaxf(m_used, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
+      for (int i = 0; i < 16; ++i)
+        mx[i] = fmaxf(__uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1]));
+#pragma unroll
+      for (int i = 32; i < 128; i += 32)
+#pragma unroll
+        for (int k = 0; k < 16; ++k)
+          mx[k] = max3(mx[k], __uint_as_float(s[i + 2 * k]), __uint_as_float(s[i + 2 * k + 1]));
+#pragma unroll
+      for (int k = 0; k < 5; ++k)
+        mx[k] = max3(mx[k], mx[5 + 2 * k], mx[6 + 2 * k]);
+      mx[0] = max3(mx[0], mx[1], mx[2]);
+      mx[3] = max3(mx[3], mx[4], mx[15]);
+      const float m_new = max3(m_used, mx[0], mx[3]);
       // Lazy rescale: only when some row of this warp moved its maximum by more
       // than 2^8; otherwise keep the stale maximum (exact after the final divide).
       const bool need = (m_new - m_used) * c > kRescaleThreshold;
@@ -790,6 +754,14 @@ int launch_flash_attention(const FaParams &p, const void *Q, const void *K, cons
       return WAVE_E_CUDA;
     }
   }
+  // WAVE_CUDA_FA_KERNEL=stream|pingpong picks the kernel (a knob for
+  // measurements; results are the same).
+  {
+    const char *env = getenv("WAVE_CUDA_FA_KERNEL");
+    const bool stream_kernel = env ? strcmp(env, "stream") == 0 : kDefaultStreamKernel;
+    if (stream_kernel)
+      return launch_flash_attention_stream(params, tq, tk, tv, poly, sm_count, stream);
+  }
   bool unsafe_budget = false;
   auto launch = [&](auto kernel) {
     // The setmaxnreg arithmetic in the kernel assumes the register count the
@@ -846,12 +818,20 @@ extern "C" int wave_cuda_fa_trace_read(long long *out, int clear) {
 }
 #endif
 
+// Status of both attention kernels: the first one that reported something.
 cudaError_t fa_read_status(int out[4], bool clear) {
   cudaError_t err = cudaMemcpyFromSymbol(out, g_fa_status, sizeof(int) * 4);
   if (err == cudaSuccess && clear) {
     int zero[4] = {0, 0, 0, 0};
     err = cudaMemcpyToSymbol(g_fa_status, zero, sizeof(zero));
   }
+  if (err != cudaSuccess)
+    return err;
+  int other[4];
+  err = fa_stream_read_status(other, clear);
+  if (err == cudaSuccess && out[0] == 0 && other[0] != 0)
+    for (int i = 0; i < 4; ++i)
+      out[i] = other[i];
   return err;
 }
 

@@ -22,6 +22,12 @@ struct FaParams {
 int launch_flash_attention(const FaParams &p, const void *Q, const void *K, const void *V, int sm_count,
                            cudaStream_t stream);
 cudaError_t fa_read_status(int out[4], bool clear);
+// The streaming kernel (fa_stream_sm100.cu): one 128-row Q tile per CTA, score
+// and probability buffers double-buffered in tensor memory.  `p.ticket` must
+// point at a zeroed work-item counter.
+int launch_flash_attention_stream(const FaParams &p, const CUtensorMap &tq, const CUtensorMap &tk,
+                                  const CUtensorMap &tv, int poly, int sm_count, cudaStream_t stream);
+cudaError_t fa_stream_read_status(int out[4], bool clear);
 
 // Provided by the backend: rank-2/3 tensor map over 16-bit elements with the
 // 128-byte swizzle and zero fill outside the tensor.

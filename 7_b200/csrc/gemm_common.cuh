@@ -60,6 +60,20 @@ __device__ __forceinline__ void store_row_chunk(const GemmParams &p, int m, int 
            ti) *
               p.tp_wnt +
           tj;
+      if (p.tp_fragment) {
+        // AMD accumulator-fragment order inside the tile (the reference runner's
+        // getOutputCoordinate, wave-matmul-calibrate-runner.cpp:809-836): the
+        // 16 values of a row go to 16 lanes' slots, values_per_lane apart.
+        const int r = m & 15;
+        const int vpl = p.tp_fragment == 1 ? 4 : 8;
+        const int lane_row = p.tp_fragment == 2 ? (r & 1) : r / vpl; // lane / 16
+        const int v_idx = p.tp_fragment == 2 ? (r >> 1) : r % vpl;
+        T *frag = reinterpret_cast<T *>(p.C) + tile * 256 + lane_row * 16 * vpl + v_idx;
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          store_elem(frag + j * vpl, v[g + j]);
+        continue;
+      }
       T *dst = reinterpret_cast<T *>(p.C) + tile * 256 + (m & 15) * 16;
 #pragma unroll
       for (int j = 0; j < 16; j += per_vec) {

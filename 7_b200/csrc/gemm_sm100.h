@@ -28,6 +28,8 @@ struct GemmParams {
   int *counters;       // Stream-K: one arrival counter per output tile, zero on entry and exit
   // tile-packed output (16 x 16 tiles in workgroup -> wave -> per-wave-tile order)
   int tile_packed, tp_bm, tp_bn, tp_wmt, tp_wnt, tp_n_blocks;
+  // order of the 256 values inside a tile: 0 row-major, 1 MFMA wave64, 2 WMMA wave32, 3 MFMA wave32 fragments
+  int tp_fragment;
 };
 
 int gemm_tile_m();

@@ -65,21 +65,42 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking look at a barrier (try_wait may suspend the thread for a while
+// before it answers; test_wait answers at once).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\t"
+               "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+               "selp.b32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok)
+               : "r"(smem_u32(bar)), "r"(parity)
+               : "memory");
+  return ok != 0;
+}
+
 // Bounded wait.  `abort_flag` lives in shared memory and is shared by every
 // role of the CTA: the first wait that runs out sets it, and every other wait
 // sees it and gives up too, so the whole CTA reaches its teardown.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
-  if (mbar_try_wait(bar, parity))
+  if (mbar_test_wait(bar, parity))
     return true;
   const long long start = clock64();
-  for (;;) {
+  // The abort flag and the clock are looked at once in 16 tries: a waiting warp
+  // should put as little as possible on the memory pipes that the loader and the
+  // UMMA-issuing thread of the same SM need.
+  for (uint32_t tries = 1;; ++tries) {
     if (mbar_try_wait(bar, parity))
       return true;
-    if (*abort_flag)
-      return false;
-    if (clock64() - start > kWaitLimitCycles) {
-      *abort_flag = 1;
-      return false;
+#ifdef WAVE_WAIT_NANOSLEEP
+    __nanosleep(WAVE_WAIT_NANOSLEEP);
+#endif
+    if ((tries & 15u) == 0) {
+      if (*abort_flag)
+        return false;
+      if (clock64() - start > kWaitLimitCycles) {
+        *abort_flag = 1;
+        return false;
+      }
     }
   }
 }

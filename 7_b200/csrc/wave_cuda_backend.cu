@@ -113,6 +113,8 @@ int sm_count(int *out) {
 
 int elem_size(int type) { return type == WAVE_F32 ? 4 : 2; }
 
+bool is_tile_packed(int layout) { return layout >= WAVE_TILE_PACKED && layout <= WAVE_TILE_PACKED_MFMA32; }
+
 // ---------------------------------------------------------------- GEMM plan
 struct GemmPlan {
   bool pair;          // CTA-pair kernel: 256 x 256 or 256 x 128 tiles, two CTAs per tile
@@ -162,7 +164,7 @@ int make_plan(const wave_gemm_desc &d, int sms, bool have_workspace, GemmPlan *p
   GemmPlan p{};
   // A 128-row UMMA wastes most of its rows on a skinny M; put N on the rows
   // instead and M on the (narrow) column tile.
-  p.swapped = d.M < tile_m && d.N > d.M && d.out_layout != WAVE_TILE_PACKED;
+  p.swapped = d.M < tile_m && d.N > d.M && !is_tile_packed(d.out_layout);
   p.Mk = p.swapped ? d.N : d.M;
   p.Nk = p.swapped ? d.M : d.N;
   const int want = p.swapped ? want_m : want_n;
@@ -327,7 +329,7 @@ HostPipeline *host_pipeline() {
 // block must keep the descriptor's tiling rules valid (a multiple of
 // 16*bn*wave_n_tiles) and fill whole 256-column tiles.
 int host_pipeline_chunk(const wave_gemm_desc &d, size_t copy_bytes) {
-  if (copy_bytes < (64u << 20) || d.out_layout == WAVE_TILE_PACKED || d.ldc != 0 || d.streamk_workers > 1)
+  if (copy_bytes < (64u << 20) || is_tile_packed(d.out_layout) || d.ldc != 0 || d.streamk_workers > 1)
     return 0;
   const int unit = 16 * d.bn * d.wave_n_tiles;
   for (int parts : {8, 6, 4, 3, 2}) {
@@ -413,7 +415,7 @@ int wave_cuda_gemm_validate(const wave_gemm_desc *d) {
                 d->wave_m_tiles, d->wave_n_tiles, d->wave_k_tiles);
   if (d->out_type != WAVE_F32 && d->out_type != WAVE_F16 && d->out_type != WAVE_BF16)
     return fail(WAVE_E_INVALID, "output_type must be one of f32, f16, bf16; got %d", d->out_type);
-  if (d->out_layout != WAVE_ROW_MAJOR && d->out_layout != WAVE_COL_MAJOR && d->out_layout != WAVE_TILE_PACKED)
+  if (d->out_layout != WAVE_ROW_MAJOR && d->out_layout != WAVE_COL_MAJOR && !is_tile_packed(d->out_layout))
     return fail(WAVE_E_INVALID, "output_layout must be one of row-major, column-major, tile-packed; got %d",
                 d->out_layout);
   if (d->in_type != WAVE_F16 && d->in_type != WAVE_BF16)
@@ -444,7 +446,7 @@ int wave_cuda_gemm_validate(const wave_gemm_desc *d) {
                 m_blocks, d->cta_group_m);
   if (d->streamk_workers < 0)
     return fail(WAVE_E_INVALID, "streamk_workers must be >= 0; got %d", d->streamk_workers);
-  if (d->out_layout == WAVE_TILE_PACKED && d->ldc != 0)
+  if (is_tile_packed(d->out_layout) && d->ldc != 0)
     return fail(WAVE_E_INVALID, "ldc must be 0 with tile-packed output; got %d", d->ldc);
   const int min_ld = d->out_layout == WAVE_ROW_MAJOR ? d->N : d->M;
   if (d->ldc != 0 && (d->ldc < min_ld || d->ldc % 16 != 0))
@@ -572,8 +574,9 @@ int wave_cuda_gemm(const wave_gemm_desc *d, const void *A, const void *B, void *
       g = plan.num_m;
     p.group_m = g;
   }
-  if (d->out_layout == WAVE_TILE_PACKED) {
+  if (is_tile_packed(d->out_layout)) {
     p.tile_packed = 1;
+    p.tp_fragment = d->out_layout - WAVE_TILE_PACKED; // 0 row-major tiles, 1 MFMA wave64, 2 WMMA wave32, 3 MFMA wave32
     p.tp_bm = d->bm;
     p.tp_bn = d->bn;
     p.tp_wmt = d->wave_m_tiles;

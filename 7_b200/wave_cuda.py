@@ -14,10 +14,13 @@ LIB_PATH = os.path.join(HERE, "libwave_cuda.so")
 
 F16, BF16, F32 = 0, 1, 2
 ROW_MAJOR, COL_MAJOR, TILE_PACKED = 0, 1, 2
+TILE_PACKED_MFMA64, TILE_PACKED_WMMA32, TILE_PACKED_MFMA32 = 3, 4, 5  # AMD fragment order inside a tile
 OK, E_INVALID, E_UNSUPPORTED, E_CUDA, E_DEVICE_STATUS, E_NOT_FOUND = 0, -1, -2, -3, -4, -5
 
 TYPE_BY_NAME = {"f16": F16, "bf16": BF16, "f32": F32}
-LAYOUT_BY_NAME = {"row-major": ROW_MAJOR, "column-major": COL_MAJOR, "tile-packed": TILE_PACKED}
+LAYOUT_BY_NAME = {"row-major": ROW_MAJOR, "column-major": COL_MAJOR, "tile-packed": TILE_PACKED,
+                  "tile-packed-mfma64": TILE_PACKED_MFMA64, "tile-packed-wmma32": TILE_PACKED_WMMA32,
+                  "tile-packed-mfma32": TILE_PACKED_MFMA32}
 
 
 class WaveCudaError(RuntimeError):

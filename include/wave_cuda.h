@@ -41,6 +41,16 @@ extern "C" {
                               workgroup -> wave -> per-wave-tile order: the order in which
                               compute_wmma_f16_matmul_reference_buffer emits them
                               (wave_matmul.py:1025-1028, 1106-1139) */
+/* The same tile order, with the 256 values of a tile in the order of the AMD
+ * accumulator fragments that the reference's timed runner checks
+ * (getOutputCoordinate / getAccumulatorRow, wave-matmul-calibrate-runner.cpp:
+ * 809-836): slot = lane * values_per_lane + v, column = lane % 16, and row
+ *   MFMA, wave64: (lane / 16) * 4 + v   (4 values per lane)
+ *   WMMA, wave32: (lane / 16) + 2 * v   (8 values per lane)
+ *   MFMA, wave32: (lane / 16) * 8 + v   (8 values per lane) */
+#define WAVE_TILE_PACKED_MFMA64 3
+#define WAVE_TILE_PACKED_WMMA32 4
+#define WAVE_TILE_PACKED_MFMA32 5
 
 const char *wave_cuda_last_error(void);
 const char *wave_cuda_version(void);
@@ -76,7 +86,7 @@ typedef struct wave_gemm_desc {
   int wave_m_tiles, wave_n_tiles, wave_k_tiles; /* 16x16 tiles per wave, K slices per step */
   int in_type;                 /* WAVE_F16 | WAVE_BF16                                      */
   int out_type;                /* WAVE_F32 | WAVE_F16 | WAVE_BF16                           */
-  int out_layout;              /* WAVE_ROW_MAJOR | WAVE_COL_MAJOR | WAVE_TILE_PACKED        */
+  int out_layout;              /* WAVE_ROW_MAJOR | WAVE_COL_MAJOR | WAVE_TILE_PACKED[_...]  */
   int cta_group_m;             /* grouped-M rasterisation (wave_matmul.py:1267-1272); >= 1 */
   int streamk_workers;         /* 0 auto, 1 plain tiles, >1 persistent Stream-K grid
                                   (--streamk-workers, wave-matmul-calibrate.py:1170)      */

@@ -248,7 +248,48 @@ def layout_output(c_rowmajor: np.ndarray, layout: str, BM: int = 1, BN: int = 1,
                             nt = wg_n * BN * wave_n_tiles + n_wave * wave_n_tiles + j
                             out.append(c_rowmajor[mt * 16:(mt + 1) * 16, nt * 16:(nt + 1) * 16].reshape(-1))
         return np.concatenate(out)
+    if layout in FRAGMENT_LAYOUTS:
+        M, N = c_rowmajor.shape
+        wmma, wave_size = FRAGMENT_LAYOUTS[layout]
+        idx = np.arange(M * N)
+        m, n = tile_packed_fragment_coordinate(idx, M, N, BM, BN, wave_m_tiles, wave_n_tiles, wmma, wave_size)
+        return np.ascontiguousarray(c_rowmajor)[m, n]
     raise ValueError(layout)
+
+
+# layout name -> (WMMA accumulator layout?, wave size) of the reference runner
+FRAGMENT_LAYOUTS = {"tile-packed-mfma64": (False, 64), "tile-packed-wmma32": (True, 32),
+                    "tile-packed-mfma32": (False, 32)}
+
+
+def tile_packed_fragment_coordinate(index, M: int, N: int, BM: int, BN: int, wave_m_tiles: int, wave_n_tiles: int,
+                                    wmma: bool, wave_size: int):
+    """Packed index -> logical (m, n) of the timed runner's tile-packed output,
+    restating getOutputCoordinate / getAccumulatorRow / makeTilePackedOutputPlan
+    (wave-matmul-calibrate-runner.cpp:771-836): tiles in workgroup -> wave ->
+    per-wave-tile order, the 256 values of a tile as lane * values_per_lane + v
+    with column lane % 16 and row (lane // 16) + 2 v (WMMA, wave32) or
+    (lane // 16) * values_per_lane + v (MFMA).  `index` may be an array."""
+    index = np.asarray(index)
+    values_per_lane = 256 // wave_size
+    m_tiles_per_block = BM * wave_m_tiles
+    n_tiles_per_block = BN * wave_n_tiles
+    n_blocks = N // (16 * n_tiles_per_block)
+    wave_elements = wave_m_tiles * wave_n_tiles * 256
+    cta_elements = BM * BN * wave_elements
+    cta, cta_rem = index // cta_elements, index % cta_elements
+    wg_m, wg_n = cta // n_blocks, cta % n_blocks
+    wave_id, wave_rem = cta_rem // wave_elements, cta_rem % wave_elements
+    tile_id, slot = wave_rem // 256, wave_rem % 256
+    m_wave, n_wave = wave_id // BN, wave_id % BN
+    lane, lane_value = slot // values_per_lane, slot % values_per_lane
+    if wmma:
+        m_lane = lane // 16 + 2 * lane_value
+    else:
+        m_lane = (lane // 16) * values_per_lane + lane_value
+    m_tile = wg_m * m_tiles_per_block + m_wave * wave_m_tiles + tile_id // wave_n_tiles
+    n_tile = wg_n * n_tiles_per_block + n_wave * wave_n_tiles + tile_id % wave_n_tiles
+    return m_tile * 16 + m_lane, n_tile * 16 + lane % 16
 
 
 # --------------------------------------------------------------------------
@@ -321,6 +362,7 @@ def ref_lib():
         R.wave_ref_streamk_scratch_bytes.restype = C.c_size_t
         R.wave_ref_streamk_counter_elements.argtypes = [C.c_int, C.c_int]
         R.wave_ref_streamk_counter_elements.restype = C.c_size_t
+        R.wave_ref_output_coordinate.argtypes = [C.c_int] * 9 + [_i32p]
         R.wave_ref_fa_input_bits.argtypes = [_u16p, C.c_size_t, C.c_int, C.c_int, C.c_float]
         R.wave_ref_fa_rows.argtypes = [_u16p, _u16p, _u16p, C.c_int, C.c_int, C.c_int, _i32p, C.c_int,
                                        _i32p, C.c_int, _f32p, C.c_int]
@@ -336,6 +378,13 @@ def ref_make_input_bits(rows: int, k: int, dtype: int, seed: int, stream: int, m
     out = np.empty((rows, k), np.uint16)
     ref_lib().wave_ref_make_input_bits(out.reshape(-1), rows, k, dtype, seed, stream, mode)
     return out
+
+
+def ref_output_coordinate(M: int, N: int, BM: int, BN: int, wave_m_tiles: int, wave_n_tiles: int, wmma: bool,
+                          wave_size: int, index: int):
+    out = np.zeros(2, np.int32)
+    ref_lib().wave_ref_output_coordinate(M, N, BM, BN, wave_m_tiles, wave_n_tiles, int(wmma), wave_size, index, out)
+    return int(out[0]), int(out[1])
 
 
 def ref_gemm_rows(a_bits, b_bits, dtype: int, rows=None, threads: int | None = None) -> np.ndarray:

@@ -79,6 +79,25 @@ size_t wave_ref_streamk_scratch_bytes(int workers) {
   args.streamKWorkers = workers;
   return getStreamKWorkspaceSizes(args).scratchBytes;
 }
+/* getOutputCoordinate (runner.cpp:809-836): packed index -> (m, n) for the
+ * fragment layouts.  wmma: 1 WMMA, 0 MFMA accumulator layout. */
+int wave_ref_output_coordinate(int m, int n, int bm, int bn, int wave_m_tiles,
+                               int wave_n_tiles, int wmma, int wave_size,
+                               int index, int *out_mn) {
+  Args args;
+  args.m = m;
+  args.n = n;
+  args.bm = bm;
+  args.bn = bn;
+  args.waveMTiles = wave_m_tiles;
+  args.waveNTiles = wave_n_tiles;
+  args.accumulatorLayout = wmma ? AccumulatorLayout::Wmma : AccumulatorLayout::Mfma;
+  args.waveSize = wave_size;
+  OutputCoordinate c = getOutputCoordinate(args, index);
+  out_mn[0] = c.m;
+  out_mn[1] = c.n;
+  return 0;
+}
 size_t wave_ref_streamk_counter_elements(int m, int n) {
   Args args;
   args.m = m;

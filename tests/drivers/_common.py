@@ -65,16 +65,19 @@ IGNORED_AMD_FLAGS = [
 
 def add_ignored_flags(parser):
     """AMD-only controls of the reference tools: accepted so that existing
-    command lines run, ignored with a one-line notice."""
+    command lines run, ignored with a one-line notice.  A flag the tool already
+    defines for itself is left alone."""
     for flag, nargs in IGNORED_AMD_FLAGS:
+        if flag in parser._option_string_actions:
+            continue
         if nargs:
             parser.add_argument(flag, default=None, help="AMD-only; accepted and ignored")
         else:
             parser.add_argument(flag, action="store_true", help="AMD-only; accepted and ignored")
 
 
-def note_ignored(args):
+def note_ignored(args, handled=()):
     used = [flag for flag, _ in IGNORED_AMD_FLAGS if getattr(args, flag[2:].replace("-", "_")) not in (None, False)]
-    used = [f for f in used if f != "--chip"]
+    used = [f for f in used if f != "--chip" and f not in handled]
     if used:
         sys.stderr.write("note: ignoring AMD-only flags on sm_100a: " + " ".join(used) + "\n")

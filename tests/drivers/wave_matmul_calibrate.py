@@ -35,7 +35,11 @@ def parse(argv):
     p.add_argument("--wave-k-tiles", type=int, default=1)
     p.add_argument("--input-type", choices=["f16", "bf16"], default="f16")
     p.add_argument("--c-type", choices=["f32", "f16", "bf16"], default="f32")
-    p.add_argument("--output-layout", choices=["automatic", "row-major", "column-major"], default="automatic")
+    p.add_argument("--output-layout", choices=["automatic", "row-major", "column-major", "tile-packed"],
+                   default="automatic")
+    p.add_argument("--accumulator-layout", choices=["automatic", "mfma", "wmma"], default="automatic",
+                   help="fragment order inside a tile of tile-packed output (runner.cpp:765-769)")
+    p.add_argument("--wave-size", type=int, choices=[32, 64], default=32)
     p.add_argument("--kernel-abi", choices=["matmul", "streamk"], default="matmul")
     p.add_argument("--streamk-workers", type=int, default=1)
     p.add_argument("--cta-group-m", type=int, default=1)
@@ -55,7 +59,7 @@ def parse(argv):
 
 def main(argv=None) -> int:
     args = parse(sys.argv[1:] if argv is None else argv)
-    note_ignored(args)
+    note_ignored(args, handled=("--wave-size",))
     if sum([args.all_ones, args.rand_int, args.hpl]) > 1:
         sys.stderr.write("--all-ones, --rand-int and --hpl are mutually exclusive\n")
         return 2
@@ -64,6 +68,15 @@ def main(argv=None) -> int:
         return 2
     torch, wc, oracle = load()
     layout = "row-major" if args.output_layout == "automatic" else args.output_layout
+    if layout == "tile-packed":
+        # getEffectiveAccumulatorLayout (runner.cpp:765-769): MFMA on wave64, WMMA on wave32 unless told otherwise
+        acc = args.accumulator_layout
+        if acc == "automatic":
+            acc = "mfma" if args.wave_size == 64 else "wmma"
+        if acc == "wmma" and args.wave_size != 32:
+            sys.stderr.write("WMMA output check requires wave32\n")
+            return 2
+        layout = f"tile-packed-{acc}{args.wave_size}"
     streamk = args.streamk_workers if args.kernel_abi == "streamk" else 1
     desc = wc.gemm_desc(args.m, args.n, args.k, bm=args.bm, bn=args.bn, wave_m_tiles=args.wave_m_tiles,
                         wave_n_tiles=args.wave_n_tiles, wave_k_tiles=args.wave_k_tiles,
@@ -103,7 +116,7 @@ def main(argv=None) -> int:
     print(f"device: {props.name} (sm_{props.major}{props.minor}a) sms={props.multi_processor_count}")
     print(f"kernel: {name}")
     print(f"shape: m={args.m} n={args.n} k={args.k} bm={args.bm} bn={args.bn} wave_m_tiles={args.wave_m_tiles} "
-          f"wave_n_tiles={args.wave_n_tiles} wave_k_tiles={args.wave_k_tiles} wave_size=32 input_type={args.input_type} "
+          f"wave_n_tiles={args.wave_n_tiles} wave_k_tiles={args.wave_k_tiles} wave_size={args.wave_size} input_type={args.input_type} "
           f"c_type={args.c_type} kernel_abi={args.kernel_abi} output_layout={layout} scale_layout=canonical "
           f"mxfp4_input_layout=canonical input_mode={MODE_NAMES[mode]}")
     print(f"output_contract: kernel={layout} final={layout} conversion=none")
@@ -127,7 +140,16 @@ def main(argv=None) -> int:
         exp = oracle.round_output(oracle.gemm_ref(a_bits, b_bits, t, rows=rows), args.c_type)
         cpu_s = time.perf_counter() - t0
         got = c.float().cpu().numpy()
-        got = got.reshape(args.m, args.n) if layout == "row-major" else got.reshape(args.n, args.m).T
+        if layout in oracle.FRAGMENT_LAYOUTS:
+            # reorderTilePackedOutput (runner.cpp:874-886): back to row-major through the index map
+            wmma, wave = oracle.FRAGMENT_LAYOUTS[layout]
+            mm, nn = oracle.tile_packed_fragment_coordinate(np.arange(args.m * args.n), args.m, args.n, args.bm, args.bn,
+                                                            args.wave_m_tiles, args.wave_n_tiles, wmma, wave)
+            logical = np.empty((args.m, args.n), got.dtype)
+            logical[mm, nn] = got
+            got = logical
+        else:
+            got = got.reshape(args.m, args.n) if layout == "row-major" else got.reshape(args.n, args.m).T
         if rows is not None:
             got = got[rows]
         diff = np.abs(got.astype(np.float64) - exp.astype(np.float64))

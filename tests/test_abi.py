@@ -44,7 +44,8 @@ def test_library_exports_every_declared_symbol(wc):
     (dict(M=1024, N=1024, bm=8, bn=8), "BM * BN must be <= 32 (RDNA3 workgroup wave cap); got BM=8, BN=8 (product=64)"),
     (dict(cta_group_m=0), "cta_group_m must be >= 1; got 0"),
     (dict(cta_group_m=3), "cta_group_m currently requires M_blocks to divide evenly; got M_blocks=4, cta_group_m=3"),
-    (dict(out_layout=3), "output_layout must be one of row-major, column-major, tile-packed; got 3"),
+    (dict(out_layout=6), "output_layout must be one of row-major, column-major, tile-packed; got 6"),
+    (dict(out_layout=4, ldc=64), "ldc must be 0 with tile-packed output"),
     (dict(out_layout=2, ldc=64), "ldc must be 0 with tile-packed output"),
     (dict(in_type=2), "input_type must be one of f16, bf16; got 2"),
     (dict(ldc=72), "ldc must be 0 or a multiple of 16"),

@@ -54,6 +54,19 @@ def test_gemm_calibrate_runner_contract(cuda):
     assert "input_mode=rand_int" in out
 
 
+@pytest.mark.parametrize("flags,layout", [
+    (("--wave-size=64",), "tile-packed-mfma64"),
+    ((), "tile-packed-wmma32"),
+    (("--accumulator-layout=mfma",), "tile-packed-mfma32"),
+])
+def test_gemm_calibrate_runner_tile_packed_fragments(cuda, flags, layout):
+    """Tile-packed output in the accumulator-fragment order the reference's runner
+    validates (wave-matmul-calibrate-runner.cpp:765-769, 809-836, 888-988)."""
+    out, _ = run("wave_matmul_calibrate.py", "--m=128", "--n=256", "--k=512", "--bm=2", "--bn=2", "--wave-m-tiles=2",
+                 "--wave-n-tiles=4", "--output-layout=tile-packed", "--iters=3", "--warmup=1", *flags)
+    assert f"output_check: passed mode=strict layout={layout} elements=32768" in out, out
+
+
 def test_gemm_calibrate_runner_streamk(cuda):
     out, _ = run("wave_matmul_calibrate.py", "--m=512", "--n=512", "--k=2048", "--bm=4", "--bn=4", "--wave-m-tiles=2",
                  "--wave-n-tiles=4", "--hpl", "--input-type=bf16", "--kernel-abi=streamk", "--streamk-workers=5",

@@ -159,6 +159,36 @@ def test_streamk_matches_oracle_and_resets_counters(cuda, wc, oracle, M, N, K, w
     assert ok, f"{nbad} elements out of tolerance, worst {worst}"
 
 
+@pytest.mark.parametrize("layout", ["tile-packed-mfma64", "tile-packed-wmma32", "tile-packed-mfma32"])
+@pytest.mark.parametrize("M,N,K,out_name,streamk,knobs", [
+    (64, 96, 32, "f32", 1, dict(bm=2, bn=2, wave_m_tiles=2, wave_n_tiles=3)),
+    (256, 512, 128, "bf16", 1, dict(bm=4, bn=4, wave_m_tiles=4, wave_n_tiles=4)),   # CTA-pair kernel
+    (384, 256, 1024, "f16", 7, dict(bm=2, bn=4, wave_m_tiles=3, wave_n_tiles=4)),   # Stream-K
+])
+def test_tile_packed_fragment_layouts(cuda, wc, oracle, layout, M, N, K, out_name, streamk, knobs):
+    """Tile-packed C with each tile in the AMD accumulator-fragment order the
+    reference's timed runner validates (wave-matmul-calibrate-runner.cpp:809-836,
+    888-988); LCG inputs, bit-exact."""
+    a_bits, b_bits = lcg_inputs(oracle, M, N, K, "f16", seed=K + 1)
+    desc = wc.gemm_desc(M, N, K, out_type=wc.TYPE_BY_NAME[out_name], out_layout=wc.LAYOUT_BY_NAME[layout],
+                        streamk_workers=streamk, **knobs)
+    a, b = to_device_bits(cuda, a_bits), to_device_bits(cuda, b_bits)
+    c = device_out(cuda, M * N, out_name)
+    scratch, counters = wc.gemm_workspace_bytes(desc)
+    ws = cuda.zeros(scratch + counters, dtype=cuda.uint8, device="cuda") if scratch + counters else None
+    os.environ["WAVE_CUDA_GEMM_KERNEL"] = "pair"
+    try:
+        wc.gemm(desc, a.data_ptr(), b.data_ptr(), c.data_ptr(), ws.data_ptr() if ws is not None else 0,
+                cuda.cuda.current_stream().cuda_stream)
+    finally:
+        del os.environ["WAVE_CUDA_GEMM_KERNEL"]
+    wc.check_device_status()
+    got = out_to_f32(cuda, c)
+    want = oracle.layout_output(expected(oracle, a_bits, b_bits, "f16", out_name), layout, knobs.get("bm", 1),
+                                knobs.get("bn", 1), knobs.get("wave_m_tiles", 1), knobs.get("wave_n_tiles", 1))
+    assert np.array_equal(got, want), f"max abs diff {np.nanmax(np.abs(got - want))}"
+
+
 def test_pair_kernel_is_selected_for_large_tiles(cuda, wc):
     plan = wc.gemm_plan(wc.gemm_desc(8192, 8192, 8192, bm=4, bn=4, wave_m_tiles=4, wave_n_tiles=4, in_type=wc.BF16))
     assert (plan["tile_m"], plan["tile_n"]) == (256, 256) and plan["grid"] % 2 == 0

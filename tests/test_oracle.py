@@ -232,6 +232,32 @@ def test_attention_matches_compiled_reference(oracle):
     assert np.array_equal(got, want)
 
 
+def test_fragment_output_coordinates_known_answers(oracle):
+    """Index -> (m, n) of the runner's tile-packed fragment layouts: the values
+    test/Integration/Inputs/wave_matmul_rand_int_test.cpp:112-139 checks."""
+    def coord(index, wmma, wave):
+        m, n = oracle.tile_packed_fragment_coordinate(index, 16, 16, 1, 1, 1, 1, wmma, wave)
+        return int(m), int(n)
+    assert [coord(i, False, 64) for i in (0, 3, 4, 64, 255)] == [(0, 0), (3, 0), (0, 1), (4, 0), (15, 15)]
+    assert [coord(i, True, 32) for i in (0, 7, 8, 128, 255)] == [(0, 0), (14, 0), (0, 1), (1, 0), (15, 15)]
+    assert [coord(i, False, 32) for i in (7, 128)] == [(7, 0), (8, 0)]
+
+
+@pytest.mark.parametrize("layout", ["tile-packed-mfma64", "tile-packed-wmma32", "tile-packed-mfma32"])
+def test_fragment_layouts_are_permutations_and_match_compiled_reference(oracle, layout):
+    M, N, BM, BN, wmt, wnt = 96, 128, 2, 2, 3, 2
+    wmma, wave = oracle.FRAGMENT_LAYOUTS[layout]
+    c = np.arange(M * N, dtype=np.float32).reshape(M, N)
+    packed = oracle.layout_output(c, layout, BM, BN, wmt, wnt)
+    assert sorted(packed.tolist()) == list(range(M * N))  # every coordinate exactly once (runner.cpp:846-872)
+    if oracle.ref_lib() is None:
+        pytest.skip("compiled reference not built")
+    rng = np.random.default_rng(5)
+    for index in rng.integers(0, M * N, 400).tolist() + [0, M * N - 1]:
+        m, n = oracle.ref_output_coordinate(M, N, BM, BN, wmt, wnt, wmma, wave, index)
+        assert packed[index] == c[m, n]
+
+
 def test_causal_extension_is_masked_softmax(oracle):
     """The causal extension equals the non-causal reference run on the prefix
     of keys a row may see."""
