@@ -8,12 +8,24 @@ test/Integration/wave_flash_attention_gfx950_runtime.mlir:3-22).  Causal
 masking, a caller-supplied scale, f16 I/O and ragged lengths are extensions
 and are checked against the oracle's labelled extensions.
 """
+import os
+
 import numpy as np
 import pytest
 
 from _util import to_device_bits
 
 pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(params=["pingpong", "stream"], autouse=True)
+def fa_kernel(request):
+    """Every test runs on both attention kernels (two Q tiles ping-ponging; one
+    Q tile with double-buffered scores).  Left alone, the library picks one by
+    the number of work items per SM."""
+    os.environ["WAVE_CUDA_FA_KERNEL"] = request.param
+    yield request.param
+    del os.environ["WAVE_CUDA_FA_KERNEL"]
 
 REFERENCE_MAX_ABS = 3.0e-2  # wave-fa-gfx950-runner.cpp:388
 

@@ -64,3 +64,40 @@ def test_runner_exit_codes(cuda, oracle, runner_exe):
     assert "BN must be a positive power of two" in err
     _, err = _run(runner_exe, "--rand-int", "--hpl", expect=2)
     assert "mutually exclusive" in err
+
+
+@pytest.fixture(scope="module")
+def fa_runner_exe(tmp_path_factory, wc):
+    wc.lib()  # builds libwave_cuda.so if needed
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    exe = str(tmp_path_factory.mktemp("fa_runner") / "wave_fa_runner")
+    subprocess.run([nvcc, "-std=c++17", "-O2", "-x", "cu", "-Wno-deprecated-gpu-targets",
+                    os.path.join(DRIVERS, "wave_fa_runner.cpp"), "-o", exe, "-I" + os.path.join(ROOT, "include"),
+                    "-L" + os.path.join(ROOT, "7_b200"), "-lwave_cuda", "-Xlinker=-rpath=" + os.path.join(ROOT, "7_b200")],
+                   check=True, cwd=DRIVERS)
+    return exe
+
+
+def test_fa_runner_rejects_bad_arguments(fa_runner_exe):
+    """Exit code 2 and the reference runner's messages
+    (tools/wave-fa-calibrate/wave-fa-gfx950-runner.cpp:63-66, 136-150); no GPU needed."""
+    _, err = _run(fa_runner_exe, "--sequence", "300", expect=2)
+    assert "sequence must be a multiple of 256" in err
+    _, err = _run(fa_runner_exe, "--bogus", "1", expect=2)
+    assert "unknown flag" in err
+    _, err = _run(fa_runner_exe, "--iters", "0", expect=2)
+    assert "invalid non-positive argument" in err
+    _, err = _run(fa_runner_exe, "--heads", "x", expect=2)
+    assert "bad integer argument" in err
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("extra", [(), ("--causal",), ("--zero-qk",), ("--input-scale", "2")])
+def test_fa_runner_contract(cuda, fa_runner_exe, extra):
+    """The reference runner's stdout lines and its sampled f64 check
+    (wave-fa-gfx950-runner.cpp:204-232, 388-394, 472-481)."""
+    out, _ = _run(fa_runner_exe, "--batch", "2", "--heads", "3", "--sequence", "1024", "--iters", "3", "--warmup", "1",
+                  "--check", "unused.hsaco", "flash_attention_bf16_gfx950", *extra)
+    for key in ("shape: B=2 H=3 N=1024 D=128", "grid: 4,6,1 block: ", "per_launch_us: ", "tflops: ",
+                "output_check: passed max_abs_diff="):
+        assert key in out, out
