@@ -42,6 +42,9 @@ __device__ int g_fa_stream_status[4]; // [0] code, [1] block, [2] role (20..), [
 
 #ifdef WAVE_FA_TRACE
 __device__ long long g_fas_trace[3][64][16];
+#ifdef WAVE_FA_TRACE_CLOCK_ONLY // only the start/end clock probe
+#define FAS_STAMP(role, blk, idx)
+#else
 #define FAS_STAMP(role, blk, idx)                                                                  \
   do {                                                                                             \
     if (blockIdx.x == 0 && (blk) < 64) {                                                           \
@@ -50,6 +53,7 @@ __device__ long long g_fas_trace[3][64][16];
       fa_trace_smem[((role)*64 + (blk)) * 16 + (idx)] = fa_stamp_clk;                              \
     }                                                                                              \
   } while (0)
+#endif
 #define FAS_TRACE_SMEM_BYTES (3 * 64 * 16 * 4)
 #else
 #define FAS_STAMP(role, blk, idx)                                                                  \
@@ -75,6 +79,7 @@ constexpr int kTmemCols = 512;
 constexpr uint32_t kTmemS = 0, kTmemP = 256, kTmemO = 384;
 constexpr float kRescaleThreshold = 8.0f; // log2 units (wave_flash_attention.py:563-569)
 constexpr int kStatusWaitTimeout = 1;
+constexpr uint32_t kTraceItem = 3; // which of a CTA's items the optional stage stamps record
 // setmaxnreg budget, as in fa_sm100.cu: warpgroup 0 gives registers up, the two
 // softmax warpgroups hold a 128-column score row per thread.
 constexpr int kLaunchRegs = 168;
@@ -174,6 +179,14 @@ fa_stream_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = sh->tmem_base;
+#ifdef WAVE_FA_TRACE
+  if (threadIdx.x == 64 && blockIdx.x == 0) { // SM clock against wall time over the CTA's life
+    unsigned long long ns;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(ns));
+    g_fas_trace[1][63][0] = clock64();
+    g_fas_trace[1][63][1] = static_cast<long long>(ns);
+  }
+#endif
 
   // A "previous phase" parity: waiting for the phase before the one block g (or
   // item n) completes passes at once on a barrier nobody has used yet.
@@ -299,7 +312,7 @@ fa_stream_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         bool ok = true;
         for (int j = 0; j < nb; ++j, ++g) {
           const uint32_t b = g & 1;
-          if (item_n == 0)
+          if (item_n == kTraceItem)
             FAS_STAMP(0, j, 0);
           // K(g) has landed; S[b] (scores of block g-2) has been read into registers.
           if (!mbar_wait(&sh->k_full[b], this_parity(g), abort_flag) ||
@@ -309,7 +322,7 @@ fa_stream_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             break;
           }
           tc_fence_after_sync();
-          if (item_n == 0)
+          if (item_n == kTraceItem)
             FAS_STAMP(0, j, 1);
           const uint32_t d = tmem_base + kTmemS + b * kBlockN;
           const uint32_t kb = k_lo + b * kTile16;
@@ -320,7 +333,7 @@ fa_stream_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             umma_ss_halves<1>(d, qa + off, kb + off, kDescHi, idesc_s);
           }
           umma_commit(&sh->s_full[b]);
-          if (item_n == 0)
+          if (item_n == kTraceItem)
             FAS_STAMP(0, j, 2);
         }
         if (!ok)
@@ -352,7 +365,7 @@ fa_stream_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         bool ok = true;
         for (int j = 0; j < nb; ++j, ++g) {
           const uint32_t b = g & 1;
-          if (item_n == 0)
+          if (item_n == kTraceItem)
             FAS_STAMP(0, j, 4);
           // V(g) has landed and the softmax warps have stored P(g).  The first
           // P*V of an item overwrites O: the softmax warps stored that block's P
@@ -364,7 +377,7 @@ fa_stream_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             break;
           }
           tc_fence_after_sync();
-          if (item_n == 0)
+          if (item_n == kTraceItem)
             FAS_STAMP(0, j, 5);
           // O += P[b] V(g): eight steps of 16 keys; P from TMEM (8 packed columns per step)
           const uint32_t a = tmem_base + kTmemP + b * (kBlockN / 2);
@@ -375,7 +388,7 @@ fa_stream_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             umma_ts_halves<1>(d, a + static_cast<uint32_t>(kk * 8), vb + static_cast<uint32_t>(kk * (2048 >> 4)),
                               kDescHi, idesc_o);
           umma_commit(&sh->v_empty[b]); // V's stage and P[b] may be written again
-          if (item_n == 0)
+          if (item_n == kTraceItem)
             FAS_STAMP(0, j, 6);
         }
         if (!ok)
@@ -449,7 +462,7 @@ fa_stream_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       for (int j = 0; j < nb; ++j, ++g) {
         if ((g & 1u) != static_cast<uint32_t>(wg))
           continue;
-        if (row == 0 && item_n == 0)
+        if (row == 0 && item_n == kTraceItem)
           FAS_STAMP(1 + wg, j, 0);
         if (!mbar_wait(&sh->s_full[wg], this_parity(g), abort_flag)) {
           if (lane == 0)
@@ -458,7 +471,7 @@ fa_stream_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           break;
         }
         tc_fence_after_sync();
-        if (row == 0 && item_n == 0)
+        if (row == 0 && item_n == kTraceItem)
           FAS_STAMP(1 + wg, j, 1);
         uint32_t s[128];
         tmem_ld_32x32b_x32(s_addr + 0, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
@@ -471,7 +484,7 @@ fa_stream_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         __syncwarp();
         if (lane == 0)
           mbar_arrive(&sh->s_free[wg]);
-        if (row == 0 && item_n == 0)
+        if (row == 0 && item_n == kTraceItem)
           FAS_STAMP(1 + wg, j, 2);
 
         const int key0 = j * kBlockN;
@@ -547,7 +560,7 @@ fa_stream_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         row_max[row] = m_used;
         __threadfence_block();
         row_seq[row] = g + 1;
-        if (row == 0 && item_n == 0)
+        if (row == 0 && item_n == kTraceItem)
           FAS_STAMP(1 + wg, j, 3);
         const float neg_mc = -m_used * c;
         const float2 c2 = make_float2(c, c), nm2 = make_float2(neg_mc, neg_mc);
@@ -569,7 +582,7 @@ fa_stream_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           pk[i] = pack2(pr.x, pr.y, bf16);
         }
         l += (la.x + la.y) + (lb.x + lb.y);
-        if (row == 0 && item_n == 0)
+        if (row == 0 && item_n == kTraceItem)
           FAS_STAMP(1 + wg, j, 4);
         // P[wg] must be free: P*V of block g-2 has ended (normally long ago).
         if (!mbar_wait(&sh->v_empty[wg], prev_parity(g), abort_flag)) {
@@ -585,7 +598,7 @@ fa_stream_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         __syncwarp();
         if (lane == 0)
           mbar_arrive(&sh->p_full[wg]);
-        if (row == 0 && item_n == 0)
+        if (row == 0 && item_n == kTraceItem)
           FAS_STAMP(1 + wg, j, 5);
       }
       if (!ok)
@@ -667,7 +680,14 @@ fa_stream_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #ifdef WAVE_FA_TRACE
   if (blockIdx.x == 0) {
     for (int i = threadIdx.x; i < 3 * 64 * 16; i += kThreads)
+      if (i / 16 != 64 + 63) // [1][63][*] holds the clock probe
         (&g_fas_trace[0][0][0])[i] = fa_trace_smem[i];
+  }
+  if (threadIdx.x == 64 && blockIdx.x == 0) {
+    unsigned long long ns;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(ns));
+    g_fas_trace[1][63][2] = clock64();
+    g_fas_trace[1][63][3] = static_cast<long long>(ns);
   }
 #endif
   if (warp == 1) {
