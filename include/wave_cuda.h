@@ -77,9 +77,11 @@ void *_mlir_ciface_wave_memref_to_ptr_global_f64(void *memref1d);
  * results; they choose the CTA tile:
  *   16*bm*wave_m_tiles x 16*bn*wave_n_tiles, snapped to a legal UMMA shape
  *   (rows 128; columns the next of 16/32/64/128/256).
- * Requested tiles of at least 256 x 256 on a problem with enough of them run on
- * CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles); the environment variable
- * WAVE_CUDA_GEMM_KERNEL=pair|single overrides that size heuristic.            */
+ * Requested tiles of at least 256 x 256 run on CTA pairs (tcgen05
+ * cta_group::2, 256 x 256 tiles) where those fill the machine at least as well
+ * as 128 x 256 tiles on single CTAs; the environment variables
+ * WAVE_CUDA_GEMM_KERNEL=pair|pair128|single and WAVE_CUDA_GEMM_SPLIT_TAIL=0
+ * override the choices (knobs for measurements; results do not change).       */
 typedef struct wave_gemm_desc {
   int M, N, K;                 /* positive multiples of 16 (wave_matmul.py:533-536)      */
   int bm, bn;                  /* waves per workgroup along M / N; bn a power of two      */
@@ -155,7 +157,14 @@ int wave_cuda_gemm_plan(const wave_gemm_desc *desc, int *tile_m, int *tile_n, in
  * statistics, exp2 with scale*log2(e) folded into the exponent
  * (wave_flash_attention.py:596-600), probabilities rounded to io_type before
  * P*V, output rounded once to io_type.  `causal` keeps key <= query (top-left
- * aligned; an extension, the reference's Wave kernel is non-causal).         */
+ * aligned; an extension, the reference's Wave kernel is non-causal).
+ * Two kernels compute it (256-row work items with two Q tiles ping-ponging,
+ * or 128-row work items with double-buffered scores); the library picks by the
+ * number of work items per SM, WAVE_CUDA_FA_KERNEL=pingpong|stream overrides,
+ * WAVE_CUDA_FA_POLY=0..4 sets the eighths of the exponentials evaluated as a
+ * polynomial on the FMA pipe (measurement knobs; the results agree within the
+ * rounding of the exponential).
+ */
 typedef struct wave_fa_desc {
   int batch, heads;
   int seq_q, seq_k; /* multiples of 16 */
