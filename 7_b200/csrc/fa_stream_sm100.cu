@@ -93,7 +93,7 @@ struct StreamShared {
   uint64_t q_full[2], q_empty[2];       // Q slots, by item parity
   uint64_t k_full[2], v_full[2], v_empty[2];
   uint64_t s_full[2], s_free[2], p_full[2];
-  uint64_t o_full, l_full;
+  uint64_t o_full, o_free, l_full;
   uint32_t tmem_base;
   int abort_flag;
   int item_idx[2];
@@ -163,6 +163,7 @@ fa_stream_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       mbar_init(&sh->p_full[s], 4); // the same, once its rows of P are stored
     }
     mbar_init(&sh->o_full, 1);
+    mbar_init(&sh->o_free, 8); // one lane of each softmax warp, once its part of O has been read out
     mbar_init(&sh->l_full, 8);
     sh->abort_flag = 0;
     fence_barrier_init();
@@ -367,11 +368,12 @@ fa_stream_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           const uint32_t b = g & 1;
           if (item_n == kTraceItem)
             FAS_STAMP(0, j, 4);
-          // V(g) has landed and the softmax warps have stored P(g).  The first
-          // P*V of an item overwrites O: the softmax warps stored that block's P
-          // after their epilogue of the item before, so O has been read.
+          // V(g) has landed and the block's softmax warpgroup has stored P(g).
+          // The first P*V of an item overwrites O: both warpgroups must have
+          // read the previous item's O out (only one of them stores this P).
           if (!mbar_wait(&sh->v_full[b], this_parity(g), abort_flag) ||
-              !mbar_wait(&sh->p_full[b], this_parity(g), abort_flag)) {
+              !mbar_wait(&sh->p_full[b], this_parity(g), abort_flag) ||
+              (j == 0 && item_n > 0 && !mbar_wait(&sh->o_free, (item_n - 1) & 1, abort_flag))) {
             fas_report(kStatusWaitTimeout, 2, 40 + b);
             ok = false;
             break;
@@ -669,9 +671,11 @@ fa_stream_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       }
       if (p.lse && live && wg == 0)
         p.lse[static_cast<size_t>(w.bh) * p.seq_q + q_row] = m_final * p.scale + logf(l_row);
-      // O has been read out; this thread's next P store (and the arrive after
-      // it) orders that before the next item's first P*V, which overwrites O.
+      // O has been read out: the next item's first P*V may overwrite it.
       tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0)
+        mbar_arrive(&sh->o_free);
     } // work items
   }
 
