@@ -91,7 +91,7 @@ constexpr int kTmemCols = 512;
 // S/P hand-offs between the softmax warps and the tensor core, not by the
 // special-function unit, so the default keeps every exponential on it.
 constexpr int kDefaultPoly = 0;
-constexpr int kStreamBelowItemsPerSm = 40; // 256-row items per SM below which the streaming kernel is used
+constexpr int kStreamFromSeqK = 6144; // key sequence length from which the streaming kernel is used
 constexpr float kRescaleThreshold = 8.0f;
 // setmaxnreg budget.  The kernel starts with kLaunchRegs per thread (12 warps,
 // one CTA per SM); warpgroup 0 shrinks to kIssueRegs and the two softmax
@@ -756,17 +756,16 @@ int launch_flash_attention(const FaParams &p, const void *Q, const void *K, cons
   }
   // WAVE_CUDA_FA_KERNEL=stream|pingpong picks the kernel (a knob for
   // measurements; results are the same).
-  // Which kernel: the streaming one hands out 128-row items, which balances the
-  // persistent CTAs better when there are few 256-row items per SM, and its
-  // decoupled pipeline gains more from short sequences; with plenty of items
-  // the ping-pong kernel's halved K/V traffic wins.  Measured (causal /
-  // non-causal TFLOP/s, ping-pong against streaming): B=16 H=32 S=4096 (55
-  // items per SM) 1043/1094 against 953/992; B=2 H=64 S=8192 (28) 886/1096
-  // against 1040/1080; B=32 H=32 S=1024 (28) 488/765 against 539/888.
+  // Which kernel: the streaming one pays more per work item (an epilogue and a
+  // hand-over of the row sums per 128 rows) and less per K/V block, so it wins
+  // on long sequences.  Measured back to back under the power cap, the kernels
+  // taking turns (causal / non-causal TFLOP/s, ping-pong against streaming):
+  // S=1024 (B=32 H=32) 571/841 against 535/811; S=2048 (B=8 H=32) 739/963
+  // against 724/951; S=4096 (B=16 H=32) 925/1049 against 926/1056; S=8192 (B=2
+  // H=64) 995/1085 against 1049/1111.
   {
     const char *env = getenv("WAVE_CUDA_FA_KERNEL");
-    const bool stream_kernel =
-        env ? strcmp(env, "stream") == 0 : total_items < static_cast<long long>(kStreamBelowItemsPerSm) * sm_count;
+    const bool stream_kernel = env ? strcmp(env, "stream") == 0 : p.seq_k >= kStreamFromSeqK;
     if (stream_kernel)
       return launch_flash_attention_stream(params, tq, tk, tv, poly, sm_count, stream);
   }

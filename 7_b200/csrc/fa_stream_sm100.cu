@@ -750,7 +750,7 @@ int launch_flash_attention_stream(const FaParams &p, const CUtensorMap &tq, cons
   auto dispatch = [&](auto bf16_tag) {
     constexpr bool B = decltype(bf16_tag)::value;
     // A quarter of the exponentials on the FMA pipe is this kernel's measured
-    // best (causal B=2 H=64 S=8192: 946 -> 1040 TFLOP/s); `poly` < 0 asks for it.
+    // best (causal B=2 H=64 S=8192, sustained: 893 -> 1049 TFLOP/s); `poly` < 0 asks for it.
     switch (poly) {
     case 0: launch(fa_stream_kernel<0, B>); break;
     case 1: launch(fa_stream_kernel<1, B>); break;

@@ -36,6 +36,8 @@ constexpr int kBK = 64;
 constexpr int kABytes = kRows * kBK * 2;
 constexpr int kThreads = 192;
 constexpr int kMaxStages = 8;
+constexpr int kStoreCols = 64;                      // 16-bit output columns per TMA store: 128 bytes, one swizzle row
+constexpr int kStoreTileBytes = kRows * kStoreCols * 2; // 16 KB
 
 // Per tile width PN: B rows held by one CTA, ring depth (192 KB of stages) and
 // TMEM columns (two PN-column accumulators).
@@ -45,7 +47,8 @@ template <int PN> struct PairCfg {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = PN == 256 ? 6 : 8;
   static constexpr int kTmemCols = 2 * PN;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+  // stage ring | 1 KB of barriers | two 128-row x 128-byte staging tiles of the TMA-store epilogue
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 1024 + 2 * kStoreTileBytes;
 };
 
 struct PairShared {
@@ -68,11 +71,11 @@ __device__ __forceinline__ void pair_report(int code, int role, int detail) {
 template <int OUT, int PN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const __grid_constant__ CUtensorMap tmap_b_half, const GemmParams p) {
+                 const __grid_constant__ CUtensorMap tmap_b_half, const __grid_constant__ CUtensorMap tmap_c,
+                 const GemmParams p) {
   using T = typename OutT<OUT>::type;
   using Cfg = PairCfg<PN>;
   constexpr int kPairN = PN;
-  constexpr int kBRows = Cfg::kBRows;
   constexpr int kStageBytes = Cfg::kStageBytes;
   constexpr int kStages = Cfg::kStages;
   constexpr int kTmemCols = Cfg::kTmemCols;
@@ -217,11 +220,27 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int row_in_tile = quarter * 32 + lane;
     int acc = 0;
     uint32_t acc_phase = 0;
+    uint32_t store_n = 0; // TMA stores issued so far (staging tile = parity)
+    uint8_t *store_tiles = tiles + kStages * kStageBytes + 1024;
     const uint32_t tempty_leader[2] = {map_to_cta(&sh->tempty[0], 0), map_to_cta(&sh->tempty[1], 0)};
+    // Barrier among the four epilogue warps (named barrier 1).
+    auto epilogue_barrier = [] { asm volatile("bar.sync 1, 128;" ::: "memory"); };
     for (int item = pair_id; item < num_items; item += num_pairs) {
       int mb, nb, n_off, width;
       decode(item, mb, nb, n_off, width);
-      if (!mbar_wait(&sh->tfull[acc], acc_phase, abort_flag)) {
+      bool failed = !mbar_wait(&sh->tfull[acc], acc_phase, abort_flag);
+      if (p.c_tma) {
+        // The four warps share named barriers below: they must leave together.
+        uint32_t any;
+        __syncwarp();
+        asm volatile("{\n\t.reg .pred pin, pout;\n\tsetp.ne.b32 pin, %1, 0;\n\t"
+                     "bar.red.or.pred pout, 1, 128, pin;\n\tselp.b32 %0, 1, 0, pout;\n\t}"
+                     : "=r"(any)
+                     : "r"(failed ? 1u : 0u)
+                     : "memory");
+        failed = any != 0;
+      }
+      if (failed) {
         if (lane == 0)
           pair_report(kStatusWaitTimeout, 2, 200 + acc);
         break;
@@ -230,6 +249,55 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const uint32_t taddr =
           tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * kPairN);
       const int m = mb * kPairM + static_cast<int>(rank) * kRows + row_in_tile;
+      if constexpr (sizeof(T) == 2) {
+        if (p.c_tma) {
+          // Row-major 16-bit output: 64 columns of the CTA's 128 rows at a time go
+          // through a swizzled shared-memory tile and out with one TMA store (whole
+          // 128-byte rows instead of 16 bytes per thread; the store clips at the
+          // matrix edge).  Two tiles, so that a store reads one while the four
+          // epilogue warps fill the other.
+#pragma unroll 1
+          for (int c = 0; c < width; c += kStoreCols, ++store_n) {
+            uint32_t r0[32], r1[32];
+            tmem_ld_32x32b_x32(taddr + c, r0);
+            tmem_ld_32x32b_x32(taddr + c + 32, r1);
+            tmem_ld_wait();
+            if (c + kStoreCols >= width) { // the accumulator has been read: the next tile may use it
+              tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0)
+                mbar_arrive_cluster(tempty_leader[acc]);
+            }
+            uint8_t *buf = store_tiles + (store_n & 1u) * kStoreTileBytes;
+            if (warp == 2 && lane == 0)
+              tma_store_wait_read<1>(); // the store that last used this tile has read it
+            epilogue_barrier();
+            uint8_t *row_ptr = buf + row_in_tile * (kStoreCols * 2);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              const uint32_t *src = k < 4 ? &r0[8 * k] : &r1[8 * (k - 4)];
+              T tmp[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                store_elem(&tmp[e], __uint_as_float(src[e]));
+              // 128-byte swizzle: 16-byte chunk k of row r sits at chunk k ^ (r & 7)
+              *reinterpret_cast<uint4 *>(row_ptr + ((k ^ (row_in_tile & 7)) << 4)) = *reinterpret_cast<uint4 *>(tmp);
+            }
+            fence_proxy_async_smem();
+            epilogue_barrier();
+            if (warp == 2 && lane == 0) {
+              tma_store_2d_evict_first(&tmap_c, buf, nb * kPairN + n_off + c,
+                                       mb * kPairM + static_cast<int>(rank) * kRows);
+              tma_store_commit();
+            }
+          }
+          if (++acc == 2) {
+            acc = 0;
+            acc_phase ^= 1;
+          }
+          continue;
+        }
+      }
 #pragma unroll 1
       for (int c = 0; c < width; c += 32) {
         uint32_t r[32];
@@ -250,6 +318,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         acc_phase ^= 1;
       }
     }
+    if (warp == 2 && lane == 0)
+      tma_store_wait_read<0>(); // the staging tiles must outlive the stores that read them
   }
 
   // Neither CTA may leave (or free TMEM) while its partner can still read its
@@ -266,26 +336,26 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 }
 
 template <int OUT, int PN>
-cudaError_t launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tbh, const GemmParams &p,
-                        int grid, cudaStream_t stream) {
+cudaError_t launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tbh, const CUtensorMap &tc,
+                        const GemmParams &p, int grid, cudaStream_t stream) {
   constexpr int smem = PairCfg<PN>::kSmemBytes;
   cudaError_t err = cudaFuncSetAttribute(gemm_pair_kernel<OUT, PN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (err != cudaSuccess)
     return err;
-  gemm_pair_kernel<OUT, PN><<<grid, kThreads, smem, stream>>>(ta, tb, tbh, p);
+  gemm_pair_kernel<OUT, PN><<<grid, kThreads, smem, stream>>>(ta, tb, tbh, tc, p);
   return cudaGetLastError();
 }
 
 template <int PN>
-cudaError_t launch_pair_out(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tbh, const GemmParams &p,
-                            int grid, cudaStream_t stream) {
+cudaError_t launch_pair_out(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tbh, const CUtensorMap &tc,
+                            const GemmParams &p, int grid, cudaStream_t stream) {
   switch (p.out_type) {
   case WAVE_GEMM_OUT_F32:
-    return launch_pair<WAVE_GEMM_OUT_F32, PN>(ta, tb, tbh, p, grid, stream);
+    return launch_pair<WAVE_GEMM_OUT_F32, PN>(ta, tb, tbh, tc, p, grid, stream);
   case WAVE_GEMM_OUT_F16:
-    return launch_pair<WAVE_GEMM_OUT_F16, PN>(ta, tb, tbh, p, grid, stream);
+    return launch_pair<WAVE_GEMM_OUT_F16, PN>(ta, tb, tbh, tc, p, grid, stream);
   case WAVE_GEMM_OUT_BF16:
-    return launch_pair<WAVE_GEMM_OUT_BF16, PN>(ta, tb, tbh, p, grid, stream);
+    return launch_pair<WAVE_GEMM_OUT_BF16, PN>(ta, tb, tbh, tc, p, grid, stream);
   }
   return cudaErrorInvalidValue;
 }
@@ -298,13 +368,17 @@ int gemm_pair_box_rows() { return kRows; }
 
 // `grid` must be even: consecutive CTAs form the pairs.  `tile_n` is 256 or
 // 128; the tensor map of B must have a box of tile_n / 2 rows, `tmap_b_half`
-// (read only when tile_n is 256 and p.split_from < p.num_tiles) one of 64 rows.
+// (read only when tile_n is 256 and p.split_from < p.num_tiles) one of 64 rows,
+// `tmap_c` (read only when p.c_tma is set) a box of 64 columns x 128 rows over
+// the row-major 16-bit output.  Rows of C a store may touch beyond M, and
+// columns beyond N, are clipped by the tensor map.
 cudaError_t launch_gemm_pair(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, const CUtensorMap &tmap_b_half,
-                             const GemmParams &p, int tile_n, int grid, cudaStream_t stream) {
+                             const CUtensorMap &tmap_c, const GemmParams &p, int tile_n, int grid,
+                             cudaStream_t stream) {
   if (tile_n == 256)
-    return launch_pair_out<256>(tmap_a, tmap_b, tmap_b_half, p, grid, stream);
+    return launch_pair_out<256>(tmap_a, tmap_b, tmap_b_half, tmap_c, p, grid, stream);
   if (tile_n == 128)
-    return launch_pair_out<128>(tmap_a, tmap_b, tmap_b_half, p, grid, stream);
+    return launch_pair_out<128>(tmap_a, tmap_b, tmap_b_half, tmap_c, p, grid, stream);
   return cudaErrorInvalidValue;
 }
 

@@ -30,6 +30,7 @@ struct GemmParams {
   int tile_packed, tp_bm, tp_bn, tp_wmt, tp_wnt, tp_n_blocks;
   // order of the 256 values inside a tile: 0 row-major, 1 MFMA wave64, 2 WMMA wave32, 3 MFMA wave32 fragments
   int tp_fragment;
+  int c_tma; // CTA-pair kernel: the output goes out through TMA stores (row-major 16-bit C)
 };
 
 int gemm_tile_m();
@@ -44,7 +45,8 @@ int gemm_pair_tile_m();
 int gemm_pair_tile_n();
 int gemm_pair_box_rows();
 cudaError_t launch_gemm_pair(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, const CUtensorMap &tmap_b_half,
-                             const GemmParams &p, int tile_n, int grid, cudaStream_t stream);
+                             const CUtensorMap &tmap_c, const GemmParams &p, int tile_n, int grid,
+                             cudaStream_t stream);
 cudaError_t gemm_pair_read_status(int out[4], bool clear);
 
 } // namespace wave

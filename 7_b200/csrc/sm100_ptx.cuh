@@ -129,6 +129,16 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap *tmap, const void
                "r"(smem_u32(smem_src)), "r"(x), "r"(y)
                : "memory");
 }
+// The same store with an L2 "evict first" hint: output that nobody reads again
+// should not push the operand panels other CTAs still share out of L2.
+__device__ __forceinline__ void tma_store_2d_evict_first(const CUtensorMap *tmap, const void *smem_src, int x,
+                                                         int y) {
+  asm volatile("{\n\t.reg .b64 pol;\n\tcreatepolicy.fractional.L2::evict_first.b64 pol, 1.0;\n\t"
+               "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], pol;\n\t}" ::
+                   "l"(reinterpret_cast<uint64_t>(tmap)),
+               "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+}
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap *tmap, const void *smem_src, int x, int y,
                                              int z) {
   asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(

@@ -80,8 +80,9 @@ void *_mlir_ciface_wave_memref_to_ptr_global_f64(void *memref1d);
  * Requested tiles of at least 256 x 256 run on CTA pairs (tcgen05
  * cta_group::2, 256 x 256 tiles) where those fill the machine at least as well
  * as 128 x 256 tiles on single CTAs; the environment variables
- * WAVE_CUDA_GEMM_KERNEL=pair|pair128|single and WAVE_CUDA_GEMM_SPLIT_TAIL=0
- * override the choices (knobs for measurements; results do not change).       */
+ * WAVE_CUDA_GEMM_KERNEL=pair|pair128|single, WAVE_CUDA_GEMM_SPLIT_TAIL=0 and
+ * WAVE_CUDA_GEMM_TMA_STORE=0 override the choices (knobs for measurements;
+ * results do not change).                                                    */
 typedef struct wave_gemm_desc {
   int M, N, K;                 /* positive multiples of 16 (wave_matmul.py:533-536)      */
   int bm, bn;                  /* waves per workgroup along M / N; bn a power of two      */
