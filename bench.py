@@ -41,7 +41,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # the same kernel (summaries under profiles/): gemm and skinny at full size; fa
 # captured at B=2 (250.58 MB) and scaled by the 8x heads of the B=16 workload,
 # since every head moves the same bytes.
-NCU_TRAFFIC_BYTES = {"gemm": 1203.57e6, "fa": 8 * 250.58e6, "skinny": 477.11e6}
+NCU_TRAFFIC_BYTES = {"gemm": 1203.57e6, "fa": 8 * 251.89e6, "skinny": 477.11e6}
 
 WORKLOADS = {
     "gemm": dict(name="gemm_bf16_8192x8192x8192_f32acc_bf16out", M=8192, N=8192, K=8192),
