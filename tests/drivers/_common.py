@@ -51,6 +51,28 @@ def time_launches(torch, fn, warmup: int, iters: int) -> float:
     return e0.elapsed_time(e1)
 
 
+def time_sustained(torch, fn, seconds: float, batch: int = 50):
+    """Back-to-back launches for at least `seconds` of GPU time (the part
+    settles at the clock its power cap allows only after a fraction of a
+    second, so a short loop overstates what it holds); batches of launches
+    between two events, the first quarter of the batches left out.  Returns
+    (milliseconds per launch, launches timed)."""
+    per = []
+    total_ms = 0.0
+    while total_ms < seconds * 1e3:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(batch):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        per.append(ms / batch)
+        total_ms += ms
+    kept = per[len(per) // 4:]
+    return statistics.median(kept), len(kept) * batch
+
+
 def median(values):
     return statistics.median(values)
 

@@ -17,7 +17,7 @@ import sys
 
 import numpy as np
 
-from _common import dev_bits, load, median, time_launches
+from _common import dev_bits, load, median, time_launches, time_sustained
 
 
 def parse(argv):
@@ -30,6 +30,8 @@ def parse(argv):
     p.add_argument("--iters", type=int, default=20)
     p.add_argument("--warmup", type=int, default=5)
     p.add_argument("--repeats", type=int, default=1)
+    p.add_argument("--sustained-seconds", type=float, default=0.0,
+                   help="also time a back-to-back loop of at least this long (the clock the power cap allows)")
     p.add_argument("--check", action="store_true")
     p.add_argument("--zero-qk", action="store_true")
     p.add_argument("--causal", action="store_true")
@@ -74,6 +76,11 @@ def main(argv=None) -> int:
         print(f"tflops: {done / t * 1e-6:.3f}")
     if args.causal:
         print(f"tflops_full_square_formula: {full / median(us) * 1e-6:.3f}")
+    if args.sustained_seconds > 0:
+        sus_ms, sus_n = time_sustained(torch, launch, args.sustained_seconds, batch=10)
+        print(f"sustained_per_launch_us: {sus_ms * 1e3:.3f}")
+        print(f"sustained_tflops: {done / (sus_ms * 1e3) * 1e-6:.3f}")
+        print(f"sustained_launches: {sus_n}")
     if args.check:
         heads, rows = oracle.fa_sample_heads(args.batch * args.heads), oracle.fa_sample_rows(args.sequence)
         scale = args.scale if args.scale > 0 else 1.0 / np.sqrt(128.0)

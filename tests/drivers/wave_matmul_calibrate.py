@@ -17,7 +17,7 @@ import time
 
 import numpy as np
 
-from _common import add_ignored_flags, dev_bits, load, median, note_ignored, time_launches
+from _common import time_sustained, add_ignored_flags, dev_bits, load, median, note_ignored, time_launches
 
 MODE_NAMES = {0: "lcg", 1: "all_ones", 2: "rand_int", 3: "hpl"}
 
@@ -46,6 +46,8 @@ def parse(argv):
     p.add_argument("--iters", type=int, default=1000)
     p.add_argument("--warmup", type=int, default=10)
     p.add_argument("--repeats", type=int, default=1)
+    p.add_argument("--sustained-seconds", type=float, default=0.0,
+                   help="also time a back-to-back loop of at least this long (the clock the power cap allows)")
     p.add_argument("--seed", type=int, default=0)
     p.add_argument("--all-ones", action="store_true")
     p.add_argument("--rand-int", action="store_true")
@@ -132,6 +134,11 @@ def main(argv=None) -> int:
         print(f"best_per_launch_us: {min(times) * 1e3 / args.iters:.3f}")
     print(f"tflops: {tflops:.3f}")
     print(f"roofline_fraction: {tflops / 2250.0:.4f} (of 2250 TFLOP/s nominal dense bf16/f16)")
+    if args.sustained_seconds > 0:
+        sus_ms, sus_n = time_sustained(torch, launch, args.sustained_seconds)
+        print(f"sustained_per_launch_us: {sus_ms * 1e3:.3f}")
+        print(f"sustained_tflops: {2.0 * args.m * args.n * args.k / (sus_ms * 1e3) * 1e-6:.3f}")
+        print(f"sustained_launches: {sus_n}")
     if not args.no_check:
         rows = None
         if args.check_rows and args.check_rows < args.m:

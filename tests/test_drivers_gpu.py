@@ -67,6 +67,17 @@ def test_gemm_calibrate_runner_tile_packed_fragments(cuda, flags, layout):
     assert f"output_check: passed mode=strict layout={layout} elements=32768" in out, out
 
 
+def test_calibrate_tools_sustained_loop(cuda):
+    """The >= N s back-to-back loop next to the 200-launch timing (the clock the
+    power cap allows shows only after a fraction of a second)."""
+    out, _ = run("wave_matmul_calibrate.py", "--m=1024", "--n=1024", "--k=1024", "--bm=4", "--bn=4", "--wave-m-tiles=2",
+                 "--wave-n-tiles=4", "--iters=5", "--warmup=1", "--no-check", "--sustained-seconds=0.2")
+    assert "sustained_per_launch_us: " in out and "sustained_tflops: " in out, out
+    out, _ = run("wave_fa_gfx950.py", "--batch=1", "--heads=4", "--sequence=1024", "--iters=3", "--warmup=1",
+                 "--sustained-seconds=0.2")
+    assert "sustained_per_launch_us: " in out and "sustained_tflops: " in out, out
+
+
 def test_gemm_calibrate_runner_streamk(cuda):
     out, _ = run("wave_matmul_calibrate.py", "--m=512", "--n=512", "--k=2048", "--bm=4", "--bn=4", "--wave-m-tiles=2",
                  "--wave-n-tiles=4", "--hpl", "--input-type=bf16", "--kernel-abi=streamk", "--streamk-workers=5",
