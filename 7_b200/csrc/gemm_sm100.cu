@@ -33,6 +33,8 @@ constexpr int kBK = 64;       // 64 16-bit elements = one 128-byte swizzle row
 constexpr int kUmmaK = 16;    // K per tcgen05.mma for 16-bit operands
 constexpr int kThreads = 192; // 6 warps
 constexpr int kEpiThreads = 128;
+constexpr int kStoreCols = 64;                         // 16-bit output columns per TMA store: one 128-byte swizzle row
+constexpr int kStoreTileBytes = kBM * kStoreCols * 2; // 16 KB
 
 template <int BN> struct TileCfg {
   static constexpr int kStages = BN >= 256 ? 4 : BN >= 128 ? 6 : BN >= 64 ? 8 : 10;
@@ -41,8 +43,10 @@ template <int BN> struct TileCfg {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kAccCols = BN < 32 ? 32 : BN; // TMEM columns per accumulator buffer
   static constexpr int kTmemCols = 2 * kAccCols < 32 ? 32 : 2 * kAccCols;
-  // tiles + barriers + bookkeeping + slack for 1024-byte alignment
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+  // Two 128-row x 128-byte staging tiles of the TMA-store epilogue (tiles of at least 64 columns).
+  static constexpr int kStoreBytes = BN >= 64 ? 2 * kStoreTileBytes : 0;
+  // slack for 1024-byte alignment + stage ring + 1 KB of barriers and bookkeeping + staging tiles
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + 1024 + kStoreBytes;
 };
 
 struct Shared {
@@ -136,7 +140,7 @@ struct WorkIter {
 template <int BN, int OUT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-            const GemmParams p) {
+            const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
   using Cfg = TileCfg<BN>;
   using T = typename OutT<OUT>::type;
   constexpr int kStages = Cfg::kStages;
@@ -265,11 +269,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     Segment seg;
     int acc = 0;
     uint32_t acc_phase = 0;
+    uint32_t store_n = 0; // TMA stores issued so far (staging tile = parity)
+    uint8_t *store_tiles = tiles + kStages * Cfg::kStageBytes + 1024;
     const long long total_iters = static_cast<long long>(p.num_tiles - p.dp_tiles) * p.k_iters; // Stream-K part
     while (work.next(seg)) {
       int mb, nb;
       tile_coords(seg.tile, p.num_m_blocks, p.num_n_blocks, p.group_m, mb, nb);
-      if (!mbar_wait(&sh->tfull[acc], acc_phase, abort_flag)) {
+      bool failed = !mbar_wait(&sh->tfull[acc], acc_phase, abort_flag);
+      {
+        // The four warps meet at named barriers below: they must leave together.
+        uint32_t any;
+        __syncwarp();
+        asm volatile("{\n\t.reg .pred pin, pout;\n\tsetp.ne.b32 pin, %1, 0;\n\t"
+                     "bar.red.or.pred pout, 1, %2, pin;\n\tselp.b32 %0, 1, 0, pout;\n\t}"
+                     : "=r"(any)
+                     : "r"(failed ? 1u : 0u), "n"(kEpiThreads)
+                     : "memory");
+        failed = any != 0;
+      }
+      if (failed) {
         if (lane == 0)
           report(kStatusWaitTimeout, 2, 200 + acc);
         break;
@@ -279,6 +297,53 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                              static_cast<uint32_t>(acc * Cfg::kAccCols);
       const int m = mb * kBM + row_in_tile;
       const bool whole = seg.k_begin == 0 && seg.k_end == p.k_iters;
+      if constexpr (sizeof(T) == 2 && BN >= 64) {
+        if (whole && p.c_tma) {
+          // Row-major 16-bit output: 64 columns of the tile's 128 rows at a time go
+          // through a swizzled shared-memory tile and out with one TMA store
+          // (whole 128-byte rows instead of 16 bytes per thread; clipped at the
+          // matrix edge).  Two tiles: a store reads one while the other is filled.
+#pragma unroll 1
+          for (int c = 0; c < BN; c += kStoreCols, ++store_n) {
+            uint32_t r0[32], r1[32];
+            tmem_ld_32x32b_x32(taddr + c, r0);
+            tmem_ld_32x32b_x32(taddr + c + 32, r1);
+            tmem_ld_wait();
+            if (c + kStoreCols >= BN) { // the accumulator has been read: the next tile may use it
+              tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0)
+                mbar_arrive(&sh->tempty[acc]);
+            }
+            uint8_t *buf = store_tiles + (store_n & 1u) * kStoreTileBytes;
+            if (epi_tid == 0)
+              tma_store_wait_read<1>(); // the store that last used this tile has read it
+            asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+            uint8_t *row_ptr = buf + row_in_tile * (kStoreCols * 2);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              const uint32_t *src = k < 4 ? &r0[8 * k] : &r1[8 * (k - 4)];
+              T tmp[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                store_elem(&tmp[e], __uint_as_float(src[e]));
+              // 128-byte swizzle: 16-byte chunk k of row r sits at chunk k ^ (r & 7)
+              *reinterpret_cast<uint4 *>(row_ptr + ((k ^ (row_in_tile & 7)) << 4)) = *reinterpret_cast<uint4 *>(tmp);
+            }
+            fence_proxy_async_smem();
+            asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+            if (epi_tid == 0) {
+              tma_store_2d_evict_first(&tmap_c, buf, nb * BN + c, mb * kBM);
+              tma_store_commit();
+            }
+          }
+          if (++acc == 2) {
+            acc = 0;
+            acc_phase ^= 1;
+          }
+          continue;
+        }
+      }
       if (whole) {
 #pragma unroll 1
         for (int c = 0; c < BN; c += CW) {
@@ -362,6 +427,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         acc_phase ^= 1;
       }
     }
+    if (epi_tid == 0)
+      tma_store_wait_read<0>(); // the staging tiles must outlive the stores that read them
   }
 
   tc_fence_before_sync();
@@ -374,8 +441,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 }
 
 template <int BN, int OUT>
-cudaError_t launch_one(const CUtensorMap &ta, const CUtensorMap &tb, const GemmParams &p, int grid,
-                       cudaStream_t stream) {
+cudaError_t launch_one(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc, const GemmParams &p,
+                       int grid, cudaStream_t stream) {
   using Cfg = TileCfg<BN>;
   // The attribute belongs to the current device's context, so it is set on
   // every launch rather than cached per process.
@@ -383,20 +450,20 @@ cudaError_t launch_one(const CUtensorMap &ta, const CUtensorMap &tb, const GemmP
       cudaFuncSetAttribute(gemm_kernel<BN, OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
   if (err != cudaSuccess)
     return err;
-  gemm_kernel<BN, OUT><<<grid, kThreads, Cfg::kSmemBytes, stream>>>(ta, tb, p);
+  gemm_kernel<BN, OUT><<<grid, kThreads, Cfg::kSmemBytes, stream>>>(ta, tb, tc, p);
   return cudaGetLastError();
 }
 
 template <int BN>
-cudaError_t launch_bn(const CUtensorMap &ta, const CUtensorMap &tb, const GemmParams &p, int grid,
-                      cudaStream_t stream) {
+cudaError_t launch_bn(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc, const GemmParams &p,
+                      int grid, cudaStream_t stream) {
   switch (p.out_type) {
   case WAVE_GEMM_OUT_F32:
-    return launch_one<BN, WAVE_GEMM_OUT_F32>(ta, tb, p, grid, stream);
+    return launch_one<BN, WAVE_GEMM_OUT_F32>(ta, tb, tc, p, grid, stream);
   case WAVE_GEMM_OUT_F16:
-    return launch_one<BN, WAVE_GEMM_OUT_F16>(ta, tb, p, grid, stream);
+    return launch_one<BN, WAVE_GEMM_OUT_F16>(ta, tb, tc, p, grid, stream);
   case WAVE_GEMM_OUT_BF16:
-    return launch_one<BN, WAVE_GEMM_OUT_BF16>(ta, tb, p, grid, stream);
+    return launch_one<BN, WAVE_GEMM_OUT_BF16>(ta, tb, tc, p, grid, stream);
   }
   return cudaErrorInvalidValue;
 }
@@ -406,19 +473,21 @@ cudaError_t launch_bn(const CUtensorMap &ta, const CUtensorMap &tb, const GemmPa
 int gemm_tile_m() { return kBM; }
 int gemm_tile_k() { return kBK; }
 
-cudaError_t launch_gemm(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, const GemmParams &p, int tile_n,
-                        int grid, cudaStream_t stream) {
+// `tmap_c` is read only when p.c_tma is set (tile_n >= 64): a box of 64 columns
+// x 128 rows over the row-major 16-bit output.
+cudaError_t launch_gemm(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, const CUtensorMap &tmap_c,
+                        const GemmParams &p, int tile_n, int grid, cudaStream_t stream) {
   switch (tile_n) {
   case 16:
-    return launch_bn<16>(tmap_a, tmap_b, p, grid, stream);
+    return launch_bn<16>(tmap_a, tmap_b, tmap_c, p, grid, stream);
   case 32:
-    return launch_bn<32>(tmap_a, tmap_b, p, grid, stream);
+    return launch_bn<32>(tmap_a, tmap_b, tmap_c, p, grid, stream);
   case 64:
-    return launch_bn<64>(tmap_a, tmap_b, p, grid, stream);
+    return launch_bn<64>(tmap_a, tmap_b, tmap_c, p, grid, stream);
   case 128:
-    return launch_bn<128>(tmap_a, tmap_b, p, grid, stream);
+    return launch_bn<128>(tmap_a, tmap_b, tmap_c, p, grid, stream);
   case 256:
-    return launch_bn<256>(tmap_a, tmap_b, p, grid, stream);
+    return launch_bn<256>(tmap_a, tmap_b, tmap_c, p, grid, stream);
   }
   return cudaErrorInvalidValue;
 }

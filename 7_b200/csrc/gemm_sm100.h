@@ -30,13 +30,13 @@ struct GemmParams {
   int tile_packed, tp_bm, tp_bn, tp_wmt, tp_wnt, tp_n_blocks;
   // order of the 256 values inside a tile: 0 row-major, 1 MFMA wave64, 2 WMMA wave32, 3 MFMA wave32 fragments
   int tp_fragment;
-  int c_tma; // CTA-pair kernel: the output goes out through TMA stores (row-major 16-bit C)
+  int c_tma; // whole tiles leave through TMA stores (row-major 16-bit C, tiles of at least 64 columns)
 };
 
 int gemm_tile_m();
 int gemm_tile_k();
-cudaError_t launch_gemm(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, const GemmParams &p, int tile_n,
-                        int grid, cudaStream_t stream);
+cudaError_t launch_gemm(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, const CUtensorMap &tmap_c,
+                        const GemmParams &p, int tile_n, int grid, cudaStream_t stream);
 cudaError_t gemm_read_status(int out[4], bool clear);
 
 // CTA-pair kernel (256 x 256 or 256 x 128 tiles, tcgen05 cta_group::2);

@@ -588,10 +588,11 @@ int wave_cuda_gemm(const wave_gemm_desc *d, const void *A, const void *B, void *
   p.scratch = static_cast<float *>(workspace);
   p.counters = workspace ? reinterpret_cast<int *>(static_cast<char *>(workspace) + plan.scratch_bytes) : nullptr;
 
-  // Row-major 16-bit output of the pair kernel leaves through TMA stores
+  // Row-major 16-bit output (tiles of at least 64 columns) leaves through TMA stores
   // (WAVE_CUDA_GEMM_TMA_STORE=0 keeps the per-thread stores, for measurements).
   CUtensorMap tc = ta;
-  if (plan.pair && d->out_layout == WAVE_ROW_MAJOR && d->out_type != WAVE_F32) {
+  if ((plan.pair || (!plan.swapped && plan.tile_n >= 64)) && d->out_layout == WAVE_ROW_MAJOR &&
+      d->out_type != WAVE_F32) {
     const char *env = getenv("WAVE_CUDA_GEMM_TMA_STORE");
     if (!(env && strcmp(env, "0") == 0)) {
       const uint64_t dims[2] = {static_cast<uint64_t>(d->N), static_cast<uint64_t>(d->M)};
@@ -603,7 +604,7 @@ int wave_cuda_gemm(const wave_gemm_desc *d, const void *A, const void *B, void *
     }
   }
   cudaError_t err = plan.pair ? wave::launch_gemm_pair(ta, tb, tbh, tc, p, plan.tile_n, plan.grid, static_cast<cudaStream_t>(stream))
-                              : wave::launch_gemm(ta, tb, p, plan.tile_n, plan.grid, static_cast<cudaStream_t>(stream));
+                              : wave::launch_gemm(ta, tb, tc, p, plan.tile_n, plan.grid, static_cast<cudaStream_t>(stream));
   if (err != cudaSuccess)
     return cuda_fail(err, "gemm launch");
   return WAVE_OK;
