@@ -189,3 +189,24 @@ def test_host_buffer_call_pipelined_by_head_groups(cuda, wc, oracle):
     check(got[np.ix_(hs, rs)], want, "host pipelined")
     dev = run_fa(cuda, wc, q, k, v, "bf16", 4, 16, True)
     assert np.array_equal(got, dev)
+
+
+def test_launches_overlapping_on_two_streams(cuda, wc, oracle):
+    """Launches that overlap on the GPU (two streams) each draw their work items
+    from a counter of their own; both results must be the single-stream ones."""
+    t = oracle.BF16
+    BH, S = 8, 1024
+    q, k, v = normal_qkv(oracle, BH, S, S, 128, t, seed=41)
+    want = run_fa(cuda, wc, q, k, v, "bf16", 2, 4, True)
+    desc = wc.fa_desc(2, 4, S, S, 128, causal=True, io_type=wc.TYPE_BY_NAME["bf16"])
+    dq, dk, dv = (to_device_bits(cuda, x) for x in (q, k, v))
+    streams = [cuda.cuda.Stream(), cuda.cuda.Stream()]
+    outs = [cuda.empty((BH, S, 128), dtype=cuda.bfloat16, device="cuda") for _ in streams]
+    cuda.cuda.synchronize()
+    for _ in range(20):
+        for st, o in zip(streams, outs):
+            wc.flash_attention_fwd(desc, dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), o.data_ptr(), 0, st.cuda_stream)
+    cuda.cuda.synchronize()
+    wc.check_device_status()
+    for o in outs:
+        assert np.array_equal(o.float().cpu().numpy(), want)
