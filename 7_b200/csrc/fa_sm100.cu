@@ -92,6 +92,7 @@ constexpr int kTmemCols = 512;
 // special-function unit, so the default keeps every exponential on it.
 constexpr int kDefaultPoly = 0;
 constexpr int kStreamFromSeqK = 6144; // key sequence length from which the streaming kernel is used
+constexpr int kStreamFromSeqKFixedRef = 2048; // the same with a fixed softmax reference
 constexpr float kRescaleThreshold = 8.0f;
 // setmaxnreg budget.  The kernel starts with kLaunchRegs per thread (12 warps,
 // one CTA per SM); warpgroup 0 shrinks to kIssueRegs and the two softmax
@@ -515,8 +516,10 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     const int bh = w.bh;
     const int q_row = w.q_blk * 2 * kBlockM + t * kBlockM + row;
     const int nb = w.n_blocks[t];
-    float m_used = -INFINITY; // running maximum the exponentials are taken against (raw score units)
-    float l = 0.0f;           // running sum of unrounded probabilities
+    // Maximum the exponentials are taken against (raw score units): the running
+    // row maximum, or with a fixed reference the caller's bound for the whole item.
+    float m_used = p.fixed_ref ? p.ref_log2 / c : -INFINITY;
+    float l = 0.0f; // running sum of unrounded probabilities
 
     for (int j = 0; j < nb; ++j) {
       if (row == 0 && item_n == 0)
@@ -549,42 +552,44 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           if (key0 + i > limit)
             s[i] = 0xFF800000u; // -inf
       }
-      // Sixteen independent chains: a three-input maximum has a long latency
-      // (a chain of 16 took ~245 cycles), so the depth is kept at four.
-      float mx[16];
+      if (!p.fixed_ref) {
+        // Sixteen independent chains: a three-input maximum has a long latency
+        // (a chain of 16 took ~245 cycles), so the depth is kept at four.
+        float mx[16];
 #pragma unroll
-      for (int i = 0; i < 16; ++i)
-        mx[i] = fmaxf(__uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1]));
+        for (int i = 0; i < 16; ++i)
+          mx[i] = fmaxf(__uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1]));
 #pragma unroll
-      for (int i = 32; i < 128; i += 32)
+        for (int i = 32; i < 128; i += 32)
 #pragma unroll
-        for (int k = 0; k < 16; ++k)
-          mx[k] = max3(mx[k], __uint_as_float(s[i + 2 * k]), __uint_as_float(s[i + 2 * k + 1]));
+          for (int k = 0; k < 16; ++k)
+            mx[k] = max3(mx[k], __uint_as_float(s[i + 2 * k]), __uint_as_float(s[i + 2 * k + 1]));
 #pragma unroll
-      for (int k = 0; k < 5; ++k)
-        mx[k] = max3(mx[k], mx[5 + 2 * k], mx[6 + 2 * k]);
-      mx[0] = max3(mx[0], mx[1], mx[2]);
-      mx[3] = max3(mx[3], mx[4], mx[15]);
-      const float m_new = max3(m_used, mx[0], mx[3]);
-      // Lazy rescale: only when some row of this warp moved its maximum by more
-      // than 2^8; otherwise keep the stale maximum (exact after the final divide).
-      const bool need = (m_new - m_used) * c > kRescaleThreshold;
-      if (__any_sync(0xffffffffu, need)) {
-        const float factor = fast_exp2((m_used - m_new) * c);
-        l *= factor;
-        if (j > 0) {
+        for (int k = 0; k < 5; ++k)
+          mx[k] = max3(mx[k], mx[5 + 2 * k], mx[6 + 2 * k]);
+        mx[0] = max3(mx[0], mx[1], mx[2]);
+        mx[3] = max3(mx[3], mx[4], mx[15]);
+        const float m_new = max3(m_used, mx[0], mx[3]);
+        // Lazy rescale: only when some row of this warp moved its maximum by more
+        // than 2^8; otherwise keep the stale maximum (exact after the final divide).
+        const bool need = (m_new - m_used) * c > kRescaleThreshold;
+        if (__any_sync(0xffffffffu, need)) {
+          const float factor = fast_exp2((m_used - m_new) * c);
+          l *= factor;
+          if (j > 0) {
 #pragma unroll 1
-          for (int cc = 0; cc < kD; cc += 32) {
-            uint32_t o[32];
-            tmem_ld_32x32b_x32(o_addr + cc, o);
-            tmem_ld_wait();
+            for (int cc = 0; cc < kD; cc += 32) {
+              uint32_t o[32];
+              tmem_ld_32x32b_x32(o_addr + cc, o);
+              tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
-            tmem_st_32x32b_x32(o_addr + cc, o);
+              for (int i = 0; i < 32; ++i)
+                o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+              tmem_st_32x32b_x32(o_addr + cc, o);
+            }
           }
+          m_used = m_new;
         }
-        m_used = m_new;
       }
       if (row == 0 && item_n == 0)
         FA_STAMP(1 + t, j, 3);
@@ -762,10 +767,15 @@ int launch_flash_attention(const FaParams &p, const void *Q, const void *K, cons
   // taking turns (causal / non-causal TFLOP/s, ping-pong against streaming):
   // S=1024 (B=32 H=32) 571/841 against 535/811; S=2048 (B=8 H=32) 739/963
   // against 724/951; S=4096 (B=16 H=32) 925/1049 against 926/1056; S=8192 (B=2
-  // H=64) 995/1085 against 1049/1111.
+  // H=64) 995/1085 against 1049/1111.  With a fixed softmax reference the
+  // streaming kernel's warpgroups no longer hand the row maximum to each other
+  // and it wins from 2048 keys on (the same shapes, ping-pong against streaming:
+  // 599/857 against 580/843; 760/967 against 774/988; 927/1064 against 962/1093;
+  // 998/1089 against 1072/1151).
   {
     const char *env = getenv("WAVE_CUDA_FA_KERNEL");
-    const bool stream_kernel = env ? strcmp(env, "stream") == 0 : p.seq_k >= kStreamFromSeqK;
+    const bool stream_kernel = env ? strcmp(env, "stream") == 0
+                                   : p.seq_k >= (p.fixed_ref ? kStreamFromSeqKFixedRef : kStreamFromSeqK);
     if (stream_kernel)
       return launch_flash_attention_stream(params, tq, tk, tv, poly, sm_count, stream);
   }

@@ -413,6 +413,8 @@ fa_stream_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const int wg = (warp - 4) >> 2; // parity of the blocks this thread takes; also its half of O in the epilogue
     const int row = quarter * 32 + lane;
     const float c = p.scale_log2e;
+    // Fixed reference in score units (ref_log2 is in units of the exponent), or none.
+    const float m_fixed = p.fixed_ref ? p.ref_log2 / c : -INFINITY;
     constexpr bool bf16 = kBf16;
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t s_addr = tmem_base + lane_base + kTmemS + static_cast<uint32_t>(wg * kBlockN);
@@ -458,7 +460,7 @@ fa_stream_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const StreamItem w = decode_item(idx, p);
       const int q_row = w.q_blk * kBlockM + row;
       const int nb = w.n_blocks;
-      float m_seen = -INFINITY; // the row maximum this thread's sum l is relative to
+      float m_seen = m_fixed; // the row maximum this thread's sum l is relative to
       float l = 0.0f;           // sum of the unrounded probabilities of this thread's blocks
 
       for (int j = 0; j < nb; ++j, ++g) {
@@ -498,70 +500,77 @@ fa_stream_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             if (key0 + i > limit)
               s[i] = 0xFF800000u; // -inf
         }
-        float mx[8];
-#pragma unroll
-        for (int k = 0; k < 8; ++k)
-          mx[k] = fmaxf(__uint_as_float(s[2 * k]), __uint_as_float(s[2 * k + 1]));
-#pragma unroll
-        for (int i = 16; i < 128; i += 16)
+        // With a fixed reference (the caller's bound on |q| and |k|) there is no
+        // maximum to find, hand over or rescale by.
+        float m_used = m_fixed;
+        if (!p.fixed_ref) {
+          float mx[8];
 #pragma unroll
           for (int k = 0; k < 8; ++k)
-            mx[k] = max3(mx[k], __uint_as_float(s[i + 2 * k]), __uint_as_float(s[i + 2 * k + 1]));
-        const float m_blk = max3(max3(mx[0], mx[1], mx[2]), max3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7]));
-        // The maximum in use after the blocks before this one (none for the
-        // first block of an item).
-        float m_prev = -INFINITY;
-        if (!max_before(g, m_prev)) {
-          if (lane == 0)
-            fas_report(kStatusWaitTimeout, 3 + wg, 63);
-          ok = false;
-          break;
-        }
-        if (j == 0)
-          m_prev = -INFINITY;
-        // The other thread of the row may have raised the maximum since this
-        // thread last added to its sum.
-        if (m_prev != m_seen) {
-          l *= fast_exp2((m_seen - m_prev) * c); // m_seen = -inf only with l = 0
-          if (m_seen == -INFINITY)
-            l = 0.0f;
-        }
-        float m_used = m_prev;
-        const float m_new = fmaxf(m_prev, m_blk);
-        // Lazy rescale: only when some row of this warp moved its maximum by more
-        // than 2^8; otherwise keep the stale maximum (exact after the final divide).
-        const bool need = (m_new - m_prev) * c > kRescaleThreshold;
-        if (__any_sync(0xffffffffu, need)) {
-          const float factor = fast_exp2((m_prev - m_new) * c);
-          l *= factor;
-          if (j > 0) {
-            // O must be at rest: P*V of block g-1 has ended (its commit says so)
-            // and P*V of block g waits for this block's P.
-            if (!mbar_wait(&sh->v_empty[(g - 1) & 1], this_parity(g - 1), abort_flag)) {
-              if (lane == 0)
-                fas_report(kStatusWaitTimeout, 3 + wg, 61);
-              ok = false;
-              break;
-            }
-            tc_fence_after_sync();
-#pragma unroll 1
-            for (int cc = 0; cc < kD; cc += 32) {
-              uint32_t o[32];
-              tmem_ld_32x32b_x32(o_addr + cc, o);
-              tmem_ld_wait();
+            mx[k] = fmaxf(__uint_as_float(s[2 * k]), __uint_as_float(s[2 * k + 1]));
 #pragma unroll
-              for (int i = 0; i < 32; ++i)
-                o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
-              tmem_st_32x32b_x32(o_addr + cc, o);
-            }
+          for (int i = 16; i < 128; i += 16)
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+              mx[k] = max3(mx[k], __uint_as_float(s[i + 2 * k]), __uint_as_float(s[i + 2 * k + 1]));
+          const float m_blk = max3(max3(mx[0], mx[1], mx[2]), max3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7]));
+          // The maximum in use after the blocks before this one (none for the
+          // first block of an item).
+          float m_prev = -INFINITY;
+          if (!max_before(g, m_prev)) {
+            if (lane == 0)
+              fas_report(kStatusWaitTimeout, 3 + wg, 63);
+            ok = false;
+            break;
           }
-          m_used = m_new;
+          if (j == 0)
+            m_prev = -INFINITY;
+          // The other thread of the row may have raised the maximum since this
+          // thread last added to its sum.
+          if (m_prev != m_seen) {
+            l *= fast_exp2((m_seen - m_prev) * c); // m_seen = -inf only with l = 0
+            if (m_seen == -INFINITY)
+              l = 0.0f;
+          }
+          m_used = m_prev;
+          const float m_new = fmaxf(m_prev, m_blk);
+          // Lazy rescale: only when some row of this warp moved its maximum by more
+          // than 2^8; otherwise keep the stale maximum (exact after the final divide).
+          const bool need = (m_new - m_prev) * c > kRescaleThreshold;
+          if (__any_sync(0xffffffffu, need)) {
+            const float factor = fast_exp2((m_prev - m_new) * c);
+            l *= factor;
+            if (j > 0) {
+              // O must be at rest: P*V of block g-1 has ended (its commit says so)
+              // and P*V of block g waits for this block's P.
+              if (!mbar_wait(&sh->v_empty[(g - 1) & 1], this_parity(g - 1), abort_flag)) {
+                if (lane == 0)
+                  fas_report(kStatusWaitTimeout, 3 + wg, 61);
+                ok = false;
+                break;
+              }
+              tc_fence_after_sync();
+#pragma unroll 1
+              for (int cc = 0; cc < kD; cc += 32) {
+                uint32_t o[32];
+                tmem_ld_32x32b_x32(o_addr + cc, o);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+                tmem_st_32x32b_x32(o_addr + cc, o);
+              }
+            }
+            m_used = m_new;
+          }
         }
         m_seen = m_used;
-        // Publish the decision: the other thread of the row may now decide about block g+1.
-        row_max[row] = m_used;
-        __threadfence_block();
-        row_seq[row] = g + 1;
+        if (!p.fixed_ref) {
+          // Publish the decision: the other thread of the row may now decide about block g+1.
+          row_max[row] = m_used;
+          __threadfence_block();
+          row_seq[row] = g + 1;
+        }
         if (row == 0 && item_n == kTraceItem)
           FAS_STAMP(1 + wg, j, 3);
         const float neg_mc = -m_used * c;
@@ -608,8 +617,8 @@ fa_stream_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
       // ---- epilogue: O / l, this thread's 64 columns of its row.  g now counts
       // all blocks of the item: bring this thread's sum to the final maximum.
-      float m_final = -INFINITY;
-      if (!max_before(g, m_final)) {
+      float m_final = m_fixed;
+      if (!p.fixed_ref && !max_before(g, m_final)) {
         if (lane == 0)
           fas_report(kStatusWaitTimeout, 3 + wg, 64);
         break;
@@ -755,6 +764,7 @@ int launch_flash_attention_stream(const FaParams &p, const CUtensorMap &tq, cons
     case 0: launch(fa_stream_kernel<0, B>); break;
     case 1: launch(fa_stream_kernel<1, B>); break;
     case 3: launch(fa_stream_kernel<3, B>); break;
+    case 4: launch(fa_stream_kernel<4, B>); break;
     default: launch(fa_stream_kernel<2, B>); break;
     }
   };

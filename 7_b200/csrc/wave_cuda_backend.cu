@@ -719,6 +719,15 @@ int wave_cuda_gemm_host(const wave_gemm_desc *d, const void *A_host, const void 
 }
 
 // ------------------------------------------------------------ flash attention
+// log2(e) * head_dim * scale * qk_max_abs^2: the largest scaled score, in log2
+// units, that entries bounded by qk_max_abs can give (amd_fa_wave.py:1599-1601;
+// with the default scale this is the log2(e) * sqrt(128) * qk_max_abs^2 of
+// wave_flash_attention.py:108-113).
+static double fa_log2_score_bound(const wave_fa_desc &d) {
+  const double scale = d.scale > 0.0f ? static_cast<double>(d.scale) : 1.0 / std::sqrt(static_cast<double>(d.head_dim));
+  return 1.4426950408889634 * d.head_dim * scale * static_cast<double>(d.qk_max_abs) * static_cast<double>(d.qk_max_abs);
+}
+
 int wave_cuda_fa_validate(const wave_fa_desc *d) {
   if (!d)
     return fail(WAVE_E_INVALID, "descriptor is null");
@@ -735,6 +744,13 @@ int wave_cuda_fa_validate(const wave_fa_desc *d) {
     return fail(WAVE_E_UNSUPPORTED, "causal attention requires seq_q == seq_k; got %d and %d", d->seq_q, d->seq_k);
   if (!(d->scale >= 0.0f) || std::isinf(d->scale))
     return fail(WAVE_E_INVALID, "scale must be finite and >= 0 (0 selects 1/sqrt(head_dim))");
+  if (d->qk_max_abs != 0.0f) {
+    // wave_flash_attention.py:64-75, amd_fa_wave.py:1592-1610
+    if (!(d->qk_max_abs > 0.0f) || std::isinf(d->qk_max_abs))
+      return fail(WAVE_E_INVALID, "qk_max_abs must be finite and positive; got %g", static_cast<double>(d->qk_max_abs));
+    if (2.0 * fa_log2_score_bound(*d) >= 126.0)
+      return fail(WAVE_E_INVALID, "qk_max_abs fixed reference exceeds BF16 range; use adaptive reference");
+  }
   return WAVE_OK;
 }
 
@@ -759,6 +775,8 @@ int wave_cuda_flash_attention_fwd(const wave_fa_desc *d, const void *Q, const vo
   const double scale = d->scale > 0.0f ? static_cast<double>(d->scale) : 1.0 / std::sqrt(static_cast<double>(d->head_dim));
   p.scale = static_cast<float>(scale);
   p.scale_log2e = static_cast<float>(scale * 1.4426950408889634);
+  p.fixed_ref = d->qk_max_abs > 0.0f ? 1 : 0;
+  p.ref_log2 = p.fixed_ref ? static_cast<float>(fa_log2_score_bound(*d)) : 0.0f;
   p.O = O;
   p.lse = lse;
   int sms = 0;

@@ -39,11 +39,19 @@ def flops(batch: int, heads: int, sequence: int, head_dim: int = HEAD_DIM, causa
     return 4.0 * batch * heads * head_dim * pairs
 
 
-def attention(q, k, v, sm_scale: float | None = None, causal: bool = False, *, out=None, lse=None):
+_F32_MIN_NORMAL = 1.1754943508222875e-38
+
+
+def attention(q, k, v, sm_scale: float | None = None, causal: bool = False, *, qk_max_abs: float | None = None,
+              out=None, lse=None):
     """Flash-attention forward on CUDA tensors of shape (B, H, N, D), bf16 or
-    f16, contiguous, same device.  `sm_scale` defaults to 1/sqrt(D).  `out` may
-    alias `q` only in the sense of being a distinct tensor of the same shape;
-    returns `out`."""
+    f16, contiguous, same device.  `sm_scale` defaults to 1/sqrt(D) and may be
+    any finite number, as in the reference.
+    `qk_max_abs`, a bound on the absolute values in q and k, selects the
+    fixed-reference softmax of the reference's operator
+    (integrations/tlx/workloads/amd_fa_wave.py:1671-1696): no running row
+    maximum; None keeps the adaptive one.  `out` may alias `q` only in the sense
+    of being a distinct tensor of the same shape; returns `out`."""
     import torch
 
     if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
@@ -62,8 +70,24 @@ def attention(q, k, v, sm_scale: float | None = None, causal: bool = False, *, o
         out = torch.empty_like(q)
     elif out.shape != q.shape or out.dtype != q.dtype or not out.is_contiguous():
         raise ValueError("out must match q in shape and dtype and be contiguous")
-    desc = wc.fa_desc(B, H, Nq, Nk, D, scale=float(sm_scale) if sm_scale is not None else 1.0 / math.sqrt(D),
-                      causal=causal, io_type=wc.BF16 if q.dtype == torch.bfloat16 else wc.F16)
+    # amd_fa_wave.py:1582-1611 (_resolve_softmax_reference): any finite scale,
+    # the bound checked against |scale|.
+    scale = 1.0 / math.sqrt(D) if sm_scale is None else float(sm_scale)
+    if not math.isfinite(scale):
+        raise ValueError("sm_scale must be finite")
+    if qk_max_abs is not None and not (math.isfinite(qk_max_abs) and qk_max_abs > 0):
+        raise ValueError("qk_max_abs must be finite and greater than zero")
+    bound = 0.0 if qk_max_abs is None else float(qk_max_abs)
+    # The kernels take a positive scale.  softmax(-|s| q.k) is softmax(|s| (-q).k),
+    # and negating 16-bit floats is exact; with scale 0 every visible key weighs
+    # the same, which is what zero queries give at any scale (the bound then has
+    # nothing left to bound).
+    if abs(scale) < _F32_MIN_NORMAL:  # zero, or a scale the f32 arithmetic would flush to zero
+        q, scale, bound = torch.zeros_like(q), 1.0, 0.0
+    elif scale < 0.0:
+        q, scale = -q, -scale
+    desc = wc.fa_desc(B, H, Nq, Nk, D, scale=scale, causal=causal,
+                      io_type=wc.BF16 if q.dtype == torch.bfloat16 else wc.F16, qk_max_abs=bound)
     try:
         wc.fa_validate(desc)
     except wc.WaveCudaError as err:

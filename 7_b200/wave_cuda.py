@@ -39,7 +39,7 @@ class GemmDesc(C.Structure):
 class FaDesc(C.Structure):
     _fields_ = [("batch", C.c_int), ("heads", C.c_int), ("seq_q", C.c_int), ("seq_k", C.c_int),
                 ("head_dim", C.c_int), ("scale", C.c_float), ("causal", C.c_int), ("io_type", C.c_int),
-                ("out_f32", C.c_int)]
+                ("out_f32", C.c_int), ("qk_max_abs", C.c_float)]
 
 
 EXPORTS = [
@@ -139,8 +139,9 @@ def gemm_host(desc: GemmDesc, a_ptr: int, b_ptr: int, c_ptr: int, stream: int = 
 
 
 def fa_desc(batch: int, heads: int, seq_q: int, seq_k: int, head_dim: int = 128, *, scale: float = 0.0,
-            causal: bool = False, io_type: int = BF16, out_f32: bool = False) -> FaDesc:
-    return FaDesc(batch, heads, seq_q, seq_k, head_dim, scale, int(causal), io_type, int(out_f32))
+            causal: bool = False, io_type: int = BF16, out_f32: bool = False, qk_max_abs: float = 0.0) -> FaDesc:
+    """`qk_max_abs` > 0 selects the fixed-reference softmax (a bound on |q| and |k| entries)."""
+    return FaDesc(batch, heads, seq_q, seq_k, head_dim, scale, int(causal), io_type, int(out_f32), qk_max_abs)
 
 
 def fa_validate(desc: FaDesc) -> None:

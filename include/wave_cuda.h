@@ -178,6 +178,13 @@ typedef struct wave_fa_desc {
   int io_type;      /* WAVE_BF16 | WAVE_F16 */
   int out_f32;      /* non-zero: O is f32 (the toy kernel `flash_attention_f32`, f16 in /
                        f32 out, wave_attention.py:18); zero: O has io_type */
+  float qk_max_abs; /* 0: adaptive running row maximum.  > 0: a bound on |q| and |k|
+                       entries that selects the reference's fixed-reference
+                       specialisation (wave_flash_attention.py:50, 64-75, 108-113,
+                       602-609; amd_fa_wave.py:1582-1611): every exponential is taken
+                       against the constant log2(e) * head_dim * scale * qk_max_abs^2,
+                       no row maximum is searched and the accumulator is never
+                       rescaled.  Twice that constant must stay below 126. */
 } wave_fa_desc;
 
 int wave_cuda_fa_validate(const wave_fa_desc *desc);

@@ -1,8 +1,8 @@
 #!/usr/bin/env python
 """Drop-in for the reference's flash-attention calibrate tool
 (tools/wave-fa-calibrate/wave-fa-gfx950.py + wave-fa-gfx950-runner.cpp) on B200:
---batch --heads --sequence --seed --input-scale --check --zero-qk --iters
---warmup --repeats (wave-fa-gfx950.py:95-128), plus --causal and --scale, which
+--batch --heads --sequence --qk-max-abs --seed --input-scale --check --zero-qk
+--iters --warmup --repeats (wave-fa-gfx950.py:95-128), plus --causal and --scale, which
 the reference's Wave kernel does not have.  Prints the runner's keys (`shape:`,
 `grid:`, `per_launch_us:`, `tflops:`, `output_check: passed max_abs_diff=...`,
 `median_per_launch_us:`, `median_tflops:`; wave-fa-gfx950-runner.cpp:465-481,
@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import argparse
 import importlib
+import math
 import sys
 
 import numpy as np
@@ -25,6 +26,7 @@ def parse(argv):
     p.add_argument("--batch", type=int, default=1)
     p.add_argument("--heads", type=int, default=1)
     p.add_argument("--sequence", type=int, default=256)
+    p.add_argument("--qk-max-abs", type=float, default=None, help="use fixed softmax reference for |Q|,|K| <= VALUE")
     p.add_argument("--seed", type=int, default=0)
     p.add_argument("--input-scale", type=int, default=1)
     p.add_argument("--iters", type=int, default=20)
@@ -38,7 +40,13 @@ def parse(argv):
     p.add_argument("--scale", type=float, default=0.0, help="softmax scale; 0 = 1/sqrt(128)")
     p.add_argument("--waves", type=int, default=None, help="AMD-only; accepted and ignored")
     p.add_argument("--threads", type=int, default=None, help="AMD-only; accepted and ignored")
-    return p.parse_args(argv)
+    args = p.parse_args(argv)
+    if args.qk_max_abs is not None:  # wave-fa-gfx950.py:70-78
+        if not math.isfinite(args.qk_max_abs) or args.qk_max_abs <= 0:
+            p.error("--qk-max-abs must be finite and positive")
+        if args.qk_max_abs < args.input_scale:
+            p.error("--qk-max-abs must cover the generated input range")
+    return args
 
 
 def main(argv=None) -> int:
@@ -54,7 +62,12 @@ def main(argv=None) -> int:
         k[:] = 0
     dq, dk, dv = (dev_bits(torch, x) for x in (q, k, v))
     o = torch.zeros(q.shape, dtype=torch.bfloat16, device="cuda")
-    desc = wc.fa_desc(args.batch, args.heads, args.sequence, args.sequence, 128, scale=args.scale, causal=args.causal)
+    desc = wc.fa_desc(args.batch, args.heads, args.sequence, args.sequence, 128, scale=args.scale, causal=args.causal,
+                      qk_max_abs=args.qk_max_abs or 0.0)
+    try:
+        wc.fa_validate(desc)
+    except wc.WaveCudaError as err:  # the reference's builder raises here (wave-fa-gfx950.py:176-177)
+        raise SystemExit(err.message) from err
     stream = torch.cuda.current_stream().cuda_stream
 
     def launch():

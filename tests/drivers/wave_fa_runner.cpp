@@ -38,6 +38,7 @@ struct Options {
   int batch = 1, heads = 1, sequence = 256;
   int seed = 0, iters = 20, warmup = 5, repeats = 1, input_scale = 1;
   bool check = false, zero_qk = false, causal = false;
+  float qk_max_abs = 0.0f; // 0: running row maximum; > 0: fixed softmax reference for |Q|,|K| <= this
 };
 
 int bad_arguments(const std::string &message) {
@@ -76,6 +77,16 @@ int parse(int argc, char **argv, Options *o) {
           return bad_arguments("missing flag value");
         value = argv[i];
       }
+      if (arg == "--qk-max-abs") {
+        // The reference bakes the bound into the code object (wave-fa-gfx950.py:103-107,
+        // 169-176); there is no code object here, so the runner takes it itself.
+        char *end = nullptr;
+        const double bound = std::strtod(value.c_str(), &end);
+        if (value.empty() || !end || *end != '\0' || !std::isfinite(bound) || bound <= 0)
+          return bad_arguments("--qk-max-abs must be finite and positive");
+        o->qk_max_abs = static_cast<float>(bound);
+        continue;
+      }
       int ignored = 0;
       int *dst = arg == "--batch"         ? &o->batch
                  : arg == "--heads"       ? &o->heads
@@ -102,6 +113,8 @@ int parse(int argc, char **argv, Options *o) {
     return bad_arguments("invalid non-positive argument");
   if (o->sequence % kRowsPerWorkgroup)
     return bad_arguments("sequence must be a multiple of 256");
+  if (o->qk_max_abs > 0.0f && o->qk_max_abs < static_cast<float>(o->input_scale))
+    return bad_arguments("--qk-max-abs must cover the generated input range"); // wave-fa-gfx950.py:77-78
   return 0;
 }
 
@@ -215,6 +228,7 @@ int main(int argc, char **argv) {
   desc.causal = o.causal ? 1 : 0;
   desc.io_type = WAVE_BF16;
   desc.out_f32 = 0;
+  desc.qk_max_abs = o.qk_max_abs;
   void *fn = nullptr;
   const int found = wave_cuda_module_get_function(o.kernel.c_str(), &desc, &fn);
   if (found == WAVE_E_INVALID || found == WAVE_E_UNSUPPORTED)

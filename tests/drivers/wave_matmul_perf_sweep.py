@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import argparse
 import csv
+import math
 import os
 import re
 import shlex
@@ -43,8 +44,12 @@ def main() -> int:
     ap.add_argument("--csv", default=os.path.join(os.getcwd(), "wave_b200_perf_sweep.csv"))
     ap.add_argument("--input-mode", choices=["rand-int", "hpl", "lcg"], default="rand-int")
     ap.add_argument("--check-rows", type=int, default=16)
+    ap.add_argument("--fa-qk-max-abs", type=float, default=1.0,
+                    help="fixed-reference |Q|,|K| bound for the bounded attention rows (wave-matmul-perf-sweep.py:887-892)")
     ap.add_argument("--quick", action="store_true", help="fewer repeats and launches, for a smoke run")
     args = ap.parse_args()
+    if not math.isfinite(args.fa_qk_max_abs) or args.fa_qk_max_abs <= 0:
+        raise SystemExit("--fa-qk-max-abs must be finite and positive")  # wave-matmul-perf-sweep.py:1046-1047
     if args.quick:
         args.iters, args.warmup, args.repeats = 20, 5, 3
     timing = ["--iters", str(args.iters), "--warmup", str(args.warmup), "--repeats", str(args.repeats)]
@@ -65,15 +70,19 @@ def main() -> int:
         gemm("f16-gemm", "b200-f16-auto", 4096, 4096, k, "f16", "f16")
     gemm("f16-gemm", "b200-f16-pair256", 8192, 8192, 8192, "f16", "f16")
     gemm("bf16-gemm", "b200-bf16-pair256", 8192, 8192, 8192, "bf16", "bf16")
-    for causal in (False, True):
+    # The reference times its attention kernel with the fixed softmax reference
+    # (bounded) and with the running maximum (adaptive):
+    # integrations/tlx/workloads/run_wave_perf_sweeps.py:428.
+    for mode, causal in (("bounded", False), ("adaptive", False), ("bounded", True), ("adaptive", True)):
         cmd = [sys.executable, os.path.join(HERE, "wave_fa_gfx950.py"), "--batch", "2", "--heads", "64", "--sequence", "8192",
-               "--check", *timing] + (["--causal"] if causal else [])
+               "--check", *timing] + (["--qk-max-abs", f"{args.fa_qk_max_abs:g}"] if mode == "bounded" else []) + (
+                   ["--causal"] if causal else [])
         us, tf, check, rc, err = run(cmd)
         if rc:
             sys.stderr.write(err)
-        rows.append(["fa-bf16" + ("-causal" if causal else ""), "b200-fa-256x128", "", "", "", "scheduled", args.iters,
-                     args.warmup, args.repeats, us, tf, "", check, rc, shlex.join(cmd), "flash-attention", 2, 64, 8192, 128,
-                     "", ""])
+        rows.append(["fa-bf16-" + mode + ("-causal" if causal else ""), "b200-fa-256x128", "", "", "", "scheduled",
+                     args.iters, args.warmup, args.repeats, us, tf, "", check, rc, shlex.join(cmd), "flash-attention", 2,
+                     64, 8192, 128, "", ""])
     with open(args.csv, "w", newline="", encoding="utf-8") as f:
         w = csv.writer(f)
         w.writerow(COLUMNS)

@@ -97,6 +97,14 @@ def test_streamk_workspace_sizes(wc, oracle):
     (dict(io_type=2), "io_type must be bf16 or f16"),
     (dict(causal=True, seq_k=512), "causal attention requires seq_q == seq_k"),
     (dict(scale=-1.0), "scale must be finite"),
+    # wave_flash_attention.py:64-75
+    (dict(qk_max_abs=-1.0), "qk_max_abs must be finite and positive; got -1"),
+    (dict(qk_max_abs=float("inf")), "qk_max_abs must be finite and positive; got inf"),
+    (dict(qk_max_abs=float("nan")), "qk_max_abs must be finite and positive; got nan"),
+    (dict(qk_max_abs=2.0), "qk_max_abs fixed reference exceeds BF16 range; use adaptive reference"),
+    # the first bf16 value whose score span passes 126 at scale 1/sqrt(128) (test_backend.py:10217-10224)
+    (dict(qk_max_abs=1.96875), "qk_max_abs fixed reference exceeds BF16 range"),
+    (dict(qk_max_abs=1.0, scale=1.0), "qk_max_abs fixed reference exceeds BF16 range"),
 ])
 def test_attention_validation_messages(wc, kwargs, message):
     base = dict(batch=1, heads=2, seq_q=256, seq_k=256, head_dim=128)
@@ -105,6 +113,16 @@ def test_attention_validation_messages(wc, kwargs, message):
         wc.fa_validate(wc.fa_desc(base.pop("batch"), base.pop("heads"), base.pop("seq_q"), base.pop("seq_k"),
                                   base.pop("head_dim"), **base))
     assert message in err.value.message
+
+
+@pytest.mark.parametrize("kwargs", [
+    dict(qk_max_abs=1.0),                      # the bound the reference's published numbers use
+    dict(qk_max_abs=1.9609375),                # the last bf16 value inside the span (test_backend.py:10217)
+    dict(qk_max_abs=8.0, scale=1.0 / 1024.0),  # a small scale widens the admissible bound
+    dict(qk_max_abs=0.0),                      # 0 = adaptive reference
+])
+def test_fixed_reference_bounds_that_pass(wc, kwargs):
+    wc.fa_validate(wc.fa_desc(1, 2, 256, 256, 128, **kwargs))
 
 
 def test_memref_shims_return_data_plus_offset(wc):

@@ -100,3 +100,11 @@ def test_attention_calibrate_runner(cuda):
     assert "output_check: passed" in out
     _, err = run("wave_fa_gfx950.py", "--sequence=300", expect=2)
     assert "multiple of 256" in err
+    # the fixed softmax reference the reference's published numbers use (wave-fa-gfx950.py:103-107)
+    out, _ = run("wave_fa_gfx950.py", "--batch=1", "--heads=2", "--sequence=1024", "--iters=3", "--warmup=1", "--check",
+                 "--qk-max-abs=1")
+    assert "output_check: passed" in out
+    _, err = run("wave_fa_gfx950.py", "--qk-max-abs=1", "--input-scale=2", expect=2)
+    assert "--qk-max-abs must cover the generated input range" in err
+    _, err = run("wave_fa_gfx950.py", "--qk-max-abs=2", "--input-scale=2", expect=1)
+    assert "qk_max_abs fixed reference exceeds BF16 range" in err

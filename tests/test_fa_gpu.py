@@ -31,12 +31,12 @@ REFERENCE_MAX_ABS = 3.0e-2  # wave-fa-gfx950-runner.cpp:388
 
 
 def run_fa(torch, wc, q_bits, k_bits, v_bits, io_name, batch, heads, causal, scale=0.0, want_lse=False,
-           out_f32=False):
+           out_f32=False, qk_max_abs=0.0):
     BH, Sq, D = q_bits.shape
     Sk = k_bits.shape[1]
     assert BH == batch * heads
     desc = wc.fa_desc(batch, heads, Sq, Sk, D, scale=scale, causal=causal, io_type=wc.TYPE_BY_NAME[io_name],
-                      out_f32=out_f32)
+                      out_f32=out_f32, qk_max_abs=qk_max_abs)
     q, k, v = (to_device_bits(torch, x) for x in (q_bits, k_bits, v_bits))
     dt = torch.float32 if out_f32 else torch.bfloat16 if io_name == "bf16" else torch.float16
     o = torch.full((BH, Sq, D), float("nan"), dtype=dt, device="cuda")
@@ -118,6 +118,70 @@ def test_f16_io_and_custom_scale(cuda, wc, oracle):
     got = run_fa(cuda, wc, q, k, v, "f16", 2, 1, True, scale=0.05)
     want = oracle.fa_ref(q, k, v, t, float(np.float32(0.05)), causal=True)
     check(got, want, "f16")
+
+
+@pytest.mark.parametrize("S,causal,io_name,bound", [
+    (256, False, "bf16", 1.0),
+    (512, True, "bf16", 1.0),
+    (1024, False, "bf16", 1.5),
+    (768, True, "bf16", 1.9609375),   # the widest bound the span check admits
+    (1280, True, "f16", 1.0),
+])
+def test_fixed_reference_matches_the_softmax(cuda, wc, oracle, S, causal, io_name, bound):
+    """`qk_max_abs` replaces the running row maximum by a constant
+    (wave_flash_attention.py:108-113, 602-609); the result is the same softmax.
+    Runner inputs with --input-scale=1, whose Q and K reach 1 in magnitude
+    (the range the reference's driver wants covered, wave-fa-gfx950.py:77-78)."""
+    BH, D = 2, 128
+    t = oracle.BF16 if io_name == "bf16" else oracle.F16
+    q, k, v = lcg_qkv(oracle, BH, S, S, D, t, seed=S)
+    assert np.abs(oracle.from_bits(q, t)).max() <= 1.0 and np.abs(oracle.from_bits(k, t)).max() <= 1.0
+    got, lse = run_fa(cuda, wc, q, k, v, io_name, 1, BH, causal, want_lse=True, qk_max_abs=bound)
+    want, want_lse = oracle.fa_ref(q, k, v, t, 1.0 / np.sqrt(128.0), causal=causal, want_lse=True)
+    check(got, want, f"fixed reference S={S} causal={causal} bound={bound}")
+    assert np.abs(lse.astype(np.float64) - want_lse).max() <= 2e-3
+
+
+def test_fixed_reference_ragged_and_small_inputs(cuda, wc, oracle):
+    """Uniform [-1, 1) inputs under the bound 1, lengths that are not multiples
+    of the 128-row tiles, separate query and key lengths."""
+    t = oracle.BF16
+    for Sq, Sk, causal in ((144, 400, False), (272, 272, True), (16, 16, True), (400, 144, False)):
+        q = oracle.baseline_inputs((3, Sq, 128), "uniform", Sq, 0, t)
+        k = oracle.baseline_inputs((3, Sk, 128), "uniform", Sq, 1, t)
+        v = oracle.baseline_inputs((3, Sk, 128), "uniform", Sq, 2, t)
+        got = run_fa(cuda, wc, q, k, v, "bf16", 1, 3, causal, qk_max_abs=1.0)
+        want = oracle.fa_ref(q, k, v, t, 1.0 / np.sqrt(128.0), causal=causal)
+        check(got, want, f"fixed reference {Sq}x{Sk} causal={causal}")
+
+
+def test_fixed_reference_at_the_edge_of_the_bf16_range(cuda, wc, oracle):
+    """All scores at minus the bound, with the largest bf16 bound the span
+    check admits at scale 1/sqrt(128): the probabilities are 2^-125.5, still
+    normal bf16 numbers, and every output row is the mean of V
+    (integrations/tlx/tests/test_backend.py:10207-10257)."""
+    BH, S, D, t = 1, 256, 128, oracle.BF16
+    bound = 1.9609375
+    q = oracle.to_bits(np.full((BH, S, D), bound, dtype=np.float32), t)
+    k = oracle.to_bits(np.full((BH, S, D), -bound, dtype=np.float32), t)
+    v = oracle.baseline_inputs((BH, S, D), "uniform", 0, 2, t)
+    got = run_fa(cuda, wc, q, k, v, "bf16", 1, 1, False, qk_max_abs=bound)
+    mean = oracle.from_bits(v, t).astype(np.float64).mean(axis=1, keepdims=True)
+    assert np.isfinite(got).all()
+    assert np.abs(got - mean).max() <= 2e-2
+
+
+def test_fixed_reference_long_sequence_sampled(cuda, wc, oracle):
+    """The perf-golden shape's sequence length (B2 H64 N8192 runs with
+    --qk-max-abs=1, test_gfx950_fa_b2_h64_n8192_d128_bf16_8wave.py:44) on 2
+    heads, on the runner's sample of rows."""
+    t = oracle.BF16
+    BH, S = 2, 8192
+    q, k, v = lcg_qkv(oracle, BH, S, S, 128, t, seed=17)
+    got = run_fa(cuda, wc, q, k, v, "bf16", 1, BH, False, qk_max_abs=1.0)
+    hs, rs = list(range(BH)), oracle.fa_sample_rows(S)
+    want = oracle.fa_ref(q, k, v, t, 1.0 / np.sqrt(128.0), causal=False, heads=hs, rows=rs)
+    check(got[np.ix_(hs, rs)], want, "fixed reference S=8192")
 
 
 @pytest.mark.parametrize("causal", [False, True])
@@ -210,3 +274,67 @@ def test_launches_overlapping_on_two_streams(cuda, wc, oracle):
     wc.check_device_status()
     for o in outs:
         assert np.array_equal(o.float().cpu().numpy(), want)
+
+
+def _operator_case(cuda, oracle, q_bits, k_bits, v_bits, **kwargs):
+    """Runs the torch-tensor operator (the mirror of the reference's
+    `attention`, integrations/tlx/workloads/amd_fa_wave.py:1671-1720) on
+    (1, H, N, D) tensors built from bit patterns; returns f32 [H, N, D]."""
+    import importlib
+    wa = importlib.import_module("7_b200.wave_attention")
+    q, k, v = (to_device_bits(cuda, x).view(cuda.bfloat16).unsqueeze(0) for x in (q_bits, k_bits, v_bits))
+    out = wa.attention(q, k, v, **kwargs)
+    cuda.cuda.synchronize()
+    importlib.import_module("7_b200.wave_cuda").check_device_status()
+    return out[0].float().cpu().numpy()
+
+
+@pytest.mark.parametrize("mode,sm_scale,qk_max_abs", [
+    ("adaptive-negative", -1.0 / np.sqrt(128.0), None),
+    ("bounded-negative", -0.3357431655837235, 1.0),
+    ("adaptive-zero", 0.0, None),
+    ("bounded-negative-zero", -0.0, 1.0),
+    ("adaptive-positive", 0.05, None),
+])
+def test_operator_signed_scale(cuda, oracle, mode, sm_scale, qk_max_abs):
+    """Any finite softmax scale, as the reference's operator takes it: constant
+    queries, keys whose sign flips every 32 tokens, values the opposite sign
+    (integrations/tlx/tests/test_backend.py:10281-10333)."""
+    t, S, D = oracle.BF16, 256, 128
+    magnitude = 2.0 if mode == "adaptive-negative" else 1.0
+    sign = np.where(np.arange(S) % 64 < 32, magnitude, -magnitude).astype(np.float32)
+    q = oracle.to_bits(np.full((1, S, D), magnitude, np.float32), t)
+    k = oracle.to_bits(np.broadcast_to(sign[None, :, None], (1, S, D)), t)
+    v = oracle.to_bits(np.broadcast_to(np.where(sign > 0, -1.0, 1.0).astype(np.float32)[None, :, None], (1, S, D)), t)
+    got = _operator_case(cuda, oracle, q, k, v, sm_scale=sm_scale, qk_max_abs=qk_max_abs)
+    want = oracle.fa_ref(q, k, v, t, float(sm_scale), causal=False)
+    assert np.isfinite(got).all()
+    assert np.abs(got - want).max() <= 2e-2  # the reference's tolerance for this case
+
+
+@pytest.mark.parametrize("qk_max_abs", [None, 1.0], ids=["adaptive", "bounded"])
+@pytest.mark.parametrize("causal", [False, True])
+def test_operator_runner_inputs(cuda, oracle, qk_max_abs, causal):
+    t = oracle.BF16
+    q, k, v = lcg_qkv(oracle, 3, 512, 512, 128, t, seed=11)
+    got = _operator_case(cuda, oracle, q, k, v, causal=causal, qk_max_abs=qk_max_abs)
+    want = oracle.fa_ref(q, k, v, t, 1.0 / np.sqrt(128.0), causal=causal)
+    check(got, want, f"operator causal={causal} bound={qk_max_abs}")
+
+
+def test_operator_rejects_what_the_reference_rejects(cuda, oracle):
+    """amd_fa_wave.py:1582-1611; test_backend.py:10195-10202, 10260-10277."""
+    import importlib
+    wa = importlib.import_module("7_b200.wave_attention")
+    x = cuda.zeros((1, 1, 256, 128), dtype=cuda.bfloat16, device="cuda")
+    for bad in (float("inf"), float("-inf"), float("nan")):
+        with pytest.raises(ValueError, match="sm_scale must be finite"):
+            wa.attention(x, x, x, sm_scale=bad)
+        with pytest.raises(ValueError, match="qk_max_abs must be finite and greater than zero"):
+            wa.attention(x, x, x, qk_max_abs=bad)
+    with pytest.raises(ValueError, match="qk_max_abs must be finite and greater than zero"):
+        wa.attention(x, x, x, qk_max_abs=0.0)
+    with pytest.raises(ValueError, match="fixed reference exceeds BF16 range"):
+        wa.attention(x, x, x, qk_max_abs=2.0)
+    with pytest.raises(ValueError, match="CUDA tensors"):
+        wa.attention(x.cpu(), x.cpu(), x.cpu())

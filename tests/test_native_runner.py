@@ -89,10 +89,16 @@ def test_fa_runner_rejects_bad_arguments(fa_runner_exe):
     assert "invalid non-positive argument" in err
     _, err = _run(fa_runner_exe, "--heads", "x", expect=2)
     assert "bad integer argument" in err
+    # tools/wave-fa-calibrate/wave-fa-gfx950.py:70-78
+    _, err = _run(fa_runner_exe, "--qk-max-abs", "-1", expect=2)
+    assert "--qk-max-abs must be finite and positive" in err
+    _, err = _run(fa_runner_exe, "--qk-max-abs", "1", "--input-scale", "2", expect=2)
+    assert "--qk-max-abs must cover the generated input range" in err
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("extra", [(), ("--causal",), ("--zero-qk",), ("--input-scale", "2")])
+@pytest.mark.parametrize("extra", [(), ("--causal",), ("--zero-qk",), ("--input-scale", "2"), ("--qk-max-abs", "1"),
+                                   ("--qk-max-abs=1.5", "--causal")])
 def test_fa_runner_contract(cuda, fa_runner_exe, extra):
     """The reference runner's stdout lines and its sampled f64 check
     (wave-fa-gfx950-runner.cpp:204-232, 388-394, 472-481)."""
