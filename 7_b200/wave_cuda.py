@@ -52,7 +52,15 @@ EXPORTS = [
     "wave_cuda_gemm_host", "wave_cuda_gemm_plan", "wave_cuda_gemm_streamk_static", "wave_cuda_fa_validate", "wave_cuda_flash_attention_fwd",
     "wave_cuda_flash_attention_fwd_host", "wave_cuda_module_get_function", "wave_cuda_launch",
     "wave_cuda_function_release", "wave_cuda_check_device_status",
+    # include/wave_mgpu.h: the wrappers a host module lowered by gpu-to-llvm calls
+    "wave_cuda_module_blob_bytes", "wave_cuda_module_blob_write", "wave_cuda_mgpu_status",
+    "mgpuModuleLoad", "mgpuModuleUnload", "mgpuModuleGetFunction", "mgpuLaunchKernel", "mgpuStreamCreate",
+    "mgpuStreamDestroy", "mgpuStreamSynchronize", "mgpuStreamWaitEvent", "mgpuEventCreate", "mgpuEventDestroy",
+    "mgpuEventSynchronize", "mgpuEventRecord", "mgpuMemAlloc", "mgpuMemFree", "mgpuMemcpy", "mgpuMemset32",
+    "mgpuMemset16", "mgpuMemHostRegister", "mgpuMemHostUnregister", "mgpuMemHostRegisterMemRef",
+    "mgpuMemHostUnregisterMemRef", "mgpuSetDefaultDevice",
 ]
+BLOB_GEMM, BLOB_FA = 0, 1
 
 _lib = None
 
@@ -88,8 +96,37 @@ def lib() -> C.CDLL:
     L.wave_cuda_function_release.argtypes = [vp]
     L.wave_cuda_function_release.restype = None
     L.wave_cuda_check_device_status.argtypes = [ip]
+    ll, sz = C.c_int64, C.c_size_t
+    L.wave_cuda_module_blob_bytes.argtypes = [C.c_uint32, C.POINTER(sz)]
+    L.wave_cuda_module_blob_write.argtypes = [C.c_uint32, vp, vp, sz]
+    L.wave_cuda_mgpu_status.argtypes = []
+    for name, res, args in [
+            ("mgpuModuleLoad", vp, [vp, sz]), ("mgpuModuleUnload", None, [vp]),
+            ("mgpuModuleGetFunction", vp, [vp, C.c_char_p]),
+            ("mgpuLaunchKernel", None, [vp, ll, ll, ll, ll, ll, ll, C.c_int32, vp, C.POINTER(vp), C.POINTER(vp), sz]),
+            ("mgpuStreamCreate", vp, []), ("mgpuStreamDestroy", None, [vp]), ("mgpuStreamSynchronize", None, [vp]),
+            ("mgpuStreamWaitEvent", None, [vp, vp]), ("mgpuEventCreate", vp, []), ("mgpuEventDestroy", None, [vp]),
+            ("mgpuEventSynchronize", None, [vp]), ("mgpuEventRecord", None, [vp, vp]),
+            ("mgpuMemAlloc", vp, [C.c_uint64, vp, C.c_uint8]), ("mgpuMemFree", None, [vp, vp]),
+            ("mgpuMemcpy", None, [vp, vp, sz, vp]), ("mgpuMemset32", None, [vp, C.c_uint, sz, vp]),
+            ("mgpuMemset16", None, [vp, C.c_ushort, sz, vp]), ("mgpuMemHostRegister", None, [vp, C.c_uint64]),
+            ("mgpuMemHostUnregister", None, [vp]), ("mgpuMemHostRegisterMemRef", None, [ll, vp, ll]),
+            ("mgpuMemHostUnregisterMemRef", None, [ll, vp, ll]), ("mgpuSetDefaultDevice", None, [C.c_int32])]:
+        getattr(L, name).restype = res
+        getattr(L, name).argtypes = args
     _lib = L
     return L
+
+
+def module_blob(kind: int, desc) -> bytes:
+    """The bytes a host module carries in place of a device code object: a
+    header and the kernel's descriptor (include/wave_mgpu.h)."""
+    n = C.c_size_t(0)
+    if lib().wave_cuda_module_blob_bytes(kind, C.byref(n)) != OK:
+        raise ValueError(f"unknown blob kind {kind}")
+    buf = C.create_string_buffer(n.value)
+    check(lib().wave_cuda_module_blob_write(kind, C.byref(desc), buf, n.value))
+    return buf.raw
 
 
 def check(rc: int) -> None:

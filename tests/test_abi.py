@@ -14,9 +14,10 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def declared_functions():
-    text = open(os.path.join(ROOT, "include", "wave_cuda.h")).read()
+    text = "".join(open(os.path.join(ROOT, "include", name)).read()
+                   for name in sorted(os.listdir(os.path.join(ROOT, "include"))) if name.endswith(".h"))
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    names = re.findall(r"\b(wave_cuda_\w+|_mlir_ciface_\w+)\s*\(", text)
+    names = re.findall(r"\b(wave_cuda_\w+|_mlir_ciface_\w+|mgpu[A-Z]\w+)\s*\(", text)
     return sorted(set(names))
 
 
