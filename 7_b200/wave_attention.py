@@ -22,11 +22,12 @@ BLOCK_M = 256    # query rows per workgroup (wave_flash_attention.py:23)
 
 
 def make_runner_inputs(batch: int, heads: int, sequence: int, *, seed: int = 0, input_scale: int = 1,
-                       io_type: str = "bf16"):
+                       io_type: str = "bf16", head_dim: int = HEAD_DIM):
     """Q, K (x0.125*input_scale) and V (x0.25) from LCG streams 0, 1, 2, rounded
-    to the I/O type, shaped [B*H, S, 128] (wave-fa-gfx950-runner.cpp:410-413)."""
-    n = batch * heads * sequence * HEAD_DIM
-    shape = (batch * heads, sequence, HEAD_DIM)
+    to the I/O type, shaped [B*H, S, 128] (wave-fa-gfx950-runner.cpp:410-413);
+    `head_dim` other than the reference's 128 is an extension."""
+    n = batch * heads * sequence * head_dim
+    shape = (batch * heads, sequence, head_dim)
     q = deterministic_random_values(n, seed=seed, stream=0, scale=0.125 * input_scale)
     k = deterministic_random_values(n, seed=seed, stream=1, scale=0.125 * input_scale)
     v = deterministic_random_values(n, seed=seed, stream=2, scale=0.25)

@@ -2,7 +2,7 @@
 """Drop-in for the reference's flash-attention calibrate tool
 (tools/wave-fa-calibrate/wave-fa-gfx950.py + wave-fa-gfx950-runner.cpp) on B200:
 --batch --heads --sequence --qk-max-abs --seed --input-scale --check --zero-qk
---iters --warmup --repeats (wave-fa-gfx950.py:95-128), plus --causal and --scale, which
+--iters --warmup --repeats (wave-fa-gfx950.py:95-128), plus --causal, --scale and --head-dim, which
 the reference's Wave kernel does not have.  Prints the runner's keys (`shape:`,
 `grid:`, `per_launch_us:`, `tflops:`, `output_check: passed max_abs_diff=...`,
 `median_per_launch_us:`, `median_tflops:`; wave-fa-gfx950-runner.cpp:465-481,
@@ -37,7 +37,8 @@ def parse(argv):
     p.add_argument("--check", action="store_true")
     p.add_argument("--zero-qk", action="store_true")
     p.add_argument("--causal", action="store_true")
-    p.add_argument("--scale", type=float, default=0.0, help="softmax scale; 0 = 1/sqrt(128)")
+    p.add_argument("--scale", type=float, default=0.0, help="softmax scale; 0 = 1/sqrt(head_dim)")
+    p.add_argument("--head-dim", type=int, default=128, help="a multiple of 16 up to 128 (the reference: 128 only)")
     p.add_argument("--waves", type=int, default=None, help="AMD-only; accepted and ignored")
     p.add_argument("--threads", type=int, default=None, help="AMD-only; accepted and ignored")
     args = p.parse_args(argv)
@@ -56,13 +57,15 @@ def main(argv=None) -> int:
         return 2
     torch, wc, oracle = load()
     wa = importlib.import_module("7_b200.wave_attention")
-    q, k, v = wa.make_runner_inputs(args.batch, args.heads, args.sequence, seed=args.seed, input_scale=args.input_scale)
+    D = args.head_dim
+    q, k, v = wa.make_runner_inputs(args.batch, args.heads, args.sequence, seed=args.seed, input_scale=args.input_scale,
+                                    head_dim=D)
     if args.zero_qk:
         q[:] = 0
         k[:] = 0
     dq, dk, dv = (dev_bits(torch, x) for x in (q, k, v))
     o = torch.zeros(q.shape, dtype=torch.bfloat16, device="cuda")
-    desc = wc.fa_desc(args.batch, args.heads, args.sequence, args.sequence, 128, scale=args.scale, causal=args.causal,
+    desc = wc.fa_desc(args.batch, args.heads, args.sequence, args.sequence, D, scale=args.scale, causal=args.causal,
                       qk_max_abs=args.qk_max_abs or 0.0)
     try:
         wc.fa_validate(desc)
@@ -80,9 +83,9 @@ def main(argv=None) -> int:
         sys.stderr.write(err.message + "\n")
         return 1
     us = [t * 1e3 / args.iters for t in times]
-    full = wa.flops(args.batch, args.heads, args.sequence)  # the reference's formula, 4*B*H*S^2*D
-    done = wa.flops(args.batch, args.heads, args.sequence, causal=args.causal)
-    print(f"shape: B={args.batch} H={args.heads} N={args.sequence} D=128 causal={int(args.causal)}")
+    full = wa.flops(args.batch, args.heads, args.sequence, D)  # the reference's formula, 4*B*H*S^2*D
+    done = wa.flops(args.batch, args.heads, args.sequence, D, causal=args.causal)
+    print(f"shape: B={args.batch} H={args.heads} N={args.sequence} D={D} causal={int(args.causal)}")
     print(f"grid: {args.sequence // 256},{args.batch * args.heads},1 block: 384,1,1 dynamic_lds=197888")
     for t in us:
         print(f"per_launch_us: {t:.3f}")
@@ -96,7 +99,7 @@ def main(argv=None) -> int:
         print(f"sustained_launches: {sus_n}")
     if args.check:
         heads, rows = oracle.fa_sample_heads(args.batch * args.heads), oracle.fa_sample_rows(args.sequence)
-        scale = args.scale if args.scale > 0 else 1.0 / np.sqrt(128.0)
+        scale = args.scale if args.scale > 0 else 1.0 / np.sqrt(float(D))
         want = oracle.fa_ref(q, k, v, oracle.BF16, scale, causal=args.causal, heads=heads, rows=rows)
         got = o.float().cpu().numpy()[np.ix_(heads, rows)]
         diff = np.abs(got.astype(np.float64) - want)

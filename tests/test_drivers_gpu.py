@@ -106,5 +106,10 @@ def test_attention_calibrate_runner(cuda):
     assert "output_check: passed" in out
     _, err = run("wave_fa_gfx950.py", "--qk-max-abs=1", "--input-scale=2", expect=2)
     assert "--qk-max-abs must cover the generated input range" in err
+    out, _ = run("wave_fa_gfx950.py", "--batch=1", "--heads=2", "--sequence=512", "--iters=3", "--warmup=1", "--check",
+                 "--head-dim=64", "--causal")
+    assert "shape: B=1 H=2 N=512 D=64" in out and "output_check: passed" in out
+    _, err = run("wave_fa_gfx950.py", "--head-dim=72", expect=1)
+    assert "head_dim must be a multiple of 16 between 16 and 128" in err
     _, err = run("wave_fa_gfx950.py", "--qk-max-abs=2", "--input-scale=2", expect=1)
     assert "qk_max_abs fixed reference exceeds BF16 range" in err
