@@ -47,6 +47,11 @@ WORKLOADS = {
     "gemm": dict(name="gemm_bf16_8192x8192x8192_f32acc_bf16out", M=8192, N=8192, K=8192),
     "skinny": dict(name="gemm_bf16_16x28672x8192_f32acc_bf16out_streamk", M=16, N=28672, K=8192),
     "fa": dict(name="fa_fwd_causal_bf16_b16_h32_s4096_d128", B=16, H=32, S=4096, D=128),
+    # The configuration the reference's own attention number is published on
+    # (docs/PerfReferences/WaveGfx950FlashAttention.md:39-44): non-causal, fixed
+    # softmax reference for |Q|,|K| <= 1, inputs of its runner's range.
+    "fa_published": dict(name="fa_fwd_noncausal_bf16_b2_h64_s8192_d128_qk_max_abs_1", B=2, H=64, S=8192, D=128,
+                         causal=False, qk_max_abs=1.0, published_tflops=1115.6),
 }
 
 
@@ -178,15 +183,22 @@ class GemmWork:
 
 
 class FaWork:
-    def __init__(self, torch, wc, B, H, S, D, rank, world, seed=0, causal=True):
+    def __init__(self, torch, wc, B, H, S, D, rank, world, seed=0, causal=True, qk_max_abs=0.0):
         self.torch, self.wc = torch, wc
         self.B, self.H, self.S, self.D, self.causal = B, H, S, D, causal
         g = torch.Generator(device="cuda")
         g.manual_seed(99 + seed + 131 * rank)
-        mk = lambda: torch.randn(B * H, S, D, device="cuda", generator=g).to(torch.bfloat16)
-        self.q, self.k, self.v = mk(), mk(), mk()
+        if qk_max_abs > 0.0:
+            # the value set of the reference runner's generator (17 buckets, Q/K x0.125, V x0.25;
+            # wave-fa-gfx950-runner.cpp:188-202), drawn from torch's generator
+            mk = lambda scale: (torch.randint(-8, 9, (B * H, S, D), device="cuda", generator=g).float()
+                                * scale).to(torch.bfloat16)
+            self.q, self.k, self.v = mk(0.125), mk(0.125), mk(0.25)
+        else:
+            mk = lambda: torch.randn(B * H, S, D, device="cuda", generator=g).to(torch.bfloat16)
+            self.q, self.k, self.v = mk(), mk(), mk()
         self.o = torch.empty_like(self.q)
-        self.desc = wc.fa_desc(B, H, S, S, D, causal=causal, io_type=wc.BF16)
+        self.desc = wc.fa_desc(B, H, S, S, D, causal=causal, io_type=wc.BF16, qk_max_abs=qk_max_abs)
         # unmasked pairs only for the causal case; the reference's own formula
         # (4*B*H*S^2*D, wave-fa-gfx950-runner.cpp:465-466) counts the full square
         pairs = S * (S + 1) / 2 if causal else float(S) * S
@@ -253,8 +265,9 @@ def time_steps(torch, work, steps, warmup, stream, dist=None, host=False):
 
 def make_work(torch, wc, workload, rank, world):
     w = WORKLOADS[workload]
-    if workload == "fa":
-        return FaWork(torch, wc, w["B"], w["H"], w["S"], w["D"], rank, world)
+    if workload.startswith("fa"):
+        return FaWork(torch, wc, w["B"], w["H"], w["S"], w["D"], rank, world, causal=w.get("causal", True),
+                      qk_max_abs=w.get("qk_max_abs", 0.0))
     return GemmWork(torch, wc, w["M"], w["N"], w["K"], rank, world, streamk=0 if workload == "skinny" else 1)
 
 
@@ -345,7 +358,7 @@ def main() -> None:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=400)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="gemm")
+    ap.add_argument("--workload", choices=["fa", "gemm", "skinny"], default="gemm")
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--gather", action="store_true", help="also time the NCCL all-gather of the output shards")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -432,17 +445,20 @@ def main() -> None:
         parity = work.check(oracle)
     if not args.no_also and args.workload == "gemm":
         del work.host
-        for other in ("fa", "skinny"):
+        for other in ("fa", "fa_published", "skinny"):
             w2 = make_work(torch, wc, other, rank, world)
-            steps2 = 10 if other == "fa" else 50
+            steps2 = 10 if other.startswith("fa") else 50
             ms2 = time_steps(torch, w2, steps2, 3, stream, dist) / steps2
             wc.check_device_status()
             launches += (steps2 + 3) * w2.launches_per_step
             entry = {"workload": WORKLOADS[other]["name"], "ms_per_step": ms2,
                      "tflops": w2.flops * world / (ms2 * 1e-3) / 1e12}
-            if other == "fa":
+            if other.startswith("fa"):
                 entry["tflops_full_square_formula"] = w2.flops_full_square * world / (ms2 * 1e-3) / 1e12
                 entry["frac_of_peak"] = entry["tflops"] / world / pk["bf16_tflops"]
+                if "published_tflops" in WORKLOADS[other]:  # one GPU's rate against the reference's one-GPU number
+                    entry["reference_published_tflops_gfx950"] = WORKLOADS[other]["published_tflops"]
+                    entry["vs_published"] = entry["tflops"] / world / WORKLOADS[other]["published_tflops"]
             else:
                 entry["gbs"] = w2.alg_bytes / (ms2 * 1e-3) / 1e9
                 entry["frac_of_hbm_peak"] = entry["gbs"] / pk["hbm_gbs"]
