@@ -93,6 +93,7 @@ constexpr int kTmemCols = 512;
 constexpr int kDefaultPoly = 0;
 constexpr int kStreamFromSeqK = 6144; // key sequence length from which the streaming kernel is used
 constexpr int kStreamFromSeqKFixedRef = 2048; // the same with a fixed softmax reference
+constexpr int kFixedRefStagger = 900;
 constexpr float kRescaleThreshold = 8.0f;
 // setmaxnreg budget.  The kernel starts with kLaunchRegs per thread (12 warps,
 // one CTA per SM); warpgroup 0 shrinks to kIssueRegs and the two softmax
@@ -744,6 +745,15 @@ int launch_flash_attention(const FaParams &p, const void *Q, const void *K, cons
   const unsigned grid = static_cast<unsigned>(total_items < sm_count ? total_items : sm_count);
   cudaError_t err = cudaSuccess;
   FaParams params = p;
+  // Streaming kernel with a fixed softmax reference: cycles the warpgroup of an
+  // item's second K/V block holds back once, so that the two warpgroups' phases
+  // interleave instead of coinciding.  Measured sustained, variants taking turns
+  // (non-causal / causal TFLOP/s, 0 -> 800..1000 cycles): B=2 H=64 S=8192
+  // 1244/1154 -> 1259..1279/1171..1175; B=16 H=32 S=4096 1185/1032 ->
+  // 1211/1058; B=8 H=32 S=2048 1059/830 -> 1097..1103/837..840; 1600 loses again.
+  params.stagger = p.fixed_ref ? kFixedRefStagger : 0;
+  if (const char *env = getenv("WAVE_CUDA_FA_STAGGER"))
+    params.stagger = atoi(env);
   {
     static std::atomic<unsigned> next_slot{0};
     void *base = nullptr;

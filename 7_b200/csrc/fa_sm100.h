@@ -14,6 +14,7 @@ struct FaParams {
   float scale;       // softmax scale applied to q.k
   float scale_log2e; // scale * log2(e): scores enter exp2 as fma(s, scale_log2e, -max)
   int fixed_ref;     // exponentials against the constant ref_log2 instead of the running row maximum
+  int stagger;       // streaming kernel, fixed reference: cycles the odd-block warpgroup holds back at each item's start
   float ref_log2;    // that constant, in log2 units of the scaled scores
   void *O;           // [batch_heads][seq_q][head_dim], the I/O type or f32
   float *lse;        // optional [batch_heads][seq_q] natural-log sum-exp, or null

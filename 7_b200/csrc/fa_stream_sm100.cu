@@ -468,6 +468,15 @@ fa_stream_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           continue;
         if (row == 0 && item_n == kTraceItem)
           FAS_STAMP(1 + wg, j, 0);
+        if (p.fixed_ref && p.stagger > 0 && j == 1) {
+          // Hold the item's second block back once, so that the two warpgroups'
+          // exponential phases do not coincide for the rest of the item.
+          uint32_t t0, t1;
+          asm volatile("mov.u32 %0, %%clock;" : "=r"(t0));
+          do {
+            asm volatile("mov.u32 %0, %%clock;" : "=r"(t1));
+          } while (t1 - t0 < static_cast<uint32_t>(p.stagger));
+        }
         if (!mbar_wait(&sh->s_full[wg], this_parity(g), abort_flag)) {
           if (lane == 0)
             fas_report(kStatusWaitTimeout, 3 + wg, 60);

@@ -163,8 +163,9 @@ int wave_cuda_gemm_plan(const wave_gemm_desc *desc, int *tile_m, int *tile_n, in
  * or 128-row work items with double-buffered scores); the library picks by the
  * number of work items per SM, WAVE_CUDA_FA_KERNEL=pingpong|stream overrides,
  * WAVE_CUDA_FA_POLY=0..4 sets the eighths of the exponentials evaluated as a
- * polynomial on the FMA pipe (measurement knobs; the results agree within the
- * rounding of the exponential).
+ * polynomial on the FMA pipe, WAVE_CUDA_FA_STAGGER=<cycles> the one-off offset
+ * between the streaming kernel's two softmax warpgroups in fixed-reference mode
+ * (measurement knobs; the results agree within the rounding of the exponential).
  */
 typedef struct wave_fa_desc {
   int batch, heads;
