@@ -161,7 +161,8 @@ int wave_cuda_gemm_plan(const wave_gemm_desc *desc, int *tile_m, int *tile_n, in
  * aligned; an extension, the reference's Wave kernel is non-causal).
  * Two kernels compute it (256-row work items with two Q tiles ping-ponging,
  * or 128-row work items with double-buffered scores); the library picks by the
- * number of work items per SM, WAVE_CUDA_FA_KERNEL=pingpong|stream overrides,
+ * key sequence length (the second from 6144 keys on, from 2048 with qk_max_abs),
+ * WAVE_CUDA_FA_KERNEL=pingpong|stream overrides,
  * WAVE_CUDA_FA_POLY=0..4 sets the eighths of the exponentials evaluated as a
  * polynomial on the FMA pipe, WAVE_CUDA_FA_STAGGER=<cycles> the one-off offset
  * between the streaming kernel's two softmax warpgroups in fixed-reference mode

@@ -22,7 +22,7 @@ pytestmark = pytest.mark.gpu
 def fa_kernel(request):
     """Every test runs on both attention kernels (two Q tiles ping-ponging; one
     Q tile with double-buffered scores).  Left alone, the library picks one by
-    the number of work items per SM."""
+    the key sequence length."""
     os.environ["WAVE_CUDA_FA_KERNEL"] = request.param
     yield request.param
     del os.environ["WAVE_CUDA_FA_KERNEL"]
