@@ -516,5 +516,16 @@ def main() -> None:
         dist.destroy_process_group()
 
 
+def _keep_stdout_for_the_result() -> None:
+    """stdout carries the one JSON line.  Libraries write there too (NCCL prints
+    its version banner with printf when NCCL_DEBUG is set on the host), so file
+    descriptor 1 is pointed at stderr for the run and `print` keeps the original."""
+    sys.stdout.flush()
+    result = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+    sys.stdout = result
+
+
 if __name__ == "__main__":
+    _keep_stdout_for_the_result()
     main()
