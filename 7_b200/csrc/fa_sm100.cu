@@ -752,8 +752,10 @@ int launch_flash_attention(const FaParams &p, const void *Q, const void *K, cons
   // 1244/1154 -> 1259..1279/1171..1175; B=16 H=32 S=4096 1185/1032 ->
   // 1211/1058; B=8 H=32 S=2048 1059/830 -> 1097..1103/837..840; 1600 loses again.
   params.stagger = p.fixed_ref ? kFixedRefStagger : 0;
-  if (const char *env = getenv("WAVE_CUDA_FA_STAGGER"))
-    params.stagger = atoi(env);
+  if (const char *env = getenv("WAVE_CUDA_FA_STAGGER")) {
+    const int cycles = atoi(env);
+    params.stagger = cycles < 0 ? 0 : (cycles > 100000 ? 100000 : cycles); // a bounded spin, whatever is asked
+  }
   {
     static std::atomic<unsigned> next_slot{0};
     void *base = nullptr;

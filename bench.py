@@ -335,6 +335,11 @@ def run_reference_arm(args) -> None:
     if rank != 0:
         return
     t_all = time.perf_counter()
+    # Each step is a bounded sample of the workload (about 8 s of CPU work), so the
+    # counts are capped to keep the run within minutes; the line says what ran.
+    warm = min(max(args.warmup, 0), 1)
+    for _ in range(warm):
+        cpu_baseline(args.workload, budget_s=2.0)
     results = []
     for _ in range(max(1, min(args.steps, 3))):
         results.append(cpu_baseline(args.workload, budget_s=8.0))
@@ -342,7 +347,8 @@ def run_reference_arm(args) -> None:
     w = WORKLOADS[args.workload]
     line = {
         "impl": "reference", "metric": METRIC, "value": best["value"], "unit": "TFLOP/s", "n_gpus": args.gpus,
-        "steps": len(results), "warmup": 0, "ms_per_step": best["seconds"] * 1e3, "higher_is_better": True,
+        "steps": len(results), "warmup": warm, "steps_requested": args.steps, "warmup_requested": args.warmup,
+        "ms_per_step": best["seconds"] * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": w["name"], "sample": best["sample"]},
         "cpu_baseline": {k: best[k] for k in ("value", "unit", "cores", "kind", "sample")},
