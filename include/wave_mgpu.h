@@ -5,7 +5,8 @@
  * gpu.launch_func, print) with three shared libraries: MLIR's
  * libmlir_rocm_runtime.so (the mgpu* wrappers that gpu-to-llvm calls),
  * libmlir_runner_utils.so (printMemrefF32/F16, host only) and its own
- * libwave_runtime.so (README.md:99-106; the RUN lines of the .mlir files under test/Integration).
+ * libwave_runtime.so (the reference's README.md:99-106 and the RUN lines of
+ * the .mlir files under its test/Integration).
  * libwave_cuda.so stands in for the first and the third: it exports the
  * seven pointer helpers of runtime/wave_runtime.cpp:46-74 (wave_cuda.h) and
  * the mgpu* entry points below with MLIR's names and argument lists, so a
