@@ -305,14 +305,20 @@ def cpu_baseline(workload: str, budget_s: float = 12.0) -> dict:
         sample = f"{nrows} of {M} output rows x all {N} columns, K={K}"
     else:
         B, H, S, D = w["B"], w["H"], w["S"], w["D"]
+        causal = w.get("causal", True)
         heads = 2
-        q = oracle.baseline_inputs((heads, S, D), "normal", 1, 0, oracle.BF16)
-        k = oracle.baseline_inputs((heads, S, D), "normal", 1, 1, oracle.BF16)
-        v = oracle.baseline_inputs((heads, S, D), "normal", 1, 2, oracle.BF16)
+        if causal:
+            q = oracle.baseline_inputs((heads, S, D), "normal", 1, 0, oracle.BF16)
+            k = oracle.baseline_inputs((heads, S, D), "normal", 1, 1, oracle.BF16)
+            v = oracle.baseline_inputs((heads, S, D), "normal", 1, 2, oracle.BF16)
+        else:  # the reference runner's own inputs
+            q = oracle.fa_input_bits(heads * S * D, oracle.BF16, 1, 0, 0.125).reshape(heads, S, D)
+            k = oracle.fa_input_bits(heads * S * D, oracle.BF16, 1, 1, 0.125).reshape(heads, S, D)
+            v = oracle.fa_input_bits(heads * S * D, oracle.BF16, 1, 2, 0.25).reshape(heads, S, D)
         nrows = 64 * cores
 
         def run(rows):
-            return oracle.fa_ref(q, k, v, oracle.BF16, 1.0 / np.sqrt(D), causal=True, rows=rows, threads=cores)
+            return oracle.fa_ref(q, k, v, oracle.BF16, 1.0 / np.sqrt(D), causal=causal, rows=rows, threads=cores)
         rows = np.linspace(0, S - 1, nrows).astype(np.int32)
         t0 = time.perf_counter()
         run(rows)
@@ -323,9 +329,9 @@ def cpu_baseline(workload: str, budget_s: float = 12.0) -> dict:
             t0 = time.perf_counter()
             run(rows)
             dt = time.perf_counter() - t0
-        flops = float(sum(4.0 * D * (r + 1) for r in rows.tolist()) * heads)
-        ref = None  # the reference runner has no causal mask: the port is used for this workload
-        sample = f"{rows.size} query rows x {heads} heads of S={S}, causal, f64"
+        flops = float(sum(4.0 * D * ((r + 1) if causal else S) for r in rows.tolist()) * heads)
+        ref = None  # the port: the compiled runner's row function has no causal mask and no thread pool
+        sample = f"{rows.size} query rows x {heads} heads of S={S}, {'causal' if causal else 'non-causal'}, f64"
     return {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": cores,
             "kind": "reference" if ref is not None else "port", "sample": sample, "seconds": dt}
 
@@ -364,7 +370,7 @@ def main() -> None:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=400)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", choices=["fa", "gemm", "skinny"], default="gemm")
+    ap.add_argument("--workload", choices=["fa", "fa_published", "gemm", "skinny"], default="gemm")
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--gather", action="store_true", help="also time the NCCL all-gather of the output shards")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -379,7 +385,7 @@ def main() -> None:
     if args.shape:
         dims = [int(x) for x in args.shape.split(",")]
         w = WORKLOADS[args.workload]
-        keys = ("B", "H", "S") if args.workload == "fa" else ("M", "N", "K")
+        keys = ("B", "H", "S") if args.workload.startswith("fa") else ("M", "N", "K")
         w.update(dict(zip(keys, dims)))
         w["name"] += "_shape_override_" + "x".join(str(d) for d in dims)
 
@@ -418,7 +424,7 @@ def main() -> None:
     if args.gather and world > 1:
         from importlib import import_module
         sh = import_module("7_b200.sharding")
-        local = work.c if args.workload != "fa" else work.o
+        local = work.c if not args.workload.startswith("fa") else work.o
         for _ in range(3):
             sh.all_gather_shards(local, dist)
         torch.cuda.synchronize()
@@ -497,7 +503,7 @@ def main() -> None:
                     + f" ({pk_kind})", "frac_of_burst_peak": work.flops / (ms_per_step * 1e-3) / 1e12 / pk["bf16_tflops"],
                     "frac_of_nominal_2250": work.flops / (ms_per_step * 1e-3) / 1e12 / 2250.0}
         roof["frac"] = roof["achieved"] / roof["peak"]
-        roof["traffic"] = NCU_TRAFFIC_BYTES[args.workload]
+        roof["traffic"] = NCU_TRAFFIC_BYTES.get(args.workload)  # None: no ncu capture of this workload
         roof["kernel_ms"] = ms_per_step
         w = WORKLOADS[args.workload]
         line = {
@@ -505,10 +511,10 @@ def main() -> None:
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": w["name"], "per_gpu": {k: v for k, v in w.items() if k != "name"},
-                       "sharding": ("N-column blocks, one 8192-column block per GPU" if args.workload != "fa"
+                       "sharding": ("N-column blocks, one 8192-column block per GPU" if not args.workload.startswith("fa")
                                     else "batch x head slabs, 512 heads per GPU") if world > 1 else "single GPU",
                        "l2": "inputs and output larger than L2 (no flush needed)",
-                       "accumulate": "f32", "plan": wc.gemm_plan(work.desc) if args.workload != "fa" else
+                       "accumulate": "f32", "plan": wc.gemm_plan(work.desc) if not args.workload.startswith("fa") else
                        {"tile_m": 256, "tile_n": 128, "grid": [w["S"] // 256, w["B"] * w["H"]]}},
             "roofline": roof,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": work.h2d,
