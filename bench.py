@@ -40,8 +40,8 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from one ncu capture of
 # the same kernel (summaries under profiles/): gemm and skinny at full size; fa
 # captured at B=2 (250.58 MB) and scaled by the 8x heads of the B=16 workload,
-# since every head moves the same bytes.
-NCU_TRAFFIC_BYTES = {"gemm": 1203.57e6, "fa": 8 * 251.89e6, "skinny": 477.11e6}
+# since every head moves the same bytes; fa_published at full size.
+NCU_TRAFFIC_BYTES = {"gemm": 1203.57e6, "fa": 8 * 251.89e6, "skinny": 477.11e6, "fa_published": 1055.49e6}
 
 WORKLOADS = {
     "gemm": dict(name="gemm_bf16_8192x8192x8192_f32acc_bf16out", M=8192, N=8192, K=8192),
@@ -503,7 +503,7 @@ def main() -> None:
                     + f" ({pk_kind})", "frac_of_burst_peak": work.flops / (ms_per_step * 1e-3) / 1e12 / pk["bf16_tflops"],
                     "frac_of_nominal_2250": work.flops / (ms_per_step * 1e-3) / 1e12 / 2250.0}
         roof["frac"] = roof["achieved"] / roof["peak"]
-        roof["traffic"] = NCU_TRAFFIC_BYTES.get(args.workload)  # None: no ncu capture of this workload
+        roof["traffic"] = NCU_TRAFFIC_BYTES.get(args.workload)
         roof["kernel_ms"] = ms_per_step
         w = WORKLOADS[args.workload]
         line = {
