@@ -25,11 +25,14 @@
 // No load uses cluster multicast.  The causal mask (key <= query) is an
 // extension: the reference's Wave kernel is non-causal.
 #include "../../include/wave_cuda.h"
+#include "backend_env.h"
 #include "fa_sm100.h"
 #include "fa_common.cuh"
+#include "launch_cache.h"
 #include "sm100_ptx.cuh"
 
-#include <atomic>
+#include <mutex>
+#include <string>
 #include <cstdlib>
 #include <cstring>
 #include <type_traits>
@@ -40,8 +43,8 @@ void set_last_error(const char *message); // wave_cuda_backend.cu
 
 __device__ int g_fa_status[4]; // [0] code, [1] linear block, [2] role, [3] detail
 
-// Work-item ticket counters: one per launch in flight (ring), cleared by the
-// launcher on the launch's stream.
+// Work-item ticket counters: one per launch in flight (a ring guarded by
+// events, see ticket_acquire), cleared by the launcher on the launch's stream.
 constexpr unsigned kTicketSlots = 64;
 __device__ unsigned int g_fa_tickets[kTicketSlots];
 
@@ -706,6 +709,99 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 
 } // namespace
 
+// ---------------------------------------------------------------- ticket ring
+// Every launch draws its work items from one of kTicketSlots device counters.
+// Slots are handed out round-robin per device; a slot carries an event recorded
+// behind the launch that last used it, and the next user of the slot makes its
+// stream wait for that event before it clears the counter.  A launch therefore
+// never shares a counter with one that is still running, however many launches
+// are queued on however many streams; the price is that launch k + kTicketSlots
+// starts only after launch k has ended.  Under stream capture the event guard
+// is left out (an event recorded outside the capture cannot be waited for
+// inside it): a captured launch keeps the slot it was captured with, so two
+// graphs that hold the same slot must not be replayed at the same time.
+namespace {
+
+constexpr int kMaxTicketDevices = 64;
+struct TicketRing {
+  cudaEvent_t done[kTicketSlots] = {};
+  bool recorded[kTicketSlots] = {};
+  unsigned next = 0;
+  unsigned int *base = nullptr; // device address of g_fa_tickets on this device
+};
+std::mutex g_ticket_mu;
+TicketRing g_ticket_rings[kMaxTicketDevices];
+
+struct TicketSlot {
+  unsigned int *counter = nullptr;
+  int device = -1;
+  unsigned index = 0;
+  bool capturing = false;
+};
+
+int ticket_fail(cudaError_t err, const char *what) {
+  std::string msg = std::string(what) + ": " + cudaGetErrorString(err);
+  set_last_error(msg.c_str());
+  return WAVE_E_CUDA;
+}
+
+// Picks the next slot of the current device's ring, orders `stream` behind the
+// slot's previous launch and clears the counter on `stream`.  The caller holds
+// g_ticket_mu from here until ticket_launched has run, so that no other host
+// thread can come round to the same slot in between.
+int ticket_acquire(cudaStream_t stream, TicketSlot *out) {
+  int dev = -1;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess)
+    return ticket_fail(err, "cudaGetDevice");
+  if (dev < 0 || dev >= kMaxTicketDevices) {
+    set_last_error("device ordinal out of range for the attention ticket ring");
+    return WAVE_E_CUDA;
+  }
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess) {
+    cudaGetLastError();
+    cap = cudaStreamCaptureStatusNone;
+  }
+  TicketRing &ring = g_ticket_rings[dev];
+  if (!ring.base) {
+    void *base = nullptr;
+    if ((err = cudaGetSymbolAddress(&base, g_fa_tickets)) != cudaSuccess)
+      return ticket_fail(err, "cudaGetSymbolAddress (attention tickets)");
+    ring.base = static_cast<unsigned int *>(base);
+  }
+  TicketSlot s;
+  s.device = dev;
+  s.index = ring.next++ % kTicketSlots;
+  s.counter = ring.base + s.index;
+  s.capturing = cap != cudaStreamCaptureStatusNone;
+  if (!s.capturing && ring.recorded[s.index] &&
+      (err = cudaStreamWaitEvent(stream, ring.done[s.index], 0)) != cudaSuccess)
+    return ticket_fail(err, "cudaStreamWaitEvent (attention ticket slot)");
+  if ((err = cudaMemsetAsync(s.counter, 0, sizeof(unsigned int), stream)) != cudaSuccess)
+    return ticket_fail(err, "cudaMemsetAsync (attention ticket)");
+  *out = s;
+  return WAVE_OK;
+}
+
+// Marks the end of the slot's launch on `stream` (called after the kernel has
+// been enqueued, also when the enqueue failed: the memset is on the stream).
+void ticket_launched(const TicketSlot &s, cudaStream_t stream) {
+  if (s.device < 0 || s.capturing)
+    return;
+  TicketRing &ring = g_ticket_rings[s.device];
+  if (!ring.done[s.index] &&
+      cudaEventCreateWithFlags(&ring.done[s.index], cudaEventDisableTiming) != cudaSuccess) {
+    cudaGetLastError();
+    ring.done[s.index] = nullptr;
+    ring.recorded[s.index] = false;
+    return;
+  }
+  ring.recorded[s.index] = cudaEventRecord(ring.done[s.index], stream) == cudaSuccess;
+}
+
+} // namespace
+
 int launch_flash_attention(const FaParams &p, const void *Q, const void *K, const void *V, int sm_count,
                            cudaStream_t stream) {
   if (p.head_dim < 16 || p.head_dim > kD || p.head_dim % 16)
@@ -733,13 +829,12 @@ int launch_flash_attention(const FaParams &p, const void *Q, const void *K, cons
   }
   // Share of the exponentials evaluated on the FMA pipe, in eighths (a tuning
   // knob for measurements; the default is the measured best).
-  int poly = -1; // each kernel's own default
-  if (const char *env = getenv("WAVE_CUDA_FA_POLY"))
-    poly = atoi(env);
+  const EnvKnobs env = env_knobs();
+  int poly = env.fa_poly; // -1: each kernel's own default
   // Persistent CTAs, one per SM, draw work items (256 query rows of one head)
   // from a ticket counter.  Each launch takes the next of a ring of counters
-  // and clears it on its stream, so launches that overlap on the GPU do not
-  // share one.
+  // and clears it on its stream, behind the launch that last used that counter,
+  // so launches that overlap on the GPU do not share one.
   const long long total_items =
       static_cast<long long>(p.batch_heads) * ((p.seq_q + 2 * kBlockM - 1) / (2 * kBlockM));
   const unsigned grid = static_cast<unsigned>(total_items < sm_count ? total_items : sm_count);
@@ -752,25 +847,13 @@ int launch_flash_attention(const FaParams &p, const void *Q, const void *K, cons
   // 1244/1154 -> 1259..1279/1171..1175; B=16 H=32 S=4096 1185/1032 ->
   // 1211/1058; B=8 H=32 S=2048 1059/830 -> 1097..1103/837..840; 1600 loses again.
   params.stagger = p.fixed_ref ? kFixedRefStagger : 0;
-  if (const char *env = getenv("WAVE_CUDA_FA_STAGGER")) {
-    const int cycles = atoi(env);
-    params.stagger = cycles < 0 ? 0 : (cycles > 100000 ? 100000 : cycles); // a bounded spin, whatever is asked
-  }
-  {
-    static std::atomic<unsigned> next_slot{0};
-    void *base = nullptr;
-    err = cudaGetSymbolAddress(&base, g_fa_tickets);
-    if (err != cudaSuccess) {
-      set_last_error(cudaGetErrorString(err));
-      return WAVE_E_CUDA;
-    }
-    params.ticket = static_cast<unsigned int *>(base) + (next_slot.fetch_add(1) % kTicketSlots);
-    err = cudaMemsetAsync(params.ticket, 0, sizeof(unsigned int), stream);
-    if (err != cudaSuccess) {
-      set_last_error(cudaGetErrorString(err));
-      return WAVE_E_CUDA;
-    }
-  }
+  if (env.fa_stagger >= 0)
+    params.stagger = env.fa_stagger;
+  std::lock_guard<std::mutex> ticket_lock(g_ticket_mu);
+  TicketSlot slot;
+  if (int rc = ticket_acquire(stream, &slot); rc != WAVE_OK)
+    return rc;
+  params.ticket = slot.counter;
   // WAVE_CUDA_FA_KERNEL=stream|pingpong picks the kernel (a knob for
   // measurements; results are the same).
   // Which kernel: the streaming one pays more per work item (an epilogue and a
@@ -785,11 +868,13 @@ int launch_flash_attention(const FaParams &p, const void *Q, const void *K, cons
   // 599/857 against 580/843; 760/967 against 774/988; 927/1064 against 962/1093;
   // 998/1089 against 1072/1151).
   {
-    const char *env = getenv("WAVE_CUDA_FA_KERNEL");
-    const bool stream_kernel = env ? strcmp(env, "stream") == 0
-                                   : p.seq_k >= (p.fixed_ref ? kStreamFromSeqKFixedRef : kStreamFromSeqK);
-    if (stream_kernel)
-      return launch_flash_attention_stream(params, tq, tk, tv, poly, sm_count, stream);
+    const bool stream_kernel = env.fa_kernel ? env.fa_kernel == 2
+                                             : p.seq_k >= (p.fixed_ref ? kStreamFromSeqKFixedRef : kStreamFromSeqK);
+    if (stream_kernel) {
+      const int rc = launch_flash_attention_stream(params, tq, tk, tv, poly, sm_count, stream);
+      ticket_launched(slot, stream);
+      return rc;
+    }
   }
   if (poly < 0)
     poly = kDefaultPoly;
@@ -798,17 +883,14 @@ int launch_flash_attention(const FaParams &p, const void *Q, const void *K, cons
     // The setmaxnreg arithmetic in the kernel assumes the register count the
     // compiler actually gave it; refuse to launch rather than risk a grow
     // request that can never be satisfied.
-    cudaFuncAttributes attr;
-    err = cudaFuncGetAttributes(&attr, kernel);
+    KernelInfo info;
+    err = prepare_kernel(kernel, kSmemBytes, &info);
     if (err != cudaSuccess)
       return;
-    if ((attr.numRegs - kIssueRegs) * 128 < (kSoftmaxRegs - attr.numRegs) * 256 || attr.numRegs * kThreads > 65536) {
+    if ((info.num_regs - kIssueRegs) * 128 < (kSoftmaxRegs - info.num_regs) * 256 || info.num_regs * kThreads > 65536) {
       unsafe_budget = true;
       return;
     }
-    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    if (err != cudaSuccess)
-      return;
     kernel<<<grid, kThreads, kSmemBytes, stream>>>(tq, tk, tv, params);
     err = cudaGetLastError();
   };
@@ -827,6 +909,7 @@ int launch_flash_attention(const FaParams &p, const void *Q, const void *K, cons
     dispatch(std::true_type{});
   else
     dispatch(std::false_type{});
+  ticket_launched(slot, stream);
   if (unsafe_budget) {
     set_last_error("attention kernel was built with a register count its setmaxnreg budget does not cover");
     return WAVE_E_CUDA;

@@ -29,6 +29,7 @@
 #include "../../include/wave_cuda.h"
 #include "fa_common.cuh"
 #include "fa_sm100.h"
+#include "launch_cache.h"
 #include "sm100_ptx.cuh"
 
 #include <atomic>
@@ -751,17 +752,14 @@ int launch_flash_attention_stream(const FaParams &p, const CUtensorMap &tq, cons
     // The setmaxnreg arithmetic in the kernel assumes the register count the
     // compiler actually gave it; refuse to launch rather than risk a grow
     // request that can never be satisfied.
-    cudaFuncAttributes attr;
-    err = cudaFuncGetAttributes(&attr, kernel);
+    KernelInfo info;
+    err = prepare_kernel(kernel, kSmemBytes, &info);
     if (err != cudaSuccess)
       return;
-    if ((attr.numRegs - kIssueRegs) * 128 < (kSoftmaxRegs - attr.numRegs) * 256 || attr.numRegs * kThreads > 65536) {
+    if ((info.num_regs - kIssueRegs) * 128 < (kSoftmaxRegs - info.num_regs) * 256 || info.num_regs * kThreads > 65536) {
       unsafe_budget = true;
       return;
     }
-    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    if (err != cudaSuccess)
-      return;
     kernel<<<grid, kThreads, kSmemBytes, stream>>>(tq, tk, tv, p);
     err = cudaGetLastError();
   };

@@ -21,6 +21,35 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int 
   nb = in_group / rows;
 }
 
+// Balanced contiguous split of `total` iterations over `workers`
+// (wave_matmul.py:88-100, streamk_worker_interval).
+__device__ __forceinline__ void streamk_interval(long long total, int workers, int worker, long long &begin,
+                                                 long long &end) {
+  const long long q = total / workers, r = total % workers;
+  begin = worker * q + min(static_cast<long long>(worker), r);
+  end = begin + q + (worker < r ? 1 : 0);
+}
+// Owner of one iteration (wave_matmul.py:103-116, streamk_owner_for_iteration).
+__device__ __forceinline__ int streamk_owner(long long total, int workers, long long it) {
+  const long long q = total / workers, r = total % workers;
+  const long long large_end = r * (q + 1);
+  if (it < large_end)
+    return static_cast<int>(it / (q + 1));
+  return static_cast<int>(r + (it - large_end) / q);
+}
+// Scratch slot (0 or 1) that `owner` uses for its partial of `tile`
+// (wave_matmul.py:135-159, streamk_worker_segments): partial tiles are
+// numbered in tile order and a contiguous interval has at most two.
+__device__ __forceinline__ int streamk_slot(long long total, int workers, int k_iters, int owner, int tile) {
+  long long b, e;
+  streamk_interval(total, workers, owner, b, e);
+  const long long first_tile = b / k_iters;
+  if (tile == first_tile)
+    return 0;
+  const bool first_partial = (b % k_iters != 0) || (e < (first_tile + 1) * static_cast<long long>(k_iters));
+  return first_partial ? 1 : 0;
+}
+
 template <int OUT> struct OutT;
 template <> struct OutT<WAVE_GEMM_OUT_F32> { using type = float; };
 template <> struct OutT<WAVE_GEMM_OUT_F16> { using type = __half; };

@@ -21,8 +21,12 @@
 // workspace.  It calls no cudaMalloc, cudaFree or other allocating routine.
 //
 // Limits and rules:
-//   * capacity WAVE_CUDA_STATIC_WORKSPACE_BYTES (8 MiB); a descriptor whose
-//     partial tiles and counters need more is refused with WAVE_E_INVALID;
+//   * capacity WAVE_CUDA_STATIC_WORKSPACE_BYTES (8 MiB); a descriptor with an
+//     explicit worker count whose partial tiles and counters need more is
+//     refused with WAVE_E_INVALID.  With streamk_workers = 0 the caller left
+//     the choice to the library: if the automatic Stream-K plan does not fit,
+//     the launch runs as whole tiles instead (no workspace, still no
+//     allocation), with the same results;
 //   * the first call on each device looks the area's device address up
 //     (cudaGetSymbolAddress) with that device current; make that first call
 //     before any stream capture begins;
@@ -89,6 +93,8 @@ extern "C" int wave_cuda_gemm_streamk_static(const wave_gemm_desc *desc, const v
   int rc = wave_cuda_gemm_workspace_bytes(desc, &scratch, &counters); // validates the descriptor too
   if (rc != WAVE_OK)
     return rc;
+  if (scratch + counters > static_cast<size_t>(WAVE_CUDA_STATIC_WORKSPACE_BYTES) && desc->streamk_workers == 0)
+    return wave_cuda_gemm(desc, A, B, C, nullptr, stream); // automatic plan too large: whole tiles, no workspace
   if (scratch + counters > static_cast<size_t>(WAVE_CUDA_STATIC_WORKSPACE_BYTES))
     return fail_msg(WAVE_E_INVALID,
                     "this Stream-K launch needs %zu bytes of partial tiles and counters but the built-in "

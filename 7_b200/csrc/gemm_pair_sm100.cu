@@ -11,6 +11,16 @@
 // only 0.69 of the wide tile's rate (1035 against 1507 TFLOP/s at 8192^3), so
 // the host never picks it by itself.
 //
+// Stream-K tail (p.streamk_workers = number of CTA pairs): tiles [0, dp_tiles)
+// are whole tiles dealt round-robin over the pairs; the K iterations of tiles
+// [dp_tiles, num_tiles) -- a last round that would leave pairs idle -- are split
+// evenly over all pairs with the reference's partition
+// (wave_matmul.py:88-159).  Each CTA of a pair treats its 128 rows on its own:
+// f32 partial -> its half of the pair's scratch slot, one arrival counter per
+// (tile, CTA rank), the last arriver sums the owners in ascending order and
+// stores C, counters return to zero (wave_matmul.py:9756-9784, 9987-10150).
+// Nothing waits for another CTA pair.
+//
 // Same numerics and operator surface as gemm_sm100.cu (the reference's
 // `wmma_f16_matmul_tiled`, python/mlir/dialects/wave_matmul.py:11163-11241).
 //
@@ -21,6 +31,7 @@
 //   tfull[a]   one per CTA; the leader's commit arrives on both
 //   tempty[a]  lives in the leader; the epilogue warps of both CTAs arrive
 #include "gemm_common.cuh"
+#include "launch_cache.h"
 
 namespace wave {
 
@@ -58,6 +69,65 @@ struct PairShared {
   uint64_t tempty[2];
   uint32_t tmem_base;
   int abort_flag;
+  int last_arriver; // Stream-K: broadcast of the arrival-counter result among the epilogue warps
+};
+
+// One unit of work of a CTA pair: a whole tile, half a tile (columns
+// [n_off, n_off + width) of it) or a K range of a Stream-K tile.
+struct PairItem {
+  int tile, mb, nb, n_off, width, k_begin, k_end;
+};
+
+// Work iterator shared by the three roles of both CTAs, so that they agree on
+// the sequence of items without talking to each other.  Data-parallel part:
+// items [0, dp_items) strided by the number of pairs (tiles below split_from
+// whole, later ones as two half-width items); Stream-K part: this pair's
+// interval of (tile, k) iterations of the tiles from dp_tiles on.
+template <int PN> struct PairWork {
+  const GemmParams &p;
+  int split_from, dp_items, num_pairs;
+  long long dp_cur, cur, end;
+  __device__ PairWork(const GemmParams &params, int pair_id, int pairs) : p(params), num_pairs(pairs) {
+    const bool sk = p.streamk_workers > 0;
+    split_from = (PN == 256 && !sk) ? p.split_from : p.num_tiles;
+    dp_items = sk ? p.dp_tiles : split_from + 2 * (p.num_tiles - split_from);
+    dp_cur = pair_id;
+    cur = end = 0;
+    if (sk)
+      streamk_interval(static_cast<long long>(p.num_tiles - p.dp_tiles) * p.k_iters, p.streamk_workers, pair_id, cur,
+                       end);
+  }
+  __device__ bool next(PairItem &it) {
+    if (dp_cur < dp_items) {
+      const int item = static_cast<int>(dp_cur);
+      dp_cur += num_pairs;
+      it.tile = item;
+      it.n_off = 0;
+      it.width = PN;
+      if (item >= split_from) {
+        const int r = item - split_from;
+        it.tile = split_from + (r >> 1);
+        it.n_off = (r & 1) * (PN / 2);
+        it.width = PN / 2;
+      }
+      it.k_begin = 0;
+      it.k_end = p.k_iters;
+    } else {
+      if (cur >= end)
+        return false;
+      const long long tile = cur / p.k_iters; // index within the Stream-K part
+      const long long tile_begin = tile * p.k_iters;
+      const long long seg_end = min(end, tile_begin + p.k_iters);
+      it.tile = static_cast<int>(tile) + p.dp_tiles;
+      it.n_off = 0;
+      it.width = PN;
+      it.k_begin = static_cast<int>(cur - tile_begin);
+      it.k_end = static_cast<int>(seg_end - tile_begin);
+      cur = seg_end;
+    }
+    tile_coords(it.tile, p.num_m_blocks, p.num_n_blocks, p.group_m, it.mb, it.nb);
+    return true;
+  }
 };
 
 __device__ __forceinline__ void pair_report(int code, int role, int detail) {
@@ -90,24 +160,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const bool leader = rank == 0;
   const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
-  // Work items: tiles [0, split_from) whole, then every later tile as two
-  // half-width items (columns [0,128) and [128,256) of the tile), so that a
-  // sparsely filled last round of tiles spreads over twice as many CTA pairs.
-  const int split_from = PN == 256 ? p.split_from : p.num_tiles;
-  const int num_items = split_from + 2 * (p.num_tiles - split_from);
-  auto decode = [&](int item, int &mb, int &nb, int &n_off, int &width) {
-    int tile = item;
-    n_off = 0;
-    width = PN;
-    if (item >= split_from) {
-      const int r = item - split_from;
-      tile = split_from + (r >> 1);
-      n_off = (r & 1) * (PN / 2);
-      width = PN / 2;
-    }
-    tile_coords(tile, p.num_m_blocks, p.num_n_blocks, p.group_m, mb, nb);
-  };
-
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&sh->full[s], 1);
@@ -118,6 +170,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       mbar_init(&sh->tempty[a], 8); // four epilogue warps in each CTA of the pair
     }
     sh->abort_flag = 0;
+    sh->last_arriver = 0;
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -136,17 +189,22 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     if (lane == 0) {
       tma_prefetch_desc(&tmap_a);
       tma_prefetch_desc(&tmap_b);
+      // A panels are shared by every tile of a row group and read again by its
+      // later rounds; a B panel is finished with once the round that holds its
+      // column block has read it.
+      const uint64_t pol_a = p.l2_hints ? l2_policy_evict_last() : l2_policy_evict_normal();
+      const uint64_t pol_b = p.l2_hints == 1 ? l2_policy_evict_first() : l2_policy_evict_normal();
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int item = pair_id; item < num_items && ok; item += num_pairs) {
-        int mb, nb, n_off, width;
-        decode(item, mb, nb, n_off, width);
-        const bool half = width != PN;
-        const int m0 = mb * kPairM + static_cast<int>(rank) * kRows;
-        const int n0 = nb * kPairN + n_off + static_cast<int>(rank) * (width / 2);
-        const uint32_t stage_tx = 2 * (kABytes + (width / 2) * kBK * 2);
-        for (int kb = 0; kb < p.k_iters; ++kb) {
+      PairWork<PN> work(p, pair_id, num_pairs);
+      PairItem it;
+      while (ok && work.next(it)) {
+        const bool half = it.width != PN;
+        const int m0 = it.mb * kPairM + static_cast<int>(rank) * kRows;
+        const int n0 = it.nb * kPairN + it.n_off + static_cast<int>(rank) * (it.width / 2);
+        const uint32_t stage_tx = 2 * (kABytes + (it.width / 2) * kBK * 2);
+        for (int kb = it.k_begin; kb < it.k_end; ++kb) {
           if (!mbar_wait(&sh->empty[stage], phase ^ 1, abort_flag)) {
             pair_report(kStatusWaitTimeout, 0, stage);
             ok = false;
@@ -156,8 +214,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           uint8_t *b_dst = a_dst + kABytes;
           if (leader)
             mbar_arrive_expect_tx(&sh->full[stage], stage_tx);
-          tma_load_2d_pair(a_dst, &tmap_a, &sh->full[stage], kb * kBK, m0);
-          tma_load_2d_pair(b_dst, half ? &tmap_b_half : &tmap_b, &sh->full[stage], kb * kBK, n0);
+          tma_load_2d_pair_hint(a_dst, &tmap_a, &sh->full[stage], kb * kBK, m0, pol_a);
+          tma_load_2d_pair_hint(b_dst, half ? &tmap_b_half : &tmap_b, &sh->full[stage], kb * kBK, n0, pol_b);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1;
@@ -177,15 +235,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int item = pair_id; item < num_items && ok; item += num_pairs) {
-        const uint32_t idesc = item >= split_from ? idesc_half : idesc_whole;
+      PairWork<PN> work(p, pair_id, num_pairs);
+      PairItem it;
+      while (ok && work.next(it)) {
+        const uint32_t idesc = it.width != PN ? idesc_half : idesc_whole;
         if (!mbar_wait(&sh->tempty[acc], acc_phase ^ 1, abort_flag)) {
           pair_report(kStatusWaitTimeout, 1, 100 + acc);
           break;
         }
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * kPairN);
-        for (int kb = 0; kb < p.k_iters; ++kb) {
+        for (int kb = it.k_begin; kb < it.k_end; ++kb) {
           if (!mbar_wait(&sh->full[stage], phase, abort_flag)) {
             pair_report(kStatusWaitTimeout, 1, stage);
             ok = false;
@@ -198,7 +258,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
           for (int k = 0; k < kBK / 16; ++k)
             umma_ss_pair(tmem_d, a_desc + static_cast<uint64_t>(k * 2), b_desc + static_cast<uint64_t>(k * 2), idesc,
-                         (kb > 0 || k > 0) ? 1u : 0u);
+                         (kb > it.k_begin || k > 0) ? 1u : 0u);
           umma_commit_pair(&sh->empty[stage], 3); // frees the stage in both CTAs
           if (++stage == kStages) {
             stage = 0;
@@ -225,11 +285,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const uint32_t tempty_leader[2] = {map_to_cta(&sh->tempty[0], 0), map_to_cta(&sh->tempty[1], 0)};
     // Barrier among the four epilogue warps (named barrier 1).
     auto epilogue_barrier = [] { asm volatile("bar.sync 1, 128;" ::: "memory"); };
-    for (int item = pair_id; item < num_items; item += num_pairs) {
-      int mb, nb, n_off, width;
-      decode(item, mb, nb, n_off, width);
+    const long long total_iters = static_cast<long long>(p.num_tiles - p.dp_tiles) * p.k_iters; // Stream-K part
+    PairWork<PN> work(p, pair_id, num_pairs);
+    PairItem it;
+    while (work.next(it)) {
+      const int mb = it.mb, nb = it.nb, n_off = it.n_off, width = it.width;
+      const bool whole = it.k_begin == 0 && it.k_end == p.k_iters;
       bool failed = !mbar_wait(&sh->tfull[acc], acc_phase, abort_flag);
-      if (p.c_tma) {
+      if (p.c_tma || p.streamk_workers > 0) {
         // The four warps share named barriers below: they must leave together.
         uint32_t any;
         __syncwarp();
@@ -249,6 +312,68 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const uint32_t taddr =
           tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * kPairN);
       const int m = mb * kPairM + static_cast<int>(rank) * kRows + row_in_tile;
+      if (!whole) {
+        // Stream-K partial: this CTA's 128 rows of the raw f32 accumulator go to its
+        // half of the pair's scratch slot, element (row, col) at col*128 + row so
+        // that a warp writes 128 contiguous bytes.  Then the arrival is counted;
+        // the last arriver of this (tile, CTA rank) reduces.
+        const int sk_tile = it.tile - p.dp_tiles;
+        const int slot = streamk_slot(total_iters, p.streamk_workers, p.k_iters, pair_id, sk_tile);
+        float *mine = p.scratch + ((static_cast<size_t>(pair_id) * 2 + slot) * 2 + rank) * (kRows * PN);
+#pragma unroll 1
+        for (int c = 0; c < PN; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + c, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            mine[(c + j) * kRows + row_in_tile] = __uint_as_float(r[j]);
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0)
+          mbar_arrive_cluster(tempty_leader[acc]); // TMEM buffer is free; the rest is global memory only
+        __threadfence();
+        epilogue_barrier();
+        const long long tile_begin = static_cast<long long>(sk_tile) * p.k_iters;
+        const int first_owner = streamk_owner(total_iters, p.streamk_workers, tile_begin);
+        const int last_owner = streamk_owner(total_iters, p.streamk_workers, tile_begin + p.k_iters - 1);
+        const int parts = last_owner - first_owner + 1;
+        int *counter = &p.counters[sk_tile * 2 + static_cast<int>(rank)];
+        if (row_in_tile == 0) {
+          const int old = atomicAdd(counter, 1);
+          sh->last_arriver = (old + 1 == parts) ? 1 : 0;
+        }
+        epilogue_barrier();
+        if (sh->last_arriver != 0) {
+          __threadfence();
+          // Fixed order: ascending owner id, starting from zero
+          // (wave_matmul.py:9756-9784), so the result is run-to-run identical.
+#pragma unroll 1
+          for (int c = 0; c < PN; c += 32) {
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              v[j] = 0.0f;
+            for (int owner = first_owner; owner <= last_owner; ++owner) {
+              const int oslot = streamk_slot(total_iters, p.streamk_workers, p.k_iters, owner, sk_tile);
+              const float *src = p.scratch + ((static_cast<size_t>(owner) * 2 + oslot) * 2 + rank) * (kRows * PN);
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                v[j] += __ldcg(&src[(c + j) * kRows + row_in_tile]);
+            }
+            store_row_chunk<T, 32>(p, m, nb * kPairN + c, v);
+          }
+          if (row_in_tile == 0)
+            atomicAdd(counter, -parts); // back to zero for the next launch
+        }
+        epilogue_barrier(); // sh->last_arriver may be rewritten
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+        continue;
+      }
       if constexpr (sizeof(T) == 2) {
         if (p.c_tma) {
           // Row-major 16-bit output: 64 columns of the CTA's 128 rows at a time go
@@ -339,7 +464,7 @@ template <int OUT, int PN>
 cudaError_t launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tbh, const CUtensorMap &tc,
                         const GemmParams &p, int grid, cudaStream_t stream) {
   constexpr int smem = PairCfg<PN>::kSmemBytes;
-  cudaError_t err = cudaFuncSetAttribute(gemm_pair_kernel<OUT, PN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  cudaError_t err = prepare_kernel(gemm_pair_kernel<OUT, PN>, smem, nullptr);
   if (err != cudaSuccess)
     return err;
   gemm_pair_kernel<OUT, PN><<<grid, kThreads, smem, stream>>>(ta, tb, tbh, tc, p);

@@ -19,6 +19,7 @@
 // accumulator is f32, and there is a single round-to-nearest-even to the C
 // element type at the end.  No alpha/beta: C is overwritten.
 #include "gemm_common.cuh"
+#include "launch_cache.h"
 
 namespace wave {
 
@@ -65,35 +66,6 @@ __device__ __forceinline__ void report(int code, int role, int detail) {
     g_gemm_status[2] = role;
     g_gemm_status[3] = detail;
   }
-}
-
-// Balanced contiguous split of `total` iterations over `workers`
-// (wave_matmul.py:88-100, streamk_worker_interval).
-__device__ __forceinline__ void streamk_interval(long long total, int workers, int worker, long long &begin,
-                                                 long long &end) {
-  const long long q = total / workers, r = total % workers;
-  begin = worker * q + min(static_cast<long long>(worker), r);
-  end = begin + q + (worker < r ? 1 : 0);
-}
-// Owner of one iteration (wave_matmul.py:103-116, streamk_owner_for_iteration).
-__device__ __forceinline__ int streamk_owner(long long total, int workers, long long it) {
-  const long long q = total / workers, r = total % workers;
-  const long long large_end = r * (q + 1);
-  if (it < large_end)
-    return static_cast<int>(it / (q + 1));
-  return static_cast<int>(r + (it - large_end) / q);
-}
-// Scratch slot (0 or 1) that `owner` uses for its partial of `tile`
-// (wave_matmul.py:135-159, streamk_worker_segments): partial tiles are
-// numbered in tile order and a contiguous interval has at most two.
-__device__ __forceinline__ int streamk_slot(long long total, int workers, int k_iters, int owner, int tile) {
-  long long b, e;
-  streamk_interval(total, workers, owner, b, e);
-  const long long first_tile = b / k_iters;
-  if (tile == first_tile)
-    return 0;
-  const bool first_partial = (b % k_iters != 0) || (e < (first_tile + 1) * static_cast<long long>(k_iters));
-  return first_partial ? 1 : 0;
 }
 
 struct Segment {
@@ -444,10 +416,8 @@ template <int BN, int OUT>
 cudaError_t launch_one(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc, const GemmParams &p,
                        int grid, cudaStream_t stream) {
   using Cfg = TileCfg<BN>;
-  // The attribute belongs to the current device's context, so it is set on
-  // every launch rather than cached per process.
-  cudaError_t err =
-      cudaFuncSetAttribute(gemm_kernel<BN, OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+  // The shared-memory opt-in belongs to the current device's context: once per (kernel, device).
+  cudaError_t err = prepare_kernel(gemm_kernel<BN, OUT>, Cfg::kSmemBytes, nullptr);
   if (err != cudaSuccess)
     return err;
   gemm_kernel<BN, OUT><<<grid, kThreads, Cfg::kSmemBytes, stream>>>(ta, tb, tc, p);

@@ -31,6 +31,8 @@ struct GemmParams {
   // order of the 256 values inside a tile: 0 row-major, 1 MFMA wave64, 2 WMMA wave32, 3 MFMA wave32 fragments
   int tp_fragment;
   int c_tma; // whole tiles leave through TMA stores (row-major 16-bit C, tiles of at least 64 columns)
+  // L2 eviction hints on the operand loads: 0 none, 1 A "evict last" + B "evict first", 2 A "evict last" only
+  int l2_hints;
 };
 
 int gemm_tile_m();
@@ -39,8 +41,10 @@ cudaError_t launch_gemm(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, co
                         const GemmParams &p, int tile_n, int grid, cudaStream_t stream);
 cudaError_t gemm_read_status(int out[4], bool clear);
 
-// CTA-pair kernel (256 x 256 or 256 x 128 tiles, tcgen05 cta_group::2);
-// data-parallel only.  gemm_pair_tile_n() is the wide tile.
+// CTA-pair kernel (256 x 256 or 256 x 128 tiles, tcgen05 cta_group::2):
+// data-parallel, optionally with a Stream-K tail over all pairs (streamk_workers
+// = grid / 2, scratch [workers][2][2][128 x 256] f32, counters [tail tiles][2]).
+// gemm_pair_tile_n() is the wide tile.
 int gemm_pair_tile_m();
 int gemm_pair_tile_n();
 int gemm_pair_box_rows();

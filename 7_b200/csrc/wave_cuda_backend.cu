@@ -7,6 +7,7 @@
 // (runner.cpp:393-408) and the kernel-argument blocks (runner.cpp:1790-1816).
 // There is no CPU fallback anywhere in this file.
 #include "../../include/wave_cuda.h"
+#include "backend_env.h"
 #include "fa_sm100.h"
 #include "gemm_sm100.h"
 
@@ -62,6 +63,54 @@ EncodeTiledFn encode_fn() {
 } // namespace
 
 namespace wave {
+
+// The WAVE_CUDA_* environment knobs are read once (at the first call that needs
+// them) and again only when the caller asks with wave_cuda_reload_env().
+namespace {
+std::mutex g_env_mu;
+EnvKnobs g_env;
+bool g_env_loaded = false;
+
+EnvKnobs read_env() {
+  EnvKnobs e;
+  if (const char *v = getenv("WAVE_CUDA_GEMM_KERNEL"))
+    e.gemm_kernel = !strcmp(v, "single") ? 1 : !strcmp(v, "pair") ? 2 : !strcmp(v, "pair128") ? 3 : 0;
+  if (const char *v = getenv("WAVE_CUDA_GEMM_SPLIT_TAIL"))
+    e.gemm_split_tail = strcmp(v, "0") != 0;
+  if (const char *v = getenv("WAVE_CUDA_GEMM_STREAMK_TAIL"))
+    e.gemm_streamk_tail = strcmp(v, "0") != 0;
+  if (const char *v = getenv("WAVE_CUDA_GEMM_TMA_STORE"))
+    e.gemm_tma_store = strcmp(v, "0") != 0;
+  if (const char *v = getenv("WAVE_CUDA_GEMM_L2_HINTS"))
+    e.gemm_l2_hints = atoi(v);
+  if (const char *v = getenv("WAVE_CUDA_GEMM_COL_SWAP"))
+    e.gemm_col_swap = strcmp(v, "0") != 0;
+  if (const char *v = getenv("WAVE_CUDA_FA_KERNEL"))
+    e.fa_kernel = !strcmp(v, "pingpong") ? 1 : !strcmp(v, "stream") ? 2 : !strcmp(v, "pair") ? 3 : 0;
+  if (const char *v = getenv("WAVE_CUDA_FA_POLY"))
+    e.fa_poly = atoi(v);
+  if (const char *v = getenv("WAVE_CUDA_FA_STAGGER")) {
+    const int cycles = atoi(v);
+    e.fa_stagger = cycles < 0 ? 0 : (cycles > 100000 ? 100000 : cycles); // a bounded spin, whatever is asked
+  }
+  return e;
+}
+} // namespace
+
+EnvKnobs env_knobs() {
+  std::lock_guard<std::mutex> lock(g_env_mu);
+  if (!g_env_loaded) {
+    g_env = read_env();
+    g_env_loaded = true;
+  }
+  return g_env;
+}
+
+void reload_env_knobs() {
+  std::lock_guard<std::mutex> lock(g_env_mu);
+  g_env = read_env();
+  g_env_loaded = true;
+}
 
 // Lets the library's other translation units record a failure message.
 void set_last_error(const char *message) { g_last_error = message ? message : ""; }
@@ -138,14 +187,34 @@ constexpr double kSingleRate = 0.915;
 // kernel relative to a round of whole tiles: half the work at 0.69 of the rate.
 constexpr double kHalfItemCost = 0.72;
 
-// Whether the last, partly filled round of `tail` whole tiles on `pairs` CTA
-// pairs is better run as 2 * tail half-width items: only if those still fit
-// one round.  WAVE_CUDA_GEMM_SPLIT_TAIL=0 turns the split off.
-bool pair_tail_splits(long long tail, long long pairs) {
-  const char *env = getenv("WAVE_CUDA_GEMM_SPLIT_TAIL");
-  if (env && strcmp(env, "0") == 0)
-    return false;
-  return tail > 0 && 2 * tail <= pairs;
+// What the Stream-K treatment of a partly filled last round costs on top of
+// its share of a round, in rounds: writing and re-reading the f32 partial
+// tiles and the second pipeline fill of a worker that finishes one tile and
+// starts another.
+constexpr double kStreamKTailOverhead = 0.10;
+
+// How the CTA-pair kernel treats a last round of `tail` whole tiles on `pairs`
+// CTA pairs, and what that round then costs in rounds of whole tiles.
+enum class PairTail { kWhole, kHalfItems, kStreamK };
+struct PairTailChoice {
+  PairTail how;
+  double rounds;
+};
+PairTailChoice pair_tail_choice(long long tail, long long pairs, int k_iters, bool streamk_allowed,
+                                const wave::EnvKnobs &env) {
+  PairTailChoice best{PairTail::kWhole, tail > 0 ? 1.0 : 0.0};
+  if (tail <= 0)
+    return best;
+  // twice as many half-width items, if those still fit one round
+  if (env.gemm_split_tail && 2 * tail <= pairs && kHalfItemCost < best.rounds)
+    best = {PairTail::kHalfItems, kHalfItemCost};
+  // the tail's K iterations dealt evenly over all pairs
+  if (streamk_allowed && env.gemm_streamk_tail && k_iters >= 8 && tail * k_iters >= pairs) {
+    const double cost = static_cast<double>(tail) / static_cast<double>(pairs) + kStreamKTailOverhead;
+    if (cost < best.rounds)
+      best = {PairTail::kStreamK, cost};
+  }
+  return best;
 }
 
 int snap_tile_n(int want) {
@@ -159,57 +228,73 @@ int snap_tile_n(int want) {
 // `sms` <= 0 means "unknown" (no device query): only legal when the
 // descriptor does not ask for automatic Stream-K.
 int make_plan(const wave_gemm_desc &d, int sms, bool have_workspace, GemmPlan *plan) {
+  const wave::EnvKnobs env = wave::env_knobs();
   const int tile_m = wave::gemm_tile_m(), tile_k = wave::gemm_tile_k();
   const int want_m = 16 * d.bm * d.wave_m_tiles, want_n = 16 * d.bn * d.wave_n_tiles;
   GemmPlan p{};
   // A 128-row UMMA wastes most of its rows on a skinny M; put N on the rows
   // instead and M on the (narrow) column tile.
-  p.swapped = d.M < tile_m && d.N > d.M && !is_tile_packed(d.out_layout);
+  const bool skinny = d.M < tile_m && d.N > d.M && !is_tile_packed(d.out_layout);
+  // Column-major 16-bit C (offset n*ld + m, wave_matmul.py:1040) is the
+  // row-major output of C^T = B * A^T: swapping the operands lets the tiles
+  // leave through the TMA-store epilogue (whole 128-byte rows) instead of one
+  // 2-byte store per thread and element.  Products and the k-ascending f32
+  // accumulation are the same either way, so the result is bit-identical.
+  // (Only where the swapped tile is wide enough for that epilogue: the knobs'
+  // M tile becomes the kernel's column tile.)
+  const bool col_swap = !skinny && env.gemm_col_swap && d.out_layout == WAVE_COL_MAJOR && d.out_type != WAVE_F32 &&
+                        d.M >= 64 && d.N >= tile_m && snap_tile_n(want_m) >= 64;
+  p.swapped = skinny || col_swap;
   p.Mk = p.swapped ? d.N : d.M;
   p.Nk = p.swapped ? d.M : d.N;
-  const int want = p.swapped ? want_m : want_n;
-  p.tile_n = snap_tile_n(want);
+  const int want_mk = p.swapped ? want_n : want_m, want_nk = p.swapped ? want_m : want_n;
+  p.tile_n = snap_tile_n(want_nk);
   const int cap = snap_tile_n(p.Nk);
   if (p.tile_n > cap)
     p.tile_n = cap;
   p.tile_m = tile_m;
-  // Large tiles on a large problem go to the CTA-pair kernel (data-parallel only).
-  p.pair = !p.swapped && want_m >= wave::gemm_pair_tile_m() && want_n >= wave::gemm_pair_tile_n() &&
-           d.M >= wave::gemm_pair_tile_m() && d.N >= wave::gemm_pair_tile_n() && d.streamk_workers <= 1;
+  const bool auto_streamk = d.streamk_workers == 0 && sms > 0 && have_workspace;
+  // Large tiles on a large problem go to the CTA-pair kernel (whole tiles, with
+  // an automatic Stream-K tail when there is a workspace; explicit worker counts
+  // are the one-CTA kernel's).
+  p.pair = !skinny && want_mk >= wave::gemm_pair_tile_m() && want_nk >= wave::gemm_pair_tile_n() &&
+           p.Mk >= wave::gemm_pair_tile_m() && p.Nk >= wave::gemm_pair_tile_n() && d.streamk_workers <= 1;
   // WAVE_CUDA_GEMM_KERNEL=pair|single overrides the size heuristic below (the
   // tiling knobs and shape must still allow the pair kernel).
-  const char *force = getenv("WAVE_CUDA_GEMM_KERNEL");
-  if (force && strcmp(force, "single") == 0)
+  if (env.gemm_kernel == 1)
     p.pair = false;
+  PairTailChoice tail_choice{PairTail::kWhole, 0.0};
   if (p.pair) {
     p.tile_m = wave::gemm_pair_tile_m();
     p.tile_n = wave::gemm_pair_tile_n();
+    const long long wide = static_cast<long long>((p.Mk + 255) / 256) * ((p.Nk + 255) / 256);
+    const long long pairs = sms / 2;
+    const int k_iters = (d.K + tile_k - 1) / tile_k;
+    if (sms > 0)
+      tail_choice = pair_tail_choice(wide % pairs, pairs, k_iters, auto_streamk, env);
     // WAVE_CUDA_GEMM_KERNEL=pair128 forces the narrow pair tile (never chosen
     // automatically: its 256 x 128 x 16 MMAs run at 0.69 of the wide tile's rate).
-    if (force && strcmp(force, "pair128") == 0)
+    if (env.gemm_kernel == 3) {
       p.tile_n = 128;
-    else if (sms > 0 && !(force && strcmp(force, "pair") == 0)) {
+      tail_choice = {PairTail::kWhole, 1.0};
+    } else if (sms > 0 && env.gemm_kernel != 2) {
       // Choose between 256 x 256 pair tiles and the one-CTA kernel's 128 x 256
       // tiles by how well each fills its last round of tiles, weighted by the
       // one-CTA kernel's measured steady-state rate relative to the pair's.
-      const long long wide = static_cast<long long>((d.M + 255) / 256) * ((d.N + 255) / 256);
-      const long long single = static_cast<long long>((d.M + 127) / 128) * ((d.N + 255) / 256);
-      const long long pairs = sms / 2;
+      const long long single = static_cast<long long>((p.Mk + 127) / 128) * ((p.Nk + 255) / 256);
       const long long r_wide = (wide + pairs - 1) / pairs, r_single = (single + sms - 1) / sms;
-      const long long tail = wide % pairs;
-      // a last round that fills at most half of the pairs runs as half-width items (see pair_tail_splits)
-      const double rounds = static_cast<double>(wide / pairs) +
-                            (tail == 0 ? 0.0 : (pair_tail_splits(tail, pairs) ? kHalfItemCost : 1.0));
+      const double rounds = static_cast<double>(wide / pairs) + tail_choice.rounds;
       const double f_wide = static_cast<double>(wide) / (rounds * static_cast<double>(pairs));
       const double f_single = kSingleRate * static_cast<double>(single) / static_cast<double>(r_single * sms);
-      // A single round is all prologue and epilogue: the smaller tile's shorter tail wins there.
-      if (f_single > f_wide || (r_wide == 1 && r_single == 1))
+      // A single round is all prologue and epilogue: the smaller tile's shorter tail wins there
+      // (unless the pair kernel spreads that round's K iterations over every pair).
+      if (f_single > f_wide || (r_wide == 1 && r_single == 1 && tail_choice.how != PairTail::kStreamK))
         p.pair = false;
     }
   }
   if (!p.pair) {
     p.tile_m = tile_m;
-    p.tile_n = snap_tile_n(want);
+    p.tile_n = snap_tile_n(want_nk);
     if (p.tile_n > cap)
       p.tile_n = cap;
   }
@@ -218,13 +303,22 @@ int make_plan(const wave_gemm_desc &d, int sms, bool have_workspace, GemmPlan *p
   p.k_iters = (d.K + tile_k - 1) / tile_k;
   const long long tiles = static_cast<long long>(p.num_m) * p.num_n;
   const long long total_iters = tiles * p.k_iters;
-  if (tiles > 0x7FFFFFFF)
+  if (tiles > 0x3FFFFFFF)
     return fail(WAVE_E_INVALID, "too many output tiles");
   int workers = d.streamk_workers;
   long long dp_tiles = 0; // explicit worker counts are pure Stream-K, as in the reference
   if (workers == 0) {     // auto
     workers = 1;
-    if (sms > 0 && have_workspace && !p.pair && p.k_iters >= 8) {
+    if (auto_streamk && p.pair) {
+      // CTA-pair kernel: whole tiles for the full rounds, the last round's K
+      // iterations dealt over all pairs when pair_tail_choice found that cheaper
+      // than leaving pairs idle.
+      if (tail_choice.how == PairTail::kStreamK) {
+        const long long pairs = sms / 2;
+        workers = static_cast<int>(pairs);
+        dp_tiles = tiles - tiles % pairs;
+      }
+    } else if (auto_streamk && p.k_iters >= 8) {
       const long long full = tiles / sms, rem = tiles % sms;
       if (full < 2) {
         // at most one full round of tiles: split everything when the machine would be badly filled
@@ -250,9 +344,11 @@ int make_plan(const wave_gemm_desc &d, int sms, bool have_workspace, GemmPlan *p
     p.streamk_workers = workers;
     p.dp_tiles = static_cast<int>(dp_tiles);
     p.split_from = static_cast<int>(tiles);
-    p.grid = workers;
-    p.scratch_bytes = static_cast<size_t>(workers) * 2 * tile_m * p.tile_n * sizeof(float);
-    p.counter_bytes = static_cast<size_t>(tiles - dp_tiles) * sizeof(int);
+    p.grid = p.pair ? 2 * workers : workers;
+    // per worker two partial tiles: 128 x tile_n f32 (one CTA) or 256 x 256 (a CTA pair);
+    // one arrival counter per Stream-K tile (per CTA of the pair)
+    p.scratch_bytes = static_cast<size_t>(workers) * 2 * p.tile_m * p.tile_n * sizeof(float);
+    p.counter_bytes = static_cast<size_t>(tiles - dp_tiles) * (p.pair ? 2 : 1) * sizeof(int);
   } else {
     p.streamk_workers = 0;
     p.dp_tiles = static_cast<int>(tiles);
@@ -260,7 +356,7 @@ int make_plan(const wave_gemm_desc &d, int sms, bool have_workspace, GemmPlan *p
     p.split_from = static_cast<int>(tiles);
     if (p.pair) {
       long long items = tiles;
-      if (sms > 0 && p.tile_n == wave::gemm_pair_tile_n() && pair_tail_splits(tiles % (sms / 2), sms / 2)) {
+      if (sms > 0 && p.tile_n == wave::gemm_pair_tile_n() && tail_choice.how == PairTail::kHalfItems) {
         p.split_from = static_cast<int>(tiles - tiles % (sms / 2));
         items += tiles % (sms / 2);
       }
@@ -273,55 +369,70 @@ int make_plan(const wave_gemm_desc &d, int sms, bool have_workspace, GemmPlan *p
 }
 
 // ------------------------------------------------------- host staging arena
-struct Arena {
-  void *ptr = nullptr;
-  size_t bytes = 0;
-  int device = -1;
+// State of the host-buffer calls, one per device ordinal: a staging arena that
+// grows on demand and the three streams of the copy/compute pipeline.  A host
+// call holds its device's mutex from the first copy to the last
+// synchronisation, so calls on different GPUs run side by side and calls on
+// one GPU take turns on its arena.
+constexpr int kMaxDevices = 64;
+struct HostPipeline {
+  cudaStream_t h2d = nullptr, compute = nullptr, d2h = nullptr;
 };
-std::mutex g_arena_mu;
-Arena g_arena;
+struct DeviceHostState {
+  std::mutex mu;
+  void *arena = nullptr;
+  size_t arena_bytes = 0;
+  HostPipeline pipeline;
+  bool have_pipeline = false;
+};
+DeviceHostState g_host_state[kMaxDevices];
 
-int arena_reserve(size_t bytes, void **out) {
+int host_state_for_current_device(DeviceHostState **out) {
   int dev = 0;
   cudaError_t err = cudaGetDevice(&dev);
   if (err != cudaSuccess)
     return cuda_fail(err, "cudaGetDevice");
-  if (g_arena.device != dev || g_arena.bytes < bytes) {
-    if (g_arena.ptr && g_arena.device == dev)
-      cudaFree(g_arena.ptr);
-    g_arena = Arena{};
-    err = cudaMalloc(&g_arena.ptr, bytes);
+  if (dev < 0 || dev >= kMaxDevices)
+    return fail(WAVE_E_CUDA, "device ordinal %d is outside the %d this library keeps host-call state for", dev,
+                kMaxDevices);
+  *out = &g_host_state[dev];
+  return WAVE_OK;
+}
+
+// Caller holds st.mu and has st's device current.
+int arena_reserve(DeviceHostState &st, size_t bytes, void **out) {
+  if (st.arena_bytes < bytes) {
+    if (st.arena)
+      cudaFree(st.arena); // synchronises the device: nothing of an earlier call is still in flight on it
+    st.arena = nullptr;
+    st.arena_bytes = 0;
+    cudaError_t err = cudaMalloc(&st.arena, bytes);
     if (err != cudaSuccess)
       return cuda_fail(err, "cudaMalloc (host-call staging)");
-    g_arena.bytes = bytes;
-    g_arena.device = dev;
+    st.arena_bytes = bytes;
   }
-  *out = g_arena.ptr;
+  *out = st.arena;
   return WAVE_OK;
 }
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-// Streams of the host-buffer pipeline (per device, created on first use).
-struct HostPipeline {
-  cudaStream_t h2d = nullptr, compute = nullptr, d2h = nullptr;
-  int device = -1;
-};
-HostPipeline g_host_pipeline;
-HostPipeline *host_pipeline() {
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess)
-    return nullptr;
-  if (g_host_pipeline.device != dev) {
+// Streams of the host-buffer pipeline (created on the device's first large call).
+HostPipeline *host_pipeline(DeviceHostState &st) {
+  if (!st.have_pipeline) {
     HostPipeline hp;
     if (cudaStreamCreateWithFlags(&hp.h2d, cudaStreamNonBlocking) != cudaSuccess ||
         cudaStreamCreateWithFlags(&hp.compute, cudaStreamNonBlocking) != cudaSuccess ||
-        cudaStreamCreateWithFlags(&hp.d2h, cudaStreamNonBlocking) != cudaSuccess)
+        cudaStreamCreateWithFlags(&hp.d2h, cudaStreamNonBlocking) != cudaSuccess) {
+      for (cudaStream_t q : {hp.h2d, hp.compute, hp.d2h})
+        if (q)
+          cudaStreamDestroy(q);
       return nullptr;
-    hp.device = dev;
-    g_host_pipeline = hp;
+    }
+    st.pipeline = hp;
+    st.have_pipeline = true;
   }
-  return &g_host_pipeline;
+  return &st.pipeline;
 }
 
 // Columns of C per pipeline step of the host-buffer GEMM, or 0 to copy, compute
@@ -365,7 +476,8 @@ template <int ElemBytes> void *memref_ptr(void *m) {
 extern "C" {
 
 const char *wave_cuda_last_error(void) { return g_last_error.c_str(); }
-const char *wave_cuda_version(void) { return "wave_cuda sm_100a 0.1"; }
+const char *wave_cuda_version(void) { return "wave_cuda sm_100a 0.2"; }
+void wave_cuda_reload_env(void) { wave::reload_env_knobs(); }
 
 // runtime/wave_runtime.cpp:35-40, 46-74: data + offset (in elements).
 void *_mlir_ciface_wave_memref_to_ptr_global_i32(void *m) { return memref_ptr<4>(m); }
@@ -562,9 +674,10 @@ int wave_cuda_gemm(const wave_gemm_desc *d, const void *A, const void *B, void *
   p.k_iters = plan.k_iters;
   p.split_from = plan.split_from;
   // The descriptor's cta_group_m counts the reference's (smaller) workgroup
-  // tiles; keep the same number of rows per group, at least one 128-row block.
+  // tiles; keep the same number of rows per group, at least one row block.
   {
-    long long rows = static_cast<long long>(d->cta_group_m) * 16 * d->bm * d->wave_m_tiles;
+    const int wg_rows = plan.swapped ? 16 * d->bn * d->wave_n_tiles : 16 * d->bm * d->wave_m_tiles;
+    long long rows = static_cast<long long>(d->cta_group_m) * wg_rows;
     int g = static_cast<int>(rows / plan.tile_m);
     if (d->cta_group_m == 1)
       g = 2048 / plan.tile_m; // the reference's "no grouping" default: use the backend's own
@@ -588,20 +701,21 @@ int wave_cuda_gemm(const wave_gemm_desc *d, const void *A, const void *B, void *
   p.scratch = static_cast<float *>(workspace);
   p.counters = workspace ? reinterpret_cast<int *>(static_cast<char *>(workspace) + plan.scratch_bytes) : nullptr;
 
-  // Row-major 16-bit output (tiles of at least 64 columns) leaves through TMA stores
-  // (WAVE_CUDA_GEMM_TMA_STORE=0 keeps the per-thread stores, for measurements).
+  // 16-bit output whose kernel-space rows are contiguous (row-major C, or
+  // column-major C computed as C^T) leaves whole tiles of at least 64 columns
+  // through TMA stores (WAVE_CUDA_GEMM_TMA_STORE=0 keeps the per-thread stores,
+  // for measurements).
+  const wave::EnvKnobs env = wave::env_knobs();
+  p.l2_hints = env.gemm_l2_hints;
   CUtensorMap tc = ta;
-  if ((plan.pair || (!plan.swapped && plan.tile_n >= 64)) && d->out_layout == WAVE_ROW_MAJOR &&
-      d->out_type != WAVE_F32) {
-    const char *env = getenv("WAVE_CUDA_GEMM_TMA_STORE");
-    if (!(env && strcmp(env, "0") == 0)) {
-      const uint64_t dims[2] = {static_cast<uint64_t>(d->N), static_cast<uint64_t>(d->M)};
-      const uint64_t strides[1] = {static_cast<uint64_t>(ld) * 2};
-      const uint32_t box[2] = {64, static_cast<uint32_t>(wave::gemm_pair_box_rows())};
-      if ((rc = wave::make_tensor_map_16bit(&tc, d->out_type == WAVE_BF16, C, 2, dims, strides, box)) != WAVE_OK)
-        return rc;
-      p.c_tma = 1;
-    }
+  if ((plan.pair || plan.tile_n >= 64) && p.stride_n == 1 && !p.tile_packed && d->out_type != WAVE_F32 &&
+      plan.Nk >= 64 && env.gemm_tma_store) {
+    const uint64_t dims[2] = {static_cast<uint64_t>(plan.Nk), static_cast<uint64_t>(plan.Mk)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(ld) * 2};
+    const uint32_t box[2] = {64, static_cast<uint32_t>(wave::gemm_pair_box_rows())};
+    if ((rc = wave::make_tensor_map_16bit(&tc, d->out_type == WAVE_BF16, C, 2, dims, strides, box)) != WAVE_OK)
+      return rc;
+    p.c_tma = 1;
   }
   cudaError_t err = plan.pair ? wave::launch_gemm_pair(ta, tb, tbh, tc, p, plan.tile_n, plan.grid, static_cast<cudaStream_t>(stream))
                               : wave::launch_gemm(ta, tb, tc, p, plan.tile_n, plan.grid, static_cast<cudaStream_t>(stream));
@@ -610,27 +724,42 @@ int wave_cuda_gemm(const wave_gemm_desc *d, const void *A, const void *B, void *
   return WAVE_OK;
 }
 
-int wave_cuda_gemm_host(const wave_gemm_desc *d, const void *A_host, const void *B_host, void *C_host,
-                        void *stream) {
+} // extern "C"
+
+namespace {
+
+// Host-buffer GEMM.  `A` is a host pointer, or with `a_on_device` a device
+// pointer whose contents are ready on `stream` (a rank of a sharded problem
+// receives the replicated A over NVLink rather than once more over PCIe).
+int gemm_host_impl(const wave_gemm_desc *d, const void *A, bool a_on_device, const void *B_host, void *C_host,
+                   void *stream) {
+  const void *A_host = A;
   int rc = wave_cuda_gemm_validate(d);
   if (rc != WAVE_OK)
     return rc;
-  if (!A_host || !B_host || !C_host)
-    return fail(WAVE_E_INVALID, "A, B and C must be non-null host pointers");
+  if (!A || !B_host || !C_host)
+    return fail(WAVE_E_INVALID, "A, B and C must be non-null pointers");
+  if (a_on_device && (reinterpret_cast<uintptr_t>(A) & 15))
+    return fail(WAVE_E_INVALID, "a device-resident A must be 16-byte aligned");
   size_t scratch = 0, counters = 0;
   if ((rc = wave_cuda_gemm_workspace_bytes(d, &scratch, &counters)) != WAVE_OK)
     return rc;
-  const size_t a_bytes = static_cast<size_t>(d->M) * d->K * 2, b_bytes = static_cast<size_t>(d->N) * d->K * 2;
+  const size_t a_bytes = a_on_device ? 0 : static_cast<size_t>(d->M) * d->K * 2;
+  const size_t b_bytes = static_cast<size_t>(d->N) * d->K * 2;
   const size_t ld = d->ldc ? d->ldc : (d->out_layout == WAVE_ROW_MAJOR ? d->N : d->M);
   const size_t c_bytes = ld * (d->out_layout == WAVE_ROW_MAJOR ? d->M : d->N) * elem_size(d->out_type);
   const size_t off_b = align_up(a_bytes, 256), off_c = off_b + align_up(b_bytes, 256);
   const size_t off_ws = off_c + align_up(c_bytes, 256);
   const size_t total = off_ws + align_up(scratch, 256) + align_up(counters, 256);
-  std::lock_guard<std::mutex> lock(g_arena_mu);
+  DeviceHostState *state = nullptr;
+  if ((rc = host_state_for_current_device(&state)) != WAVE_OK)
+    return rc;
+  std::lock_guard<std::mutex> lock(state->mu);
   void *base = nullptr;
-  if ((rc = arena_reserve(total, &base)) != WAVE_OK)
+  if ((rc = arena_reserve(*state, total, &base)) != WAVE_OK)
     return rc;
   char *dev = static_cast<char *>(base);
+  const char *a_dev = a_on_device ? static_cast<const char *>(A) : dev;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaError_t err;
 
@@ -640,7 +769,7 @@ int wave_cuda_gemm_host(const wave_gemm_desc *d, const void *A_host, const void 
   // "copy A + copy B" instead of "copy A + copy B + compute + copy C".
   const int chunk = host_pipeline_chunk(*d, b_bytes + c_bytes);
   if (chunk > 0) {
-    HostPipeline *hp = host_pipeline();
+    HostPipeline *hp = host_pipeline(*state);
     if (!hp)
       return fail(WAVE_E_CUDA, "could not create the streams of the host-call pipeline");
     const int nchunks = d->N / chunk;
@@ -660,7 +789,8 @@ int wave_cuda_gemm_host(const wave_gemm_desc *d, const void *A_host, const void 
       check(cudaEventRecord(ev_start, s), "record");
       for (cudaStream_t q : {hp->h2d, hp->compute, hp->d2h})
         check(cudaStreamWaitEvent(q, ev_start, 0), "order after the caller's stream");
-      check(cudaMemcpyAsync(dev, A_host, a_bytes, cudaMemcpyHostToDevice, hp->h2d), "copy A to device");
+      if (!a_on_device)
+        check(cudaMemcpyAsync(dev, A_host, a_bytes, cudaMemcpyHostToDevice, hp->h2d), "copy A to device");
       check(cudaEventRecord(ev_a, hp->h2d), "record");
       check(cudaStreamWaitEvent(hp->compute, ev_a, 0), "wait for A");
       wave_gemm_desc sub = *d;
@@ -676,7 +806,7 @@ int wave_cuda_gemm_host(const wave_gemm_desc *d, const void *A_host, const void 
         check(cudaStreamWaitEvent(hp->compute, ev[2 * i], 0), "wait for a block of B");
         const size_t c_off = d->out_layout == WAVE_ROW_MAJOR ? static_cast<size_t>(i) * chunk * es
                                                              : static_cast<size_t>(i) * chunk * d->M * es;
-        if (!failed && wave_cuda_gemm(&sub, dev, dev + off_b + b_off, dev + off_c + c_off, nullptr, hp->compute) != WAVE_OK)
+        if (!failed && wave_cuda_gemm(&sub, a_dev, dev + off_b + b_off, dev + off_c + c_off, nullptr, hp->compute) != WAVE_OK)
           failed = true; // message already recorded
         check(cudaEventRecord(ev[2 * i + 1], hp->compute), "record");
         check(cudaStreamWaitEvent(hp->d2h, ev[2 * i + 1], 0), "wait for a block of C");
@@ -699,23 +829,44 @@ int wave_cuda_gemm_host(const wave_gemm_desc *d, const void *A_host, const void 
     return failed ? WAVE_E_CUDA : WAVE_OK;
   }
 
-  if ((err = cudaMemcpyAsync(dev, A_host, a_bytes, cudaMemcpyHostToDevice, s)) != cudaSuccess)
-    return cuda_fail(err, "copy A to device");
-  if ((err = cudaMemcpyAsync(dev + off_b, B_host, b_bytes, cudaMemcpyHostToDevice, s)) != cudaSuccess)
-    return cuda_fail(err, "copy B to device");
+  // One piece: copy, compute, copy back on the caller's stream.  Whatever
+  // fails, the stream is drained before the arena is given up to the next call.
+  rc = WAVE_OK;
+  auto step = [&](cudaError_t e, const char *what) {
+    if (rc == WAVE_OK && e != cudaSuccess)
+      rc = cuda_fail(e, what);
+    return rc == WAVE_OK;
+  };
   void *ws = nullptr;
-  if (scratch + counters > 0) {
-    ws = dev + off_ws;
-    if ((err = cudaMemsetAsync(dev + off_ws + scratch, 0, counters, s)) != cudaSuccess)
-      return cuda_fail(err, "clear Stream-K counters");
+  if ((a_on_device || step(cudaMemcpyAsync(dev, A_host, a_bytes, cudaMemcpyHostToDevice, s), "copy A to device")) &&
+      step(cudaMemcpyAsync(dev + off_b, B_host, b_bytes, cudaMemcpyHostToDevice, s), "copy B to device")) {
+    if (scratch + counters > 0) {
+      ws = dev + off_ws;
+      step(cudaMemsetAsync(dev + off_ws + scratch, 0, counters, s), "clear Stream-K counters");
+    }
+    if (rc == WAVE_OK)
+      rc = wave_cuda_gemm(d, a_dev, dev + off_b, dev + off_c, ws, stream);
+    if (rc == WAVE_OK)
+      step(cudaMemcpyAsync(C_host, dev + off_c, c_bytes, cudaMemcpyDeviceToHost, s), "copy C to host");
   }
-  if ((rc = wave_cuda_gemm(d, dev, dev + off_b, dev + off_c, ws, stream)) != WAVE_OK)
-    return rc;
-  if ((err = cudaMemcpyAsync(C_host, dev + off_c, c_bytes, cudaMemcpyDeviceToHost, s)) != cudaSuccess)
-    return cuda_fail(err, "copy C to host");
-  if ((err = cudaStreamSynchronize(s)) != cudaSuccess)
-    return cuda_fail(err, "synchronise after GEMM");
-  return WAVE_OK;
+  err = cudaStreamSynchronize(s);
+  if (rc == WAVE_OK && err != cudaSuccess)
+    rc = cuda_fail(err, "synchronise after GEMM");
+  return rc;
+}
+
+} // namespace
+
+extern "C" {
+
+int wave_cuda_gemm_host(const wave_gemm_desc *d, const void *A_host, const void *B_host, void *C_host,
+                        void *stream) {
+  return gemm_host_impl(d, A_host, false, B_host, C_host, stream);
+}
+
+int wave_cuda_gemm_host_a_resident(const wave_gemm_desc *d, const void *A_device, const void *B_host, void *C_host,
+                                   void *stream) {
+  return gemm_host_impl(d, A_device, true, B_host, C_host, stream);
 }
 
 // ------------------------------------------------------------ flash attention
@@ -798,9 +949,12 @@ int wave_cuda_flash_attention_fwd_host(const wave_fa_desc *d, const void *Q_host
   const size_t off_k = align_up(q_bytes, 256), off_v = off_k + align_up(kv_bytes, 256);
   const size_t o_bytes = d->out_f32 ? 2 * q_bytes : q_bytes;
   const size_t off_o = off_v + align_up(kv_bytes, 256), total = off_o + align_up(o_bytes, 256);
-  std::lock_guard<std::mutex> lock(g_arena_mu);
+  DeviceHostState *state = nullptr;
+  if ((rc = host_state_for_current_device(&state)) != WAVE_OK)
+    return rc;
+  std::lock_guard<std::mutex> lock(state->mu);
   void *base = nullptr;
-  if ((rc = arena_reserve(total, &base)) != WAVE_OK)
+  if ((rc = arena_reserve(*state, total, &base)) != WAVE_OK)
     return rc;
   char *dev = static_cast<char *>(base);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -817,7 +971,7 @@ int wave_cuda_flash_attention_fwd_host(const wave_fa_desc *d, const void *Q_host
         break;
       }
   if (parts > 0) {
-    HostPipeline *hp = host_pipeline();
+    HostPipeline *hp = host_pipeline(*state);
     if (!hp)
       return fail(WAVE_E_CUDA, "could not create the streams of the host-call pipeline");
     const size_t group = bh / parts;
@@ -867,19 +1021,23 @@ int wave_cuda_flash_attention_fwd_host(const wave_fa_desc *d, const void *Q_host
     return failed ? WAVE_E_CUDA : WAVE_OK;
   }
 
-  if ((err = cudaMemcpyAsync(dev, Q_host, q_bytes, cudaMemcpyHostToDevice, s)) != cudaSuccess)
-    return cuda_fail(err, "copy Q to device");
-  if ((err = cudaMemcpyAsync(dev + off_k, K_host, kv_bytes, cudaMemcpyHostToDevice, s)) != cudaSuccess)
-    return cuda_fail(err, "copy K to device");
-  if ((err = cudaMemcpyAsync(dev + off_v, V_host, kv_bytes, cudaMemcpyHostToDevice, s)) != cudaSuccess)
-    return cuda_fail(err, "copy V to device");
-  if ((rc = wave_cuda_flash_attention_fwd(d, dev, dev + off_k, dev + off_v, dev + off_o, nullptr, stream)) != WAVE_OK)
-    return rc;
-  if ((err = cudaMemcpyAsync(O_host, dev + off_o, o_bytes, cudaMemcpyDeviceToHost, s)) != cudaSuccess)
-    return cuda_fail(err, "copy O to host");
-  if ((err = cudaStreamSynchronize(s)) != cudaSuccess)
-    return cuda_fail(err, "synchronise after attention");
-  return WAVE_OK;
+  rc = WAVE_OK;
+  auto step = [&](cudaError_t e, const char *what) {
+    if (rc == WAVE_OK && e != cudaSuccess)
+      rc = cuda_fail(e, what);
+    return rc == WAVE_OK;
+  };
+  if (step(cudaMemcpyAsync(dev, Q_host, q_bytes, cudaMemcpyHostToDevice, s), "copy Q to device") &&
+      step(cudaMemcpyAsync(dev + off_k, K_host, kv_bytes, cudaMemcpyHostToDevice, s), "copy K to device") &&
+      step(cudaMemcpyAsync(dev + off_v, V_host, kv_bytes, cudaMemcpyHostToDevice, s), "copy V to device")) {
+    rc = wave_cuda_flash_attention_fwd(d, dev, dev + off_k, dev + off_v, dev + off_o, nullptr, stream);
+    if (rc == WAVE_OK)
+      step(cudaMemcpyAsync(O_host, dev + off_o, o_bytes, cudaMemcpyDeviceToHost, s), "copy O to host");
+  }
+  err = cudaStreamSynchronize(s); // also on failure: the arena goes to the next call
+  if (rc == WAVE_OK && err != cudaSuccess)
+    rc = cuda_fail(err, "synchronise after attention");
+  return rc;
 }
 
 // ------------------------------------------------------- name-based facade

@@ -45,3 +45,40 @@ def all_gather_shards(local, dist, group=None):
     flat = torch.empty(world * local.numel(), dtype=local.dtype, device=local.device)
     dist.all_gather_into_tensor(flat, local.reshape(-1), group=group)
     return flat.reshape((world,) + tuple(local.shape))
+
+
+def row_shard(m_total: int, world: int, rank: int, align: int = 16) -> tuple[int, int]:
+    """[begin, end) of the rows of the replicated A that `rank` brings to the
+    device from its host before the ranks exchange them (same split as
+    column_shard)."""
+    return column_shard(m_total, world, rank, align)
+
+
+def gather_replicated_rows(a_full_dev, a_host, dist, rank: int, world: int, group=None):
+    """Fills `a_full_dev` (device, [M, K]) with the replicated operand A, of
+    which every rank holds a host copy `a_host` (pinned, [M, K]): each rank
+    copies only its M/world rows over PCIe and the ranks exchange them with
+    one all-gather over NVLink, so that the host links carry A once in total
+    instead of once per GPU.  With one rank it is a plain copy."""
+    if world == 1:
+        a_full_dev.copy_(a_host, non_blocking=True)
+        return
+    m_total = a_full_dev.shape[0]
+    if m_total % (16 * world):
+        raise ValueError(f"M must be a multiple of {16 * world} for an even row exchange; got {m_total}")
+    r0, r1 = row_shard(m_total, world, rank)
+    a_full_dev[r0:r1].copy_(a_host[r0:r1], non_blocking=True)
+    dist.all_gather_into_tensor(a_full_dev.reshape(-1), a_full_dev[r0:r1].reshape(-1), group=group)
+
+
+def sharded_gemm_host(wc, desc_shard, a_full_dev, a_host, b_host_shard, c_host_shard, dist, rank: int, world: int,
+                      stream: int, group=None) -> None:
+    """One rank's part of C = A * B^T with B and C split by N-column blocks and
+    every operand starting and ending in (pinned) host memory: A reaches the
+    device by gather_replicated_rows, the rank's B block and C block travel
+    through the library's host-buffer call.  `desc_shard` describes the rank's
+    block (N = its columns; column-major C makes the block contiguous,
+    python/mlir/dialects/wave_matmul.py:1040)."""
+    gather_replicated_rows(a_full_dev, a_host, dist, rank, world, group)
+    wc.gemm_host_a_resident(desc_shard, a_full_dev.data_ptr(), b_host_shard.data_ptr(), c_host_shard.data_ptr(),
+                            stream)

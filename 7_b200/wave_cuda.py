@@ -43,13 +43,13 @@ class FaDesc(C.Structure):
 
 
 EXPORTS = [
-    "wave_cuda_last_error", "wave_cuda_version",
+    "wave_cuda_last_error", "wave_cuda_version", "wave_cuda_reload_env",
     "_mlir_ciface_wave_memref_to_ptr_global_i32", "_mlir_ciface_wave_memref_to_ptr_global_i8",
     "_mlir_ciface_wave_memref_to_ptr_global_f32", "_mlir_ciface_wave_memref_to_ptr_global_f16",
     "_mlir_ciface_wave_memref_to_ptr_global_bf16", "_mlir_ciface_wave_memref_to_ptr_global_i64",
     "_mlir_ciface_wave_memref_to_ptr_global_f64",
     "wave_cuda_gemm_desc_init", "wave_cuda_gemm_validate", "wave_cuda_gemm_workspace_bytes", "wave_cuda_gemm",
-    "wave_cuda_gemm_host", "wave_cuda_gemm_plan", "wave_cuda_gemm_streamk_static", "wave_cuda_fa_validate", "wave_cuda_flash_attention_fwd",
+    "wave_cuda_gemm_host", "wave_cuda_gemm_host_a_resident", "wave_cuda_gemm_plan", "wave_cuda_gemm_streamk_static", "wave_cuda_fa_validate", "wave_cuda_flash_attention_fwd",
     "wave_cuda_flash_attention_fwd_host", "wave_cuda_module_get_function", "wave_cuda_launch",
     "wave_cuda_function_release", "wave_cuda_check_device_status",
     # include/wave_mgpu.h: the wrappers a host module lowered by gpu-to-llvm calls
@@ -77,7 +77,9 @@ def lib() -> C.CDLL:
     vp, ip = C.c_void_p, C.POINTER(C.c_int)
     L.wave_cuda_last_error.restype = C.c_char_p
     L.wave_cuda_version.restype = C.c_char_p
-    for name in EXPORTS[2:9]:
+    L.wave_cuda_reload_env.restype = None
+    L.wave_cuda_reload_env.argtypes = []
+    for name in EXPORTS[3:10]:
         getattr(L, name).restype = vp
         getattr(L, name).argtypes = [vp]
     L.wave_cuda_gemm_desc_init.argtypes = [C.POINTER(GemmDesc), C.c_int, C.c_int, C.c_int]
@@ -86,6 +88,7 @@ def lib() -> C.CDLL:
     L.wave_cuda_gemm_workspace_bytes.argtypes = [C.POINTER(GemmDesc), C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]
     L.wave_cuda_gemm.argtypes = [C.POINTER(GemmDesc), vp, vp, vp, vp, vp]
     L.wave_cuda_gemm_host.argtypes = [C.POINTER(GemmDesc), vp, vp, vp, vp]
+    L.wave_cuda_gemm_host_a_resident.argtypes = [C.POINTER(GemmDesc), vp, vp, vp, vp]
     L.wave_cuda_gemm_streamk_static.argtypes = [C.POINTER(GemmDesc), vp, vp, vp, vp]
     L.wave_cuda_gemm_plan.argtypes = [C.POINTER(GemmDesc), ip, ip, ip, ip, ip]
     L.wave_cuda_fa_validate.argtypes = [C.POINTER(FaDesc)]
@@ -127,6 +130,12 @@ def module_blob(kind: int, desc) -> bytes:
     buf = C.create_string_buffer(n.value)
     check(lib().wave_cuda_module_blob_write(kind, C.byref(desc), buf, n.value))
     return buf.raw
+
+
+def reload_env() -> None:
+    """Has the library read its WAVE_CUDA_* environment knobs again (it reads
+    them once by itself); call after changing os.environ."""
+    lib().wave_cuda_reload_env()
 
 
 def check(rc: int) -> None:
@@ -173,6 +182,11 @@ def gemm_streamk_static(desc: GemmDesc, a_ptr: int, b_ptr: int, c_ptr: int, stre
 
 def gemm_host(desc: GemmDesc, a_ptr: int, b_ptr: int, c_ptr: int, stream: int = 0) -> None:
     check(lib().wave_cuda_gemm_host(C.byref(desc), a_ptr, b_ptr, c_ptr, stream or None))
+
+
+def gemm_host_a_resident(desc: GemmDesc, a_dev_ptr: int, b_ptr: int, c_ptr: int, stream: int = 0) -> None:
+    """Host-buffer GEMM of one rank's column block with the replicated A already on the device."""
+    check(lib().wave_cuda_gemm_host_a_resident(C.byref(desc), a_dev_ptr, b_ptr, c_ptr, stream or None))
 
 
 def fa_desc(batch: int, heads: int, seq_q: int, seq_k: int, head_dim: int = 128, *, scale: float = 0.0,

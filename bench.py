@@ -1,18 +1,25 @@
 #!/usr/bin/env python
 """Benchmark of the B200 backend for the Wave GEMM / flash-attention hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload gemm|fa|skinny]
-                    [--impl ours|reference] [--gather]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload gemm|fa|fa_published|skinny]
+                    [--impl ours|reference] [--scaling strong|weak] [--no-gather]
 
 One "step" is one pass of the hot path over one batch of synthetic input.  The
 headline workload (default) is the bf16 GEMM M=N=K=8192 with f32 accumulation
-and bf16 output; with N GPUs every rank owns one 8192-column block of a C that
-is N times wider (weak scaling, no collective in the timed region; --gather
-adds and separately times the NCCL all-gather of C).  `--workload fa` is the
-causal flash-attention forward B=16 H=32 S=4096 D=128 (batch x head sharded),
-`--workload skinny` the M=16, N=28672, K=8192 decode-shaped GEMM.  The default
-run also measures the other two workloads briefly and reports them under
-"also".  Prints ONE JSON line on rank 0.
+and bf16 output.  With N GPUs it stays ONE 8192^3 problem (strong scaling):
+rank r computes the N-column block `column_shard(8192, N, r)` of C from the
+replicated A and its rows of B, into the reference's column-major layout
+(offset n*M + m, python/mlir/dialects/wave_matmul.py:1040) in which the block
+is contiguous; `value` is the whole problem's FLOP over the slowest rank's
+compute time.  The NCCL all-gather that gives every rank the whole C is timed
+separately (`gather`), and rows of the GATHERED matrix are checked against the
+CPU oracle, so that columns computed by every rank are compared.
+`--workload fa` is the causal flash-attention forward B=16 H=32 S=4096 D=128,
+its 512 (batch, head) slabs split over the ranks the same way; `--workload
+skinny` the M=16, N=28672, K=8192 decode-shaped GEMM (single-GPU by
+definition: N independent replicas).  `--scaling weak` gives every rank the
+whole single-GPU problem instead.  The default run also measures the other
+workloads briefly and reports them under "also".  Prints ONE JSON line on rank 0.
 
 `--impl reference` times the reference's own CPU implementation of the same
 path (its calibrate runner's host code compiled as a shared object, else the
@@ -37,11 +44,11 @@ sys.path.insert(0, ROOT)
 
 METRIC = "TFLOP/s + % tensor roofline: GEMM 8192^3 bf16, FA-fwd S=4096 d=128 @1/2/4/8 B200"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from one ncu capture of
-# the same kernel (summaries under profiles/): gemm and skinny at full size; fa
-# captured at B=2 (250.58 MB) and scaled by the 8x heads of the B=16 workload,
-# since every head moves the same bytes; fa_published at full size.
-NCU_TRAFFIC_BYTES = {"gemm": 1203.57e6, "fa": 8 * 251.89e6, "skinny": 477.11e6, "fa_published": 1055.49e6}
+NVLINK_PEER_GBS = 770.0  # measured peer copy per direction on this pool (nominal 900)
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the single-GPU
+# workload from one ncu capture of the same kernel (summaries under
+# profiles/, each captured at the workload's full size).
+NCU_TRAFFIC_BYTES = {"gemm": 1203.57e6, "fa": None, "skinny": 477.11e6, "fa_published": 1055.49e6}
 
 WORKLOADS = {
     "gemm": dict(name="gemm_bf16_8192x8192x8192_f32acc_bf16out", M=8192, N=8192, K=8192),
@@ -74,12 +81,15 @@ def host_threads() -> int:
 # clocks
 # ----------------------------------------------------------------------------
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while a timed
-    region runs (reading only; no setting is changed)."""
+    """Samples SM clocks and throttle reasons with nvidia-smi while timed
+    regions run (reading only; no setting is changed).  One sampler runs for
+    the whole benchmark; each timed region is summarised from the samples whose
+    timestamps fall inside it."""
 
     FIELDS = ("timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
+              "clocks_event_reasons.sw_power_cap,power.draw")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self, index: int):
         self.index = index
@@ -100,114 +110,183 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
-    def stop(self, t_begin: float | None = None, t_end: float | None = None) -> dict:
-        """Summarises the samples whose timestamp falls inside [t_begin, t_end]
-        (host wall-clock seconds); all samples if no window is given or none
-        fell inside it."""
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
+    def _rows(self):
         import datetime
         rows = []
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        for line in list(self.lines):
             parts = [x.strip() for x in line.split(",")]
             if len(parts) < 7:
                 continue
             try:
                 ts = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                power = float(parts[7]) if len(parts) > 7 else None
                 rows.append((ts, float(parts[1]), float(parts[2]),
-                             [n for n, v in zip(names, parts[3:7]) if v.lower().startswith("active")]))
+                             [n for n, v in zip(self.NAMES, parts[3:7]) if v.lower().startswith("active")], power))
             except ValueError:
                 continue
+        return rows
+
+    def window(self, t_begin: float | None = None, t_end: float | None = None) -> dict:
+        """Summary of the samples inside [t_begin, t_end] (host wall-clock
+        seconds); of all samples if no window is given or none fell inside it."""
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        rows = self._rows()
         inside = [r for r in rows if t_begin is not None and t_begin <= r[0] <= t_end]
-        window = "timed region" if inside else "whole run"
         use = inside or rows
-        reasons = sorted({n for r in use for n in r[3]})
+        powers = [r[4] for r in use if r[4] is not None]
         return {"sm_mhz": statistics.median([r[1] for r in use]) if use else None,
                 "sm_max_mhz": max([r[2] for r in use]) if use else None,
-                "reasons": reasons, "samples": len(use), "window": window}
+                "reasons": sorted({n for r in use for n in r[3]}), "samples": len(use),
+                "window": "timed region" if inside else "whole run",
+                "power_w_max": max(powers) if powers else None}
+
+    def stop(self):
+        if self.proc is None:
+            return
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
 
 
 # ----------------------------------------------------------------------------
 # workloads on the GPU
 # ----------------------------------------------------------------------------
 class GemmWork:
-    def __init__(self, torch, wc, M, N, K, rank, world, seed=0, streamk=1):
-        self.torch, self.wc = torch, wc
-        self.M, self.N, self.K = M, N, K
+    """C = A * B^T, bf16 in, f32 accumulate, bf16 out.  strong: one M x N x K
+    problem, this rank owns the columns column_shard(N, world, rank); weak: the
+    whole problem on every rank (its own B).  C is column-major (this rank's
+    block [n_local][M] is contiguous and gathers in place)."""
+
+    kind = "gemm"
+
+    def __init__(self, torch, wc, sh, M, N, K, rank, world, strong, seed=0, streamk=0):
+        self.torch, self.wc, self.sh = torch, wc, sh
+        self.M, self.N, self.K, self.rank, self.world, self.strong = M, N, K, rank, world, strong
         g = torch.Generator(device="cuda")
         g.manual_seed(1234 + seed)
-        # A is replicated across ranks (same seed); each rank has its own B block.
+        # A is replicated across ranks (same seed).
         self.a = (torch.randn(M, K, device="cuda", generator=g) * (K ** -0.5 if M > 16 else 1.0)).to(torch.bfloat16)
-        g.manual_seed(4321 + seed + 977 * rank)
-        self.b = (torch.randn(N, K, device="cuda", generator=g) * K ** -0.5).to(torch.bfloat16)
-        self.c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
-        knobs = dict(bm=4, bn=4, wave_m_tiles=4, wave_n_tiles=4) if M % 256 == 0 else dict(bn=1)
-        self.desc = wc.gemm_desc(M, N, K, in_type=wc.BF16, out_type=wc.BF16, streamk_workers=streamk, **knobs)
+        g.manual_seed(4321 + seed + (0 if strong else 977 * rank))
+        b_full = (torch.randn(N, K, device="cuda", generator=g) * K ** -0.5).to(torch.bfloat16)
+        self.skinny = M % 256 != 0
+        if strong and world > 1:
+            self.n0, self.n1 = sh.column_shard(N, world, rank, 256)
+        else:
+            self.n0, self.n1 = 0, N
+        self.b_full = b_full if (strong and rank == 0) else None  # rank 0 checks the gathered C against all of B
+        self.b = b_full[self.n0:self.n1].contiguous() if strong and world > 1 else b_full
+        self.nl = self.n1 - self.n0
+        knobs = dict(bm=4, bn=4, wave_m_tiles=4, wave_n_tiles=4) if not self.skinny else dict(bn=1)
+        layout = wc.ROW_MAJOR if self.skinny else wc.COL_MAJOR
+        self.col_major = layout == wc.COL_MAJOR
+        self.c = torch.empty((self.nl, M) if self.col_major else (M, self.nl), device="cuda", dtype=torch.bfloat16)
+        self.desc = wc.gemm_desc(M, self.nl, K, in_type=wc.BF16, out_type=wc.BF16, out_layout=layout,
+                                 streamk_workers=streamk, **knobs)
         s, c = wc.gemm_workspace_bytes(self.desc)
         self.ws = torch.zeros(s + c, dtype=torch.uint8, device="cuda") if s + c else None
-        self.flops = 2.0 * M * N * K
-        self.alg_bytes = 2.0 * (M * K + N * K + M * N)
+        total_n = N if strong else N * world
+        self.flops = 2.0 * M * total_n * K                 # whole job, all ranks
+        self.flops_rank = 2.0 * M * self.nl * K
+        self.alg_bytes = 2.0 * (M * K + self.nl * K + M * self.nl)  # this rank's launch
         self.launches_per_step = 1
-        self.h2d = 2 * (M * K + N * K)
-        self.d2h = 2 * M * N
         self.host = None
 
     def step(self, stream):
         self.wc.gemm(self.desc, self.a.data_ptr(), self.b.data_ptr(), self.c.data_ptr(),
                      self.ws.data_ptr() if self.ws is not None else 0, stream)
 
+    # ---- end to end: every operand starts and ends in pinned host memory
     def prepare_host(self):
         t = self.torch
-        self.host = (self.a.cpu().pin_memory(), self.b.cpu().pin_memory(),
-                     t.empty(self.M, self.N, dtype=t.bfloat16).pin_memory())
+        self.host = (self.a.cpu().pin_memory(), self.b.cpu().pin_memory(), t.empty_like(self.c, device="cpu").pin_memory())
+        sharded = self.strong and self.world > 1
+        self.a_stage = t.empty_like(self.a) if sharded else None
+        a_rows = self.M // self.world if sharded else self.M
+        self.h2d = 2 * (a_rows * self.K + self.nl * self.K)
+        self.d2h = 2 * self.M * self.nl
 
-    def step_host(self, stream):
+    def step_host(self, stream, dist=None):
         a, b, c = self.host
-        self.wc.gemm_host(self.desc, a.data_ptr(), b.data_ptr(), c.data_ptr(), stream)
+        if self.a_stage is not None:
+            self.sh.sharded_gemm_host(self.wc, self.desc, self.a_stage, a, b, c, dist, self.rank, self.world, stream)
+        else:
+            self.wc.gemm_host(self.desc, a.data_ptr(), b.data_ptr(), c.data_ptr(), stream)
 
-    def check(self, oracle) -> float:
-        """Sampled parity check outside the timed region: a few rows against the
-        CPU oracle (f32 accumulate, k ascending)."""
+    def host_result(self):
+        return self.host[2]
+
+    # ---- the all-gather that gives every rank the whole output
+    def local_output(self):
+        return self.c
+
+    def check(self, oracle, gathered=None) -> dict:
+        """Sampled parity outside the timed region: 8 rows of C (all columns, so
+        every rank's block of a gathered C is compared) against the CPU oracle
+        (f32 accumulate, k ascending)."""
+        t = self.torch
         rows = np.unique(np.linspace(0, self.M - 1, 8).astype(np.int32))
-        a = self.a.cpu().view(self.torch.int16).numpy().view(np.uint16)
-        b = self.b.cpu().view(self.torch.int16).numpy().view(np.uint16)
+        a = self.a.cpu().view(t.int16).numpy().view(np.uint16)
+        if gathered is not None:
+            b_src, c_src, what = self.b_full, gathered.reshape(self.N, self.M), f"gathered C, columns of all {self.world} ranks"
+        else:
+            b_src, c_src, what = self.b, self.c, "this rank's C"
+        b = b_src.cpu().view(t.int16).numpy().view(np.uint16)
         want = oracle.round_output(oracle.gemm_ref(a, b, oracle.BF16, rows=rows), "bf16")
-        got = self.c.float().cpu().numpy()[rows]
-        return float(np.max(np.abs(got - want) / (1.0e-2 + 2.0 ** -7 * np.abs(want))))
+        got = (c_src[:, rows.tolist()].float().cpu().numpy().T if self.col_major
+               else c_src[rows.tolist()].float().cpu().numpy())
+        worst = float(np.max(np.abs(got - want) / (1.0e-2 + 2.0 ** -7 * np.abs(want))))
+        return {"worst_over_tolerance": worst, "checked": what, "rows": int(rows.size), "columns": int(want.shape[1]),
+                "tolerance": "|d| <= 1e-2 + 2^-7*|exp| (bf16 output: one ulp in place of the runner's 1e-3 term)"}
+
+    def check_host(self, oracle) -> float:
+        """The end-to-end call's host result against the device-resident run's bits."""
+        return float((self.host_result().view(self.torch.int16) != self.c.cpu().view(self.torch.int16)).sum().item())
 
 
 class FaWork:
-    def __init__(self, torch, wc, B, H, S, D, rank, world, seed=0, causal=True, qk_max_abs=0.0):
-        self.torch, self.wc = torch, wc
+    """Flash-attention forward; strong: B*H slabs split by head_shard."""
+
+    kind = "fa"
+
+    def __init__(self, torch, wc, sh, B, H, S, D, rank, world, strong, seed=0, causal=True, qk_max_abs=0.0):
+        self.torch, self.wc, self.sh = torch, wc, sh
         self.B, self.H, self.S, self.D, self.causal = B, H, S, D, causal
+        self.rank, self.world, self.strong = rank, world, strong
+        BH = B * H
         g = torch.Generator(device="cuda")
-        g.manual_seed(99 + seed + 131 * rank)
+        g.manual_seed(99 + seed + (0 if strong else 131 * rank))
         if qk_max_abs > 0.0:
             # the value set of the reference runner's generator (17 buckets, Q/K x0.125, V x0.25;
             # wave-fa-gfx950-runner.cpp:188-202), drawn from torch's generator
-            mk = lambda scale: (torch.randint(-8, 9, (B * H, S, D), device="cuda", generator=g).float()
+            mk = lambda scale: (torch.randint(-8, 9, (BH, S, D), device="cuda", generator=g).float()
                                 * scale).to(torch.bfloat16)
-            self.q, self.k, self.v = mk(0.125), mk(0.125), mk(0.25)
+            q, k, v = mk(0.125), mk(0.125), mk(0.25)
         else:
-            mk = lambda: torch.randn(B * H, S, D, device="cuda", generator=g).to(torch.bfloat16)
-            self.q, self.k, self.v = mk(), mk(), mk()
+            mk = lambda: torch.randn(BH, S, D, device="cuda", generator=g).to(torch.bfloat16)
+            q, k, v = mk(), mk(), mk()
+        if strong and world > 1:
+            self.h0, self.h1 = sh.head_shard(BH, world, rank)
+            self.full = (q, k, v) if rank == 0 else None  # rank 0 checks heads of every rank's slab
+            q, k, v = (x[self.h0:self.h1] for x in (q, k, v))
+        else:
+            self.h0, self.h1 = 0, BH
+            self.full = None
+        self.q, self.k, self.v = q, k, v
+        self.hl = self.h1 - self.h0
         self.o = torch.empty_like(self.q)
-        self.desc = wc.fa_desc(B, H, S, S, D, causal=causal, io_type=wc.BF16, qk_max_abs=qk_max_abs)
+        self.desc = wc.fa_desc(1, self.hl, S, S, D, causal=causal, io_type=wc.BF16, qk_max_abs=qk_max_abs)
         # unmasked pairs only for the causal case; the reference's own formula
         # (4*B*H*S^2*D, wave-fa-gfx950-runner.cpp:465-466) counts the full square
         pairs = S * (S + 1) / 2 if causal else float(S) * S
-        self.flops = 4.0 * B * H * D * pairs
-        self.flops_full_square = 4.0 * B * H * D * float(S) * S
-        self.alg_bytes = 4.0 * B * H * S * D * 2
+        total_bh = BH if strong else BH * world
+        self.flops = 4.0 * total_bh * D * pairs
+        self.flops_rank = 4.0 * self.hl * D * pairs
+        self.flops_full_square = 4.0 * total_bh * D * float(S) * S
+        self.alg_bytes = 4.0 * self.hl * S * D * 2
         self.launches_per_step = 1
-        self.h2d = 3 * B * H * S * D * 2
-        self.d2h = B * H * S * D * 2
         self.host = None
 
     def step(self, stream):
@@ -218,27 +297,43 @@ class FaWork:
         t = self.torch
         self.host = tuple(x.cpu().pin_memory() for x in (self.q, self.k, self.v)) + (
             t.empty(self.q.shape, dtype=t.bfloat16).pin_memory(),)
+        self.h2d = 3 * self.hl * self.S * self.D * 2
+        self.d2h = self.hl * self.S * self.D * 2
 
-    def step_host(self, stream):
+    def step_host(self, stream, dist=None):
         q, k, v, o = self.host
         self.wc.flash_attention_fwd_host(self.desc, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), stream)
 
-    def check(self, oracle) -> float:
-        BH = self.B * self.H
-        heads = oracle.fa_sample_heads(BH)
+    def host_result(self):
+        return self.host[3]
+
+    def local_output(self):
+        return self.o
+
+    def check(self, oracle, gathered=None) -> dict:
+        if gathered is not None:
+            q, k, v = self.full
+            o, what = gathered.reshape(q.shape), f"gathered O, heads of the first, middle and last rank of {self.world}"
+        else:
+            q, k, v, o, what = self.q, self.k, self.v, self.o, "this rank's O"
+        heads = oracle.fa_sample_heads(q.shape[0])
         rows = oracle.fa_sample_rows(self.S)
         bits = lambda x: x[heads.tolist()].cpu().view(self.torch.int16).numpy().view(np.uint16)
-        want = oracle.fa_ref(bits(self.q), bits(self.k), bits(self.v), oracle.BF16, 1.0 / np.sqrt(self.D),
-                             causal=self.causal, rows=rows)
-        got = self.o[heads.tolist()].float().cpu().numpy()[:, rows]
-        return float(np.max(np.abs(got - want)) / 3.0e-2)
+        want = oracle.fa_ref(bits(q), bits(k), bits(v), oracle.BF16, 1.0 / np.sqrt(self.D), causal=self.causal, rows=rows)
+        got = o[heads.tolist()].float().cpu().numpy()[:, rows]
+        return {"worst_over_tolerance": float(np.max(np.abs(got - want)) / 3.0e-2), "checked": what,
+                "heads": [int(h) for h in heads], "rows": int(rows.size),
+                "tolerance": "max abs <= 3e-2 (wave-fa-gfx950-runner.cpp:388) on the runner's head/row sample"}
+
+    def check_host(self, oracle) -> float:
+        return float((self.host_result().view(self.torch.int16) != self.o.cpu().view(self.torch.int16)).sum().item())
 
 
 def time_steps(torch, work, steps, warmup, stream, dist=None, host=False):
     """W untimed warm-up steps, then exactly K steps between two CUDA events on
     the launching stream, bracketed by barrier + synchronize; returns the
     maximum over ranks of the elapsed milliseconds."""
-    fn = work.step_host if host else work.step
+    fn = (lambda s: work.step_host(s, dist)) if host else work.step
     for _ in range(warmup):
         fn(stream.cuda_stream)
     torch.cuda.synchronize()
@@ -263,12 +358,145 @@ def time_steps(torch, work, steps, warmup, stream, dist=None, host=False):
     return ms
 
 
-def make_work(torch, wc, workload, rank, world):
+def make_work(torch, wc, sh, workload, rank, world, strong):
     w = WORKLOADS[workload]
     if workload.startswith("fa"):
-        return FaWork(torch, wc, w["B"], w["H"], w["S"], w["D"], rank, world, causal=w.get("causal", True),
+        return FaWork(torch, wc, sh, w["B"], w["H"], w["S"], w["D"], rank, world, strong, causal=w.get("causal", True),
                       qk_max_abs=w.get("qk_max_abs", 0.0))
-    return GemmWork(torch, wc, w["M"], w["N"], w["K"], rank, world, streamk=0 if workload == "skinny" else 1)
+    # the skinny GEMM is a single-GPU configuration: N independent replicas
+    return GemmWork(torch, wc, sh, w["M"], w["N"], w["K"], rank, world, strong and workload != "skinny")
+
+
+def time_gather(torch, sh, work, dist, stream, world) -> tuple[dict, object]:
+    """The NCCL all-gather of the ranks' output blocks (column-major C blocks /
+    O slabs, contiguous and equally sized), timed by itself, max over ranks."""
+    local = work.local_output()
+    full = None
+    for _ in range(3):
+        full = sh.all_gather_shards(local, dist)
+    torch.cuda.synchronize()
+    dist.barrier()
+    iters = 10
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(iters):
+        full = sh.all_gather_shards(local, dist)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    nbytes = local.numel() * local.element_size()
+    recv_gbs = (world - 1) * nbytes / (ms * 1e-3) / 1e9
+    return {"collective": "ncclAllGather over NVLink (torch.distributed all_gather_into_tensor)", "ms": ms,
+            "bytes_per_rank": nbytes, "received_gbs_per_rank": recv_gbs,
+            "frac_of_nvlink_peer_copy": recv_gbs / NVLINK_PEER_GBS, "nvlink_peer_copy_gbs": NVLINK_PEER_GBS}, full
+
+
+def sustained_leg(torch, work, stream, sampler, seconds, pk) -> dict:
+    """Back-to-back launches for about `seconds` (the power-capped regime a
+    short burst never reaches), with the SM clock sampled meanwhile."""
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(3):
+        work.step(stream.cuda_stream)
+    torch.cuda.synchronize()
+    probe = 10
+    e0.record(stream)
+    for _ in range(probe):
+        work.step(stream.cuda_stream)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    per = max(e0.elapsed_time(e1) / probe, 1e-3)
+    n = int(min(max(seconds * 1e3 / per, 20), 20000))
+    t0 = time.time()
+    e0.record(stream)
+    for _ in range(n):
+        work.step(stream.cuda_stream)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    t1 = time.time()
+    ms = e0.elapsed_time(e1) / n
+    clk = sampler.window(t0 + 0.3 * (t1 - t0), t1) if sampler is not None else {}
+    tflops = work.flops_rank / (ms * 1e-3) / 1e12
+    out = {"launches": n, "seconds": (t1 - t0), "ms_per_launch": ms, "tflops": tflops,
+           "frac_of_sustained_peak": tflops / pk["bf16_tflops_sustained"], "sm_mhz_median": clk.get("sm_mhz"),
+           "reasons": clk.get("reasons"), "power_w_max": clk.get("power_w_max")}
+    if clk.get("sm_mhz"):
+        out["ms_x_mhz"] = ms * clk["sm_mhz"]  # clock-independent cost: milliseconds at 1 MHz
+    return out
+
+
+def cublas_comparison(torch, work, stream, seconds=2.5) -> dict:
+    """This library's GEMM against torch.matmul (cuBLAS) on the same operands,
+    interleaved in one loop so that both run under the same power cap and
+    clocks: blocks of launches take turns, each block timed with CUDA events."""
+    a, b = work.a, work.b
+    out = torch.empty(a.shape[0], b.shape[0], device="cuda", dtype=torch.bfloat16)
+    bt = b.t()
+    ours = lambda: work.step(stream.cuda_stream)
+    theirs = lambda: torch.matmul(a, bt, out=out)
+    for _ in range(3):
+        ours()
+        theirs()
+    torch.cuda.synchronize()
+
+    def block(fn, n):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(n):
+            fn()
+        e1.record(stream)
+        return e0, e1, n
+    # burst: a short block each after an idle moment
+    burst = {}
+    for name, fn in (("ours", ours), ("cublas", theirs)):
+        time.sleep(0.5)
+        e0, e1, n = block(fn, 10)
+        torch.cuda.synchronize()
+        burst[name] = work.flops_rank / (e0.elapsed_time(e1) / n * 1e-3) / 1e12
+    # sustained: alternate blocks of 40 launches until the time is up; the first third is warm-up
+    blocks = []
+    t_end = time.time() + seconds
+    while time.time() < t_end:
+        blocks.append(("ours",) + block(ours, 40))
+        blocks.append(("cublas",) + block(theirs, 40))
+        torch.cuda.synchronize()
+    keep = blocks[len(blocks) // 3:]
+    rate = {}
+    for name in ("ours", "cublas"):
+        ms = [e0.elapsed_time(e1) / n for nm, e0, e1, n in keep if nm == name]
+        rate[name] = work.flops_rank / (statistics.median(ms) * 1e-3) / 1e12
+    return {"ours_tflops_sustained": rate["ours"], "cublas_tflops_sustained": rate["cublas"],
+            "ratio_sustained": rate["ours"] / rate["cublas"], "ours_tflops_burst": burst["ours"],
+            "cublas_tflops_burst": burst["cublas"], "ratio_burst": burst["ours"] / burst["cublas"],
+            "how": "torch.matmul(A, B^T) on the same bf16 operands; blocks of 40 launches taking turns for "
+                   f"{seconds} s (median of the last two thirds), and 10-launch bursts after 0.5 s idle",
+            "launches": 20 + 40 * len(blocks) // 2}
+
+
+def roofline_for(workload, work, ms_per_step, clocks, pk, pk_kind) -> dict:
+    """Roofline of this rank's launch: algorithmic FLOP (or bytes) over the
+    measured launch duration against the measured peak."""
+    if workload == "skinny":
+        roof = {"bound": "hbm", "achieved": work.alg_bytes / (ms_per_step * 1e-3) / 1e9, "peak": pk["hbm_gbs"],
+                "unit": "GB/s", "peak_kind": f"copy bandwidth ({pk_kind})"}
+    else:
+        # Under a long back-to-back loop the part runs into its power cap and the
+        # SM clock drops; the matching denominator is then the sustained cuBLAS
+        # figure, otherwise the burst one.
+        capped = bool(clocks and clocks.get("sm_mhz") and "sw_power_cap" in (clocks.get("reasons") or [])
+                      and clocks["sm_mhz"] < 0.85 * clocks["sm_max_mhz"])
+        achieved = work.flops_rank / (ms_per_step * 1e-3) / 1e12
+        roof = {"bound": "tensor", "achieved": achieved,
+                "peak": pk["bf16_tflops_sustained"] if capped else pk["bf16_tflops"], "unit": "TFLOP/s",
+                "peak_kind": ("sustained, power-capped clocks" if capped else "burst") + f" ({pk_kind})",
+                "frac_of_burst_peak": achieved / pk["bf16_tflops"], "frac_of_nominal_2250": achieved / 2250.0}
+    roof["frac"] = roof["achieved"] / roof["peak"]
+    single_gpu_problem = work.world == 1 or not work.strong
+    roof["traffic"] = NCU_TRAFFIC_BYTES.get(workload) if single_gpu_problem else None
+    roof["algorithmic_bytes"] = work.alg_bytes
+    roof["kernel_ms"] = ms_per_step
+    return roof
 
 
 # ----------------------------------------------------------------------------
@@ -355,7 +583,8 @@ def run_reference_arm(args) -> None:
         "impl": "reference", "metric": METRIC, "value": best["value"], "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": len(results), "warmup": warm, "steps_requested": args.steps, "warmup_requested": args.warmup,
         "ms_per_step": best["seconds"] * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "scaling": "strong" if args.scaling == "strong" and args.workload != "skinny" else "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": w["name"], "sample": best["sample"]},
         "cpu_baseline": {k: best[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": best["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -365,6 +594,83 @@ def run_reference_arm(args) -> None:
 
 
 # ----------------------------------------------------------------------------
+def measure_workload(torch, wc, sh, workload, rank, world, strong, steps, warmup, e2e_steps, stream, dist, sampler,
+                     pk, pk_kind, want_gather, want_cpu, want_sustained, counters) -> dict:
+    """Everything reported for one workload: device-timed rate, roofline, the
+    separately timed all-gather with parity of the gathered output, the
+    end-to-end rate through the host-buffer calls, the CPU baseline and the
+    sustained leg."""
+    from oracle import oracle
+    work = make_work(torch, wc, sh, workload, rank, world, strong)
+    sharded = work.strong and world > 1
+    ms = time_steps(torch, work, steps, warmup, stream, dist) / steps
+    clocks = sampler.window(work.t_begin, work.t_end) if sampler is not None else None
+    wc.check_device_status()
+    counters["launches"] += (steps + warmup) * work.launches_per_step
+    res = {"workload": WORKLOADS[workload]["name"], "ms_per_step": ms, "tflops": work.flops / (ms * 1e-3) / 1e12,
+           "scaling": "strong" if work.strong else "weak"}
+    if workload.startswith("fa"):
+        res["tflops_full_square_formula"] = work.flops_full_square / (ms * 1e-3) / 1e12
+        if "published_tflops" in WORKLOADS[workload]:  # one GPU's rate against the reference's one-GPU number
+            res["reference_published_tflops_gfx950"] = WORKLOADS[workload]["published_tflops"]
+            res["vs_published_per_gpu"] = work.flops_rank / (ms * 1e-3) / 1e12 / WORKLOADS[workload]["published_tflops"]
+    if workload == "skinny":
+        res["gbs_per_gpu"] = work.alg_bytes / (ms * 1e-3) / 1e9
+    if rank == 0:
+        res["roofline"] = roofline_for(workload, work, ms, clocks, pk, pk_kind)
+        res["clocks"] = clocks
+
+    # parity of the device-resident result (this rank), then of the gathered output (all ranks)
+    work.step(stream.cuda_stream)
+    torch.cuda.synchronize()
+    counters["launches"] += 1
+    gathered = None
+    if sharded and want_gather:
+        res["gather"], gathered = time_gather(torch, sh, work, dist, stream, world)
+        res["ms_per_step_with_gather"] = ms + res["gather"]["ms"]
+        res["tflops_with_gather"] = work.flops / ((ms + res["gather"]["ms"]) * 1e-3) / 1e12
+    else:
+        res["gather"] = None
+    if rank == 0:
+        oracle.build()
+        res["parity"] = work.check(oracle, gathered)
+    del gathered
+
+    # end to end: host buffers in, host buffers out
+    work.prepare_host()
+    e2e_ms = time_steps(torch, work, e2e_steps, 3, stream, dist, host=True) / e2e_steps
+    wc.check_device_status()
+    counters["launches"] += (e2e_steps + 3) * work.launches_per_step
+    mismatched = work.check_host(oracle)
+    res["e2e"] = {"value": work.flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": work.h2d,
+                  "d2h_bytes_per_step": work.d2h, "ms_per_step": e2e_ms,
+                  "h2d_gbs_per_rank": work.h2d / (e2e_ms * 1e-3) / 1e9, "d2h_gbs_per_rank": work.d2h / (e2e_ms * 1e-3) / 1e9,
+                  "host_link_gbs_all_ranks": (work.h2d + work.d2h) * world / (e2e_ms * 1e-3) / 1e9,
+                  "elements_differing_from_device_run": mismatched,
+                  "path": ("each rank copies M/N rows of A and its B block from pinned host memory, the ranks "
+                           "all-gather A over NVLink, wave_cuda_gemm_host_a_resident computes and returns the C block"
+                           if sharded and work.kind == "gemm" else
+                           "wave_cuda_gemm_host" if work.kind == "gemm" else "wave_cuda_flash_attention_fwd_host")
+                          + "; copies inside the timed region"}
+    work.host = None
+
+    if want_sustained:
+        res["sustained"] = sustained_leg(torch, work, stream, sampler if rank == 0 else None, want_sustained, pk)
+        counters["launches"] += res["sustained"]["launches"] + 13
+    if workload == "gemm" and want_sustained and not work.skinny:
+        res["vs_cublas"] = cublas_comparison(torch, work, stream)
+        counters["launches"] += res["vs_cublas"]["launches"]
+    if want_cpu and rank == 0:
+        cpu = cpu_baseline(workload)
+        res["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    res["plan"] = wc.gemm_plan(work.desc) if work.kind == "gemm" else {
+        "work_item_rows": 128 if (WORKLOADS[workload]["S"] >= 6144 or WORKLOADS[workload].get("qk_max_abs")) else 256,
+        "heads_per_gpu": work.hl}
+    del work
+    torch.cuda.empty_cache()
+    return res
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -372,9 +678,13 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", choices=["fa", "fa_published", "gemm", "skinny"], default="gemm")
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--gather", action="store_true", help="also time the NCCL all-gather of the output shards")
+    ap.add_argument("--scaling", choices=["strong", "weak"], default="strong",
+                    help="strong: one fixed problem split over the GPUs (default); weak: the whole problem on every GPU")
+    ap.add_argument("--no-gather", action="store_true", help="skip the NCCL all-gather of the output shards")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-also", action="store_true")
+    ap.add_argument("--no-sustained", action="store_true")
+    ap.add_argument("--sustained-seconds", type=float, default=2.0)
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--shape", default=None,
                     help="override the workload's size for profiling smaller cases: M,N,K (gemm, skinny) or B,H,S (fa)")
@@ -388,6 +698,7 @@ def main() -> None:
         keys = ("B", "H", "S") if args.workload.startswith("fa") else ("M", "N", "K")
         w.update(dict(zip(keys, dims)))
         w["name"] += "_shape_override_" + "x".join(str(d) for d in dims)
+        NCU_TRAFFIC_BYTES[args.workload] = None
 
     if args.impl == "reference":
         run_reference_arm(args)
@@ -404,123 +715,55 @@ def main() -> None:
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    wc = importlib.import_module("7_b200").wave_cuda
+    pkg = importlib.import_module("7_b200")
+    wc, sh = pkg.wave_cuda, importlib.import_module("7_b200.sharding")
     wc.lib()
     pk, pk_kind = peaks()
     stream = torch.cuda.current_stream()
+    strong = args.scaling == "strong"
 
-    work = make_work(torch, wc, args.workload, rank, world)
-    sampler = ClockSampler(local_rank)
+    sampler = None
     if rank == 0:
+        sampler = ClockSampler(local_rank)
         sampler.start()
         time.sleep(0.5)  # let nvidia-smi come up so that samples fall inside the timed region
-    ms = time_steps(torch, work, args.steps, args.warmup, stream, dist)
-    clocks = sampler.stop(work.t_begin, work.t_end) if rank == 0 else None
-    wc.check_device_status()
-    ms_per_step = ms / args.steps
-    value = work.flops * world / (ms_per_step * 1e-3) / 1e12
-
-    gather = None
-    if args.gather and world > 1:
-        from importlib import import_module
-        sh = import_module("7_b200.sharding")
-        local = work.c if not args.workload.startswith("fa") else work.o
-        for _ in range(3):
-            sh.all_gather_shards(local, dist)
-        torch.cuda.synchronize()
-        dist.barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for _ in range(10):
-            sh.all_gather_shards(local, dist)
-        e1.record(stream)
-        torch.cuda.synchronize()
-        t = torch.tensor([e0.elapsed_time(e1) / 10], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        gather = {"ms": float(t.item()), "bytes_per_rank": local.numel() * local.element_size()}
-
-    # end-to-end: host buffers in, host buffers out, through the C-ABI host call
-    work.prepare_host()
-    e2e_ms = time_steps(torch, work, args.e2e_steps, 3, stream, dist, host=True) / args.e2e_steps
-    wc.check_device_status()
-    e2e_value = work.flops * world / (e2e_ms * 1e-3) / 1e12
-    launches = (args.steps + args.warmup) * work.launches_per_step + (args.e2e_steps + 3) * work.launches_per_step
-
-    parity = None
+    counters = {"launches": 0}
+    sustained = 0.0 if args.no_sustained else args.sustained_seconds
+    main_res = measure_workload(torch, wc, sh, args.workload, rank, world, strong, args.steps, args.warmup,
+                                args.e2e_steps, stream, dist, sampler, pk, pk_kind, not args.no_gather,
+                                not args.no_cpu_baseline, sustained, counters)
     also = {}
-    cpu = None
-    if rank == 0:
-        from oracle import oracle
-        oracle.build()
-        work.step(stream.cuda_stream)
-        torch.cuda.synchronize()
-        parity = work.check(oracle)
     if not args.no_also and args.workload == "gemm":
-        del work.host
         for other in ("fa", "fa_published", "skinny"):
-            w2 = make_work(torch, wc, other, rank, world)
             steps2 = 10 if other.startswith("fa") else 50
-            ms2 = time_steps(torch, w2, steps2, 3, stream, dist) / steps2
-            wc.check_device_status()
-            launches += (steps2 + 3) * w2.launches_per_step
-            entry = {"workload": WORKLOADS[other]["name"], "ms_per_step": ms2,
-                     "tflops": w2.flops * world / (ms2 * 1e-3) / 1e12}
-            if other.startswith("fa"):
-                entry["tflops_full_square_formula"] = w2.flops_full_square * world / (ms2 * 1e-3) / 1e12
-                entry["frac_of_peak"] = entry["tflops"] / world / pk["bf16_tflops"]
-                if "published_tflops" in WORKLOADS[other]:  # one GPU's rate against the reference's one-GPU number
-                    entry["reference_published_tflops_gfx950"] = WORKLOADS[other]["published_tflops"]
-                    entry["vs_published"] = entry["tflops"] / world / WORKLOADS[other]["published_tflops"]
-            else:
-                entry["gbs"] = w2.alg_bytes / (ms2 * 1e-3) / 1e9
-                entry["frac_of_hbm_peak"] = entry["gbs"] / pk["hbm_gbs"]
-            if rank == 0:
-                from oracle import oracle
-                w2.step(stream.cuda_stream)
-                torch.cuda.synchronize()
-                entry["parity_worst_over_tolerance"] = w2.check(oracle)
-            also[other] = entry
-            del w2
-            torch.cuda.empty_cache()
-    if rank == 0 and not args.no_cpu_baseline:
-        cpu = cpu_baseline(args.workload)
-        cpu = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+            also[other] = measure_workload(torch, wc, sh, other, rank, world, strong, steps2, 3,
+                                           3 if other != "skinny" else 5, stream, dist, sampler, pk, pk_kind,
+                                           not args.no_gather, (not args.no_cpu_baseline) and other == "fa",
+                                           sustained if other == "fa" else 0.0, counters)
+    if sampler is not None:
+        sampler.stop()
 
     if rank == 0:
-        # Under a long back-to-back loop the part runs into its power cap and
-        # the SM clock drops; the matching denominator is then the sustained
-        # cuBLAS figure, otherwise the burst one.
-        capped = bool(clocks and clocks.get("sm_mhz") and "sw_power_cap" in clocks.get("reasons", [])
-                      and clocks["sm_mhz"] < 0.85 * clocks["sm_max_mhz"])
-        timed_alone = not capped
-        if args.workload == "skinny":
-            roof = {"bound": "hbm", "achieved": work.alg_bytes / (ms_per_step * 1e-3) / 1e9, "peak": pk["hbm_gbs"],
-                    "unit": "GB/s"}
-        else:
-            peak = pk["bf16_tflops"] if timed_alone else pk["bf16_tflops_sustained"]
-            roof = {"bound": "tensor", "achieved": work.flops / (ms_per_step * 1e-3) / 1e12, "peak": peak,
-                    "unit": "TFLOP/s", "peak_kind": ("burst" if timed_alone else "sustained, power-capped clocks")
-                    + f" ({pk_kind})", "frac_of_burst_peak": work.flops / (ms_per_step * 1e-3) / 1e12 / pk["bf16_tflops"],
-                    "frac_of_nominal_2250": work.flops / (ms_per_step * 1e-3) / 1e12 / 2250.0}
-        roof["frac"] = roof["achieved"] / roof["peak"]
-        roof["traffic"] = NCU_TRAFFIC_BYTES.get(args.workload)
-        roof["kernel_ms"] = ms_per_step
         w = WORKLOADS[args.workload]
+        is_strong = main_res["scaling"] == "strong"
+        per = {k: v for k, v in w.items() if k != "name"}
         line = {
-            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": w["name"], "per_gpu": {k: v for k, v in w.items() if k != "name"},
-                       "sharding": ("N-column blocks, one 8192-column block per GPU" if not args.workload.startswith("fa")
-                                    else "batch x head slabs, 512 heads per GPU") if world > 1 else "single GPU",
-                       "l2": "inputs and output larger than L2 (no flush needed)",
-                       "accumulate": "f32", "plan": wc.gemm_plan(work.desc) if not args.workload.startswith("fa") else
-                       {"tile_m": 256, "tile_n": 128, "grid": [w["S"] // 256, w["B"] * w["H"]]}},
-            "roofline": roof,
-            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": work.h2d,
-                    "d2h_bytes_per_step": work.d2h, "ms_per_step": e2e_ms},
-            "cpu_baseline": cpu, "gpu_launches": launches, "clocks": clocks,
-            "parity_worst_over_tolerance": parity, "also": also or None, "gather": gather,
+            "metric": METRIC, "value": main_res["tflops"], "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": main_res["ms_per_step"], "higher_is_better": True,
+            "scaling": main_res["scaling"], "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": w["name"], "problem": per,
+                       "sharding": ("single GPU" if world == 1 else
+                                    ("one problem: " if is_strong else "one problem per GPU: ") +
+                                    ("N-column blocks of B and C (A replicated), column-major C blocks"
+                                     if not args.workload.startswith("fa") else "contiguous (batch x head) slabs of Q, K, V, O")),
+                       "l2": "inputs and output larger than L2 (no flush needed)" if world == 1 or not is_strong else
+                             "replicated operand larger than L2 (no flush needed)",
+                       "accumulate": "f32", "plan": main_res.pop("plan")},
+            "roofline": main_res.get("roofline"), "e2e": main_res["e2e"], "cpu_baseline": main_res.get("cpu_baseline"),
+            "gpu_launches": counters["launches"], "clocks": main_res.get("clocks"),
+            "parity_worst_over_tolerance": main_res["parity"]["worst_over_tolerance"], "parity": main_res["parity"],
+            "gather": main_res.get("gather"), "value_with_gather": main_res.get("tflops_with_gather"),
+            "sustained": main_res.get("sustained"), "vs_cublas": main_res.get("vs_cublas"), "also": also or None,
         }
         print(json.dumps(line), flush=True)
     if dist is not None:

@@ -55,6 +55,13 @@ extern "C" {
 const char *wave_cuda_last_error(void);
 const char *wave_cuda_version(void);
 
+/* The WAVE_CUDA_* environment variables named below are measurement knobs.
+ * The library reads them once, at the first call that needs one; a process
+ * that changes its environment afterwards calls this to have them read again.
+ * (The reference's tools take the corresponding choices as command-line
+ * flags, wave-matmul-calibrate.py:1170; there is no reference function.) */
+void wave_cuda_reload_env(void);
+
 /* ---- mlir-runner host ABI ---------------------------------------------- *
  * Same seven symbols as runtime/wave_runtime.cpp:46-74: a rank-1 strided
  * memref descriptor {base, data, offset, size, stride} -> data + offset, the
@@ -79,9 +86,15 @@ void *_mlir_ciface_wave_memref_to_ptr_global_f64(void *memref1d);
  *   (rows 128; columns the next of 16/32/64/128/256).
  * Requested tiles of at least 256 x 256 run on CTA pairs (tcgen05
  * cta_group::2, 256 x 256 tiles) where those fill the machine at least as well
- * as 128 x 256 tiles on single CTAs; the environment variables
- * WAVE_CUDA_GEMM_KERNEL=pair|pair128|single, WAVE_CUDA_GEMM_SPLIT_TAIL=0 and
- * WAVE_CUDA_GEMM_TMA_STORE=0 override the choices (knobs for measurements;
+ * as 128 x 256 tiles on single CTAs.  A last round of tiles that would leave
+ * CTA pairs idle runs as half-width items or, with streamk_workers = 0 and a
+ * workspace, has its K iterations dealt over all pairs (Stream-K tail).
+ * Column-major 16-bit C is computed as the row-major C^T = B * A^T (operands
+ * swapped inside the library; bit-identical results).  The environment
+ * variables WAVE_CUDA_GEMM_KERNEL=pair|pair128|single,
+ * WAVE_CUDA_GEMM_SPLIT_TAIL=0, WAVE_CUDA_GEMM_STREAMK_TAIL=0,
+ * WAVE_CUDA_GEMM_TMA_STORE=0, WAVE_CUDA_GEMM_COL_SWAP=0 and
+ * WAVE_CUDA_GEMM_L2_HINTS=0|1|2 override the choices (knobs for measurements;
  * results do not change).                                                    */
 typedef struct wave_gemm_desc {
   int M, N, K;                 /* positive multiples of 16 (wave_matmul.py:533-536)      */
@@ -128,6 +141,16 @@ int wave_cuda_gemm(const wave_gemm_desc *desc, const void *A, const void *B, voi
 int wave_cuda_gemm_host(const wave_gemm_desc *desc, const void *A_host, const void *B_host, void *C_host,
                         void *stream);
 
+/* The same call for one rank of an N-column-sharded GEMM: B and C are the
+ * rank's column block in host memory, A (replicated on every rank) is already
+ * on the device, 16-byte aligned and ready on `stream` -- e.g. gathered over
+ * NVLink from the M/ranks rows each rank copied from its host, instead of
+ * every rank copying the whole of A over PCIe.  (The reference is
+ * single-device; its host main registers A, B and C alike,
+ * wave_matmul.py:6926-6937.) */
+int wave_cuda_gemm_host_a_resident(const wave_gemm_desc *desc, const void *A_device, const void *B_host,
+                                   void *C_host, void *stream);
+
 /* No counterpart in the reference.  Stream-K GEMM for callers that cannot
  * supply (or allocate) the workspace wave_cuda_gemm asks for: hosts written to
  * the reference's plain {A, B, C, trip} argument list, which has no workspace
@@ -136,7 +159,9 @@ int wave_cuda_gemm_host(const wave_gemm_desc *desc, const void *A_host, const vo
  * counters live in one fixed WAVE_CUDA_STATIC_WORKSPACE_BYTES area inside the
  * library's device image (held by every GPU that loads the library until the
  * process exits); nothing is allocated or freed.  A descriptor that needs more
- * than the area holds is refused with WAVE_E_INVALID.  The first call on a
+ * than the area holds is refused with WAVE_E_INVALID when it names a worker
+ * count; with streamk_workers = 0 (automatic) a plan that does not fit runs as
+ * whole tiles instead, without a workspace.  The first call on a
  * device looks the area's address up and should be made before any stream
  * capture.  Every call shares the area: calls whose kernels overlap on the GPU
  * race and must be serialised by the caller.  Same arguments and results as
@@ -167,6 +192,13 @@ int wave_cuda_gemm_plan(const wave_gemm_desc *desc, int *tile_m, int *tile_n, in
  * polynomial on the FMA pipe, WAVE_CUDA_FA_STAGGER=<cycles> the one-off offset
  * between the streaming kernel's two softmax warpgroups in fixed-reference mode
  * (measurement knobs; the results agree within the rounding of the exponential).
+ * Launches in flight: each launch draws its work items from one of 64 device
+ * counters per GPU, handed out in turn.  The launch that comes round to a
+ * counter is ordered (by an event) behind the launch that used it 64 launches
+ * earlier, so any number of launches may be queued on any number of streams;
+ * at most 64 of them run side by side.  Under stream capture that ordering is
+ * left out: two captured graphs that hold the same counter (captured 64
+ * launches apart) must not be replayed at the same time.
  */
 typedef struct wave_fa_desc {
   int batch, heads;

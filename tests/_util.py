@@ -2,7 +2,29 @@
 (plumbing only); every compute call goes through the C ABI."""
 from __future__ import annotations
 
+import contextlib
+import os
+
 import numpy as np
+
+
+@contextlib.contextmanager
+def env_knobs(wc, **knobs):
+    """Sets WAVE_CUDA_* measurement knobs for the enclosed calls.  The library
+    reads its environment once, so it is told to read it again on the way in
+    and on the way out."""
+    old = {k: os.environ.get(k) for k in knobs}
+    os.environ.update({k: str(v) for k, v in knobs.items()})
+    wc.reload_env()
+    try:
+        yield
+    finally:
+        for k, v in old.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v
+        wc.reload_env()
 
 
 def to_device_bits(torch, bits: np.ndarray):

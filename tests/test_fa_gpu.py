@@ -13,19 +13,18 @@ import os
 import numpy as np
 import pytest
 
-from _util import to_device_bits
+from _util import env_knobs, to_device_bits
 
 pytestmark = pytest.mark.gpu
 
 
 @pytest.fixture(params=["pingpong", "stream"], autouse=True)
-def fa_kernel(request):
+def fa_kernel(request, wc):
     """Every test runs on both attention kernels (two Q tiles ping-ponging; one
     Q tile with double-buffered scores).  Left alone, the library picks one by
     the key sequence length."""
-    os.environ["WAVE_CUDA_FA_KERNEL"] = request.param
-    yield request.param
-    del os.environ["WAVE_CUDA_FA_KERNEL"]
+    with env_knobs(wc, WAVE_CUDA_FA_KERNEL=request.param):
+        yield request.param
 
 REFERENCE_MAX_ABS = 3.0e-2  # wave-fa-gfx950-runner.cpp:388
 
@@ -274,6 +273,32 @@ def test_launches_overlapping_on_two_streams(cuda, wc, oracle):
     wc.check_device_status()
     for o in outs:
         assert np.array_equal(o.float().cpu().numpy(), want)
+
+
+def test_more_queued_launches_than_ticket_counters(cuda, wc, oracle):
+    """The work-item counters are a ring of 64 per GPU.  With more launches
+    queued than that (70 per stream on 4 streams, each launch with an output of
+    its own), the launch that comes round to a counter is ordered behind the one
+    that used it before, so no launch may lose or repeat work items: every one
+    of the 280 outputs must be the single-stream result."""
+    t = oracle.BF16
+    BH, S = 4, 512
+    q, k, v = normal_qkv(oracle, BH, S, S, 128, t, seed=43)
+    want = run_fa(cuda, wc, q, k, v, "bf16", 1, 4, True)
+    desc = wc.fa_desc(1, 4, S, S, 128, causal=True, io_type=wc.TYPE_BY_NAME["bf16"])
+    dq, dk, dv = (to_device_bits(cuda, x) for x in (q, k, v))
+    streams = [cuda.cuda.Stream() for _ in range(4)]
+    per_stream = 70
+    outs = cuda.full((len(streams), per_stream, BH, S, 128), float("nan"), dtype=cuda.bfloat16, device="cuda")
+    cuda.cuda.synchronize()
+    for i in range(per_stream):
+        for s_idx, st in enumerate(streams):
+            wc.flash_attention_fwd(desc, dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), outs[s_idx, i].data_ptr(), 0,
+                                   st.cuda_stream)
+    cuda.cuda.synchronize()
+    wc.check_device_status()
+    got = outs.float().cpu().numpy()
+    assert np.array_equal(got, np.broadcast_to(want, got.shape))
 
 
 def _operator_case(cuda, oracle, q_bits, k_bits, v_bits, **kwargs):

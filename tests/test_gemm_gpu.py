@@ -11,7 +11,7 @@ import os
 import numpy as np
 import pytest
 
-from _util import device_out, out_to_f32, runner_tolerance_ok, to_device_bits
+from _util import device_out, env_knobs, out_to_f32, runner_tolerance_ok, to_device_bits
 
 pytestmark = pytest.mark.gpu
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
@@ -20,11 +20,8 @@ GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
 def run_gemm(torch, wc, a_bits, b_bits, in_name, out_name, layout="row-major", streamk=1, ldc=0, kernel="pair",
              **knobs):
     # small shapes must still exercise the CTA-pair kernel when their knobs ask for 256 x 256 tiles
-    os.environ["WAVE_CUDA_GEMM_KERNEL"] = kernel
-    try:
+    with env_knobs(wc, WAVE_CUDA_GEMM_KERNEL=kernel):
         return _run_gemm(torch, wc, a_bits, b_bits, in_name, out_name, layout, streamk, ldc, **knobs)
-    finally:
-        del os.environ["WAVE_CUDA_GEMM_KERNEL"]
 
 
 def _run_gemm(torch, wc, a_bits, b_bits, in_name, out_name, layout="row-major", streamk=1, ldc=0, **knobs):
@@ -159,6 +156,81 @@ def test_streamk_matches_oracle_and_resets_counters(cuda, wc, oracle, M, N, K, w
     assert ok, f"{nbad} elements out of tolerance, worst {worst}"
 
 
+PAIR_KNOBS = dict(bm=4, bn=4, wave_m_tiles=4, wave_n_tiles=4)
+
+
+@pytest.mark.parametrize("M,N,K,out_name,layout,knobs", [
+    (2560, 2560, 1024, "bf16", "row-major", PAIR_KNOBS),     # 100 tiles on 74 CTA pairs: 74 whole, 26 split over all pairs
+    (2560, 2560, 1024, "f32", "row-major", PAIR_KNOBS),
+    (768, 1024, 512, "bf16", "row-major", PAIR_KNOBS),       # 12 tiles, less than one round: every tile split
+    (2560, 2560, 640, "bf16", "column-major", PAIR_KNOBS),   # computed as C^T, Stream-K tail on the swapped problem
+    (2576, 2448, 576, "f16", "row-major", dict(bm=1, bn=1, wave_m_tiles=23, wave_n_tiles=17)),  # ragged edges on split tiles
+    (8192, 1024, 1024, "bf16", "row-major", PAIR_KNOBS),     # an eighth of the 8192-column problem: 128 tiles, 54 in the tail
+])
+def test_pair_kernel_streamk_tail(cuda, wc, oracle, M, N, K, out_name, layout, knobs):
+    """With streamk_workers = 0 and a workspace, the CTA-pair kernel deals the K
+    iterations of a partly filled last round of tiles over all pairs.  LCG
+    inputs: the oracle's bits whatever the grouping of the sum; the arrival
+    counters are zero afterwards; two runs on random inputs are bit-identical
+    (fixed reduction order); and the same with the tail treatment switched off."""
+    in_name = "f16" if out_name == "f16" else "bf16"
+    with env_knobs(wc, WAVE_CUDA_GEMM_KERNEL="pair"):
+        desc = wc.gemm_desc(M, N, K, in_type=wc.TYPE_BY_NAME[in_name], out_type=wc.TYPE_BY_NAME[out_name],
+                            out_layout=wc.LAYOUT_BY_NAME[layout], streamk_workers=0, **knobs)
+        plan = wc.gemm_plan(desc)
+        assert (plan["tile_m"], plan["tile_n"]) == (256, 256) and plan["streamk_workers"] == plan["grid"] // 2 > 1, plan
+    a, b = lcg_inputs(oracle, M, N, K, in_name, seed=M + 7)
+    got, counters = run_gemm(cuda, wc, a, b, in_name, out_name, layout, streamk=0, **knobs)
+    want = expected(oracle, a, b, in_name, out_name)
+    assert np.array_equal(got, want), f"max abs diff {np.nanmax(np.abs(got - want))}"
+    assert counters is not None and counters.size > 0 and not counters.any()
+    t = oracle.F16 if in_name == "f16" else oracle.BF16
+    a = oracle.baseline_inputs((M, K), "normal", 9, 0, t)
+    b = oracle.baseline_inputs((N, K), "normal", 9, 1, t, scale=K ** -0.5)
+    r1, _ = run_gemm(cuda, wc, a, b, in_name, out_name, layout, streamk=0, **knobs)
+    r2, _ = run_gemm(cuda, wc, a, b, in_name, out_name, layout, streamk=0, **knobs)
+    assert np.array_equal(r1, r2)
+    ok, worst, nbad = runner_tolerance_ok(r1, expected(oracle, a, b, in_name, out_name), out_name)
+    assert ok, f"{nbad} elements out of tolerance, worst {worst}"
+    with env_knobs(wc, WAVE_CUDA_GEMM_STREAMK_TAIL="0"):
+        whole, _ = run_gemm(cuda, wc, a, b, in_name, out_name, layout, streamk=0, **knobs)
+    ok, worst, nbad = runner_tolerance_ok(r1, whole, out_name)
+    assert ok, f"tail on/off differ beyond rounding: {nbad} elements, worst {worst}"
+
+
+@pytest.mark.parametrize("kernel", ["pair", "single"])
+@pytest.mark.parametrize("M,N,K,out_name,ldc,knobs", [
+    (512, 768, 256, "bf16", 0, PAIR_KNOBS),
+    (1024, 256, 320, "f16", 0, PAIR_KNOBS),
+    (400, 272, 208, "f16", 0, dict(bm=1, bn=1, wave_m_tiles=25, wave_n_tiles=17)),   # ragged in both directions
+    (1024, 512, 128, "bf16", 1536, PAIR_KNOBS),                                       # a column shard of a wider C
+    (256, 2048, 192, "bf16", 0, dict(bm=4, bn=4, wave_m_tiles=2, wave_n_tiles=4)),
+])
+def test_column_major_16bit_runs_as_transposed_row_major(cuda, wc, oracle, M, N, K, out_name, ldc, knobs, kernel):
+    """Column-major 16-bit C is computed as C^T = B * A^T so that it leaves
+    through the TMA-store epilogue; the bits must be the oracle's, the same as
+    without the operand swap, and a shard written with ldc must leave the rest
+    of the wider C untouched."""
+    in_name = "f16" if out_name == "f16" else "bf16"
+    a, b = lcg_inputs(oracle, M, N, K, in_name, seed=M + N)
+    want = expected(oracle, a, b, in_name, out_name)
+    got, _ = run_gemm(cuda, wc, a, b, in_name, out_name, "column-major", ldc=ldc, kernel=kernel, **knobs)
+    assert np.array_equal(got, want), f"max abs diff {np.nanmax(np.abs(got - want))}"
+    with env_knobs(wc, WAVE_CUDA_GEMM_COL_SWAP="0"):
+        plain, _ = run_gemm(cuda, wc, a, b, in_name, out_name, "column-major", ldc=ldc, kernel=kernel, **knobs)
+    assert np.array_equal(plain, want)
+    if ldc:
+        desc = wc.gemm_desc(M, N, K, in_type=wc.TYPE_BY_NAME[in_name], out_type=wc.TYPE_BY_NAME[out_name],
+                            out_layout=wc.COL_MAJOR, ldc=ldc, **knobs)
+        da, db = to_device_bits(cuda, a), to_device_bits(cuda, b)
+        c = device_out(cuda, ldc * N, out_name)
+        with env_knobs(wc, WAVE_CUDA_GEMM_KERNEL=kernel):
+            wc.gemm(desc, da.data_ptr(), db.data_ptr(), c.data_ptr(), 0, cuda.cuda.current_stream().cuda_stream)
+        wc.check_device_status()
+        full = out_to_f32(cuda, c).reshape(N, ldc)
+        assert np.array_equal(full[:, :M].T, want) and np.isnan(full[:, M:]).all()
+
+
 @pytest.mark.parametrize("layout", ["tile-packed-mfma64", "tile-packed-wmma32", "tile-packed-mfma32"])
 @pytest.mark.parametrize("M,N,K,out_name,streamk,knobs", [
     (64, 96, 32, "f32", 1, dict(bm=2, bn=2, wave_m_tiles=2, wave_n_tiles=3)),
@@ -176,12 +248,9 @@ def test_tile_packed_fragment_layouts(cuda, wc, oracle, layout, M, N, K, out_nam
     c = device_out(cuda, M * N, out_name)
     scratch, counters = wc.gemm_workspace_bytes(desc)
     ws = cuda.zeros(scratch + counters, dtype=cuda.uint8, device="cuda") if scratch + counters else None
-    os.environ["WAVE_CUDA_GEMM_KERNEL"] = "pair"
-    try:
+    with env_knobs(wc, WAVE_CUDA_GEMM_KERNEL="pair"):
         wc.gemm(desc, a.data_ptr(), b.data_ptr(), c.data_ptr(), ws.data_ptr() if ws is not None else 0,
                 cuda.cuda.current_stream().cuda_stream)
-    finally:
-        del os.environ["WAVE_CUDA_GEMM_KERNEL"]
     wc.check_device_status()
     got = out_to_f32(cuda, c)
     want = oracle.layout_output(expected(oracle, a_bits, b_bits, "f16", out_name), layout, knobs.get("bm", 1),
@@ -234,11 +303,8 @@ def test_pair_kernel_split_tail(cuda, wc, oracle, M, N, K, layout, split):
     a, b = lcg_inputs(oracle, M, N, K, "bf16", seed=M + K)
     knobs = dict(bm=4, bn=4, wave_m_tiles=4, wave_n_tiles=4) if M % 256 == 0 and N % 256 == 0 else \
         dict(bm=1, bn=1, wave_m_tiles=23 if M == 2576 else 16, wave_n_tiles=17 if N == 2448 else 16)
-    os.environ["WAVE_CUDA_GEMM_SPLIT_TAIL"] = split
-    try:
+    with env_knobs(wc, WAVE_CUDA_GEMM_SPLIT_TAIL=split):
         got, _ = run_gemm(cuda, wc, a, b, "bf16", "f32", layout, **knobs)
-    finally:
-        del os.environ["WAVE_CUDA_GEMM_SPLIT_TAIL"]
     want = expected(oracle, a, b, "bf16", "f32")
     assert np.array_equal(got, want), f"max abs diff {np.nanmax(np.abs(got - want))}"
 
@@ -270,12 +336,9 @@ def test_tile_packed_output(cuda, wc, oracle, M, N, K, out_name, streamk, knobs)
     c = device_out(cuda, M * N, out_name)
     scratch, counters = wc.gemm_workspace_bytes(desc)
     ws = cuda.zeros(scratch + counters, dtype=cuda.uint8, device="cuda") if scratch + counters else None
-    os.environ["WAVE_CUDA_GEMM_KERNEL"] = "pair"
-    try:
+    with env_knobs(wc, WAVE_CUDA_GEMM_KERNEL="pair"):
         wc.gemm(desc, a.data_ptr(), b.data_ptr(), c.data_ptr(), ws.data_ptr() if ws is not None else 0,
                 cuda.cuda.current_stream().cuda_stream)
-    finally:
-        del os.environ["WAVE_CUDA_GEMM_KERNEL"]
     wc.check_device_status()
     want = oracle.layout_output(expected(oracle, a_bits, b_bits, "f16", out_name), "tile-packed", knobs.get("bm", 1),
                                 knobs.get("bn", 2), knobs.get("wave_m_tiles", 1), knobs.get("wave_n_tiles", 1))
@@ -315,6 +378,28 @@ def test_host_buffer_call_pipelined(cuda, wc, oracle, layout, out_name):
     got = c if out_name == "f32" else oracle.from_bits(c, oracle.BF16)
     got = got.reshape(M, N) if layout == "row-major" else got.reshape(N, M).T
     assert np.array_equal(got, expected(oracle, a, b, "bf16", out_name))
+
+
+@pytest.mark.parametrize("M,N,K", [(512, 768, 256), (2048, 8192, 4096)])
+def test_host_buffer_call_with_device_resident_a(cuda, wc, oracle, pkg, M, N, K):
+    """One rank's part of an N-column-sharded GEMM whose operands live in host
+    memory: the replicated A is already on the device (on more than one GPU it
+    arrives by an all-gather of row blocks; one rank here), B and the
+    column-major bf16 C block travel through the host-buffer call, one-piece and
+    pipelined sizes."""
+    import importlib
+    sh = importlib.import_module("7_b200.sharding")
+    a, b = lcg_inputs(oracle, M, N, K, "bf16", seed=23)
+    a_host = cuda.from_numpy(a.view(np.int16)).pin_memory()
+    b_host = cuda.from_numpy(b.view(np.int16)).pin_memory()
+    c_host = cuda.zeros(N * M, dtype=cuda.int16).pin_memory()
+    a_dev = cuda.empty((M, K), dtype=cuda.int16, device="cuda")
+    desc = wc.gemm_desc(M, N, K, bm=4, bn=4, wave_m_tiles=4, wave_n_tiles=4, in_type=wc.BF16, out_type=wc.BF16,
+                        out_layout=wc.COL_MAJOR, streamk_workers=0)
+    sh.sharded_gemm_host(wc, desc, a_dev, a_host, b_host, c_host, None, 0, 1, cuda.cuda.current_stream().cuda_stream)
+    wc.check_device_status()
+    got = oracle.from_bits(c_host.numpy().view(np.uint16), oracle.BF16).reshape(N, M).T
+    assert np.array_equal(got, expected(oracle, a, b, "bf16", "bf16"))
 
 
 def test_name_based_launch_facade(cuda, wc, oracle):

@@ -37,7 +37,7 @@ def _worker(rank, world, port, tmpdir):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         # GEMM: A replicated, B split by rows (= C columns), column-major C blocks gathered
-        M, N, K = 48, 64, 96
+        M, N, K = 64, 64, 96
         a = oracle.make_input_bits(M, K, oracle.BF16, 3, 0, oracle.MODE_LCG)
         b = oracle.make_input_bits(N, K, oracle.BF16, 3, 1, oracle.MODE_LCG)
         n0, n1 = sh.column_shard(N, world, rank)
@@ -45,6 +45,12 @@ def _worker(rank, world, port, tmpdir):
         local = torch.from_numpy(np.ascontiguousarray(c_block.T))           # column-major block: [n1-n0, M]
         full_cm = sh.all_gather_shards(local, dist).reshape(N, M).numpy()   # n*M + m
         assert np.array_equal(full_cm.T, oracle.gemm_ref(a, b, oracle.BF16))
+        # the replicated A reaches every rank as row blocks exchanged by an all-gather
+        a_t = torch.from_numpy(a.view(np.int16))
+        r0, r1 = sh.row_shard(M, world, rank)
+        assert (r1 - r0) * world == M
+        a_rows = sh.all_gather_shards(a_t[r0:r1], dist).reshape(M, K)
+        assert torch.equal(a_rows, a_t)
         # attention: (batch*head) slabs
         BH, S, D = 4, 32, 128
         q, k, v = (oracle.baseline_inputs((BH, S, D), "normal", 7, i, oracle.BF16) for i in range(3))

@@ -72,3 +72,74 @@ def test_static_workspace_refuses_oversized_launch(cuda, wc):
         wc.gemm_streamk_static(desc, x.data_ptr(), x.data_ptr(), c.data_ptr())
     assert err.value.code == wc.E_INVALID
     assert "built-in workspace holds" in err.value.message
+
+
+CASES = [
+    (16, 4096, 4096, 148, dict(bn=1)),
+    (256, 512, 2048, 7, dict(bm=4, bn=4, wave_m_tiles=2, wave_n_tiles=4)),
+]
+
+
+def test_static_workspace_allocates_nothing_and_survives_alternating_shapes(cuda, wc, oracle):
+    """The two properties the entry point exists for.  Free device memory, as
+    the driver reports it, does not move across the calls (after one warm-up
+    call per shape, which loads the kernels).  And two descriptors with
+    different scratch sizes, called alternately, still give the caller-workspace
+    bits: the counters sit behind the partial tiles, so their offset inside the
+    shared area moves from call to call and each call finds the other shape's
+    leftovers where its own counters belong."""
+    torch = cuda
+    stream = torch.cuda.current_stream().cuda_stream
+    prepared = []
+    for M, N, K, workers, knobs in CASES:
+        a_bits, b_bits = _inputs(oracle, M, N, K, seed=3 * M + workers)
+        a, b = to_device_bits(torch, a_bits), to_device_bits(torch, b_bits)
+        desc = wc.gemm_desc(M, N, K, in_type=wc.BF16, out_type=wc.F32, streamk_workers=workers, **knobs)
+        scratch, counters = wc.gemm_workspace_bytes(desc)
+        ws = torch.zeros(scratch + counters, dtype=torch.uint8, device="cuda")
+        c_ref = device_out(torch, M * N, "f32")
+        wc.gemm(desc, a.data_ptr(), b.data_ptr(), c_ref.data_ptr(), ws.data_ptr(), stream)
+        c = device_out(torch, M * N, "f32")
+        wc.gemm_streamk_static(desc, a.data_ptr(), b.data_ptr(), c.data_ptr(), stream)  # warm-up
+        prepared.append((desc, a, b, c, out_to_f32(torch, c_ref), scratch))
+    assert prepared[0][5] != prepared[1][5], "the two cases must place their counters at different offsets"
+    wc.check_device_status()
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        for desc, a, b, c, want, _ in prepared:
+            c.fill_(float("nan"))
+            wc.gemm_streamk_static(desc, a.data_ptr(), b.data_ptr(), c.data_ptr(), stream)
+            torch.cuda.synchronize()
+            assert np.array_equal(out_to_f32(torch, c), want)
+    free_after, _ = torch.cuda.mem_get_info()
+    wc.check_device_status()
+    assert free_after == free_before, f"device memory in use moved by {free_before - free_after} bytes"
+
+
+def test_static_workspace_automatic_plan_falls_back_to_whole_tiles(cuda, wc, oracle):
+    """streamk_workers = 0 leaves the choice to the library.  Where its
+    automatic Stream-K plan needs more than the built-in area holds, the call
+    runs as whole tiles (no workspace, nothing allocated) instead of being
+    refused, and returns the caller-workspace result."""
+    torch = cuda
+    stream = torch.cuda.current_stream().cuda_stream
+    # (skinny: the automatic plan splits K over every SM with 128 x 16 partial tiles and fits the area;
+    #  100 tiles of 128 x 256 on 148 SMs: the automatic plan wants 148 x 2 partial tiles, 38.8 MB, and does not)
+    for M2, N2, K2, knobs, fits in [(16, 28672, 1024, dict(bn=1), True),
+                                    (1280, 2560, 1024, dict(bm=4, bn=4, wave_m_tiles=2, wave_n_tiles=4), False)]:
+        a_bits, b_bits = _inputs(oracle, M2, N2, K2, seed=77 + M2)
+        a, b = to_device_bits(torch, a_bits), to_device_bits(torch, b_bits)
+        desc = wc.gemm_desc(M2, N2, K2, in_type=wc.BF16, out_type=wc.F32, streamk_workers=0, **knobs)
+        scratch, counters = wc.gemm_workspace_bytes(desc)
+        assert scratch > 0 and (scratch + counters <= wc.STATIC_WORKSPACE_BYTES) == fits
+        ws = torch.zeros(max(scratch + counters, 16), dtype=torch.uint8, device="cuda")
+        c_ref = device_out(torch, M2 * N2, "f32")
+        wc.gemm(desc, a.data_ptr(), b.data_ptr(), c_ref.data_ptr(), ws.data_ptr(), stream)
+        c = device_out(torch, M2 * N2, "f32")
+        wc.gemm_streamk_static(desc, a.data_ptr(), b.data_ptr(), c.data_ptr(), stream)
+        wc.check_device_status()
+        got, want = out_to_f32(torch, c), out_to_f32(torch, c_ref)
+        assert not np.isnan(got).any()
+        # whole tiles and Stream-K add the same products in a different grouping
+        assert np.all(np.abs(got - want) <= 1.0e-2 + 1.0e-3 * np.abs(want))
