@@ -10,9 +10,10 @@ namespace wave {
 struct EnvKnobs {
   int gemm_kernel = 0;           // WAVE_CUDA_GEMM_KERNEL: 0 auto, 1 single, 2 pair, 3 pair128
   bool gemm_split_tail = true;   // WAVE_CUDA_GEMM_SPLIT_TAIL=0: no half-width items in a sparse last round
-  bool gemm_streamk_tail = true; // WAVE_CUDA_GEMM_STREAMK_TAIL=0: no Stream-K treatment of the pair kernel's last round
+  int gemm_streamk_tail = 1;     // WAVE_CUDA_GEMM_STREAMK_TAIL: 0 never, 1 where the cost model says it pays, 2 whenever possible
+  int gemm_pair_tile_n = 0;      // WAVE_CUDA_GEMM_PAIR_TILE_N: width of the CTA-pair kernel's tiles (a multiple of 32 in (128, 256]), 0 = chosen
   bool gemm_tma_store = true;    // WAVE_CUDA_GEMM_TMA_STORE=0: per-thread stores instead of the TMA-store epilogue
-  int gemm_l2_hints = 1;         // WAVE_CUDA_GEMM_L2_HINTS: 0 none, 1 A evict-last + B evict-first, 2 A evict-last only
+  int gemm_l2_hints = 2;         // WAVE_CUDA_GEMM_L2_HINTS: 0 none, 1 A evict-last + B evict-first, 2 A evict-last only
   bool gemm_col_swap = true;     // WAVE_CUDA_GEMM_COL_SWAP=0: column-major 16-bit C without the operand swap
   int fa_kernel = 0;             // WAVE_CUDA_FA_KERNEL: 0 auto, 1 pingpong, 2 stream, 3 pair
   int fa_poly = -1;              // WAVE_CUDA_FA_POLY: eighths of the exponentials on the FMA pipe, -1 = each kernel's default

@@ -86,10 +86,12 @@ struct PairItem {
 template <int PN> struct PairWork {
   const GemmParams &p;
   int split_from, dp_items, num_pairs;
+  int tile_w; // columns of a whole tile: PN, or with PN = 256 any multiple of 32 the host chose (p.pair_tile_n)
   long long dp_cur, cur, end;
   __device__ PairWork(const GemmParams &params, int pair_id, int pairs) : p(params), num_pairs(pairs) {
     const bool sk = p.streamk_workers > 0;
-    split_from = (PN == 256 && !sk) ? p.split_from : p.num_tiles;
+    tile_w = PN == 256 ? p.pair_tile_n : PN;
+    split_from = (PN == 256 && !sk && tile_w == 256) ? p.split_from : p.num_tiles;
     dp_items = sk ? p.dp_tiles : split_from + 2 * (p.num_tiles - split_from);
     dp_cur = pair_id;
     cur = end = 0;
@@ -103,12 +105,12 @@ template <int PN> struct PairWork {
       dp_cur += num_pairs;
       it.tile = item;
       it.n_off = 0;
-      it.width = PN;
+      it.width = tile_w;
       if (item >= split_from) {
         const int r = item - split_from;
         it.tile = split_from + (r >> 1);
-        it.n_off = (r & 1) * (PN / 2);
-        it.width = PN / 2;
+        it.n_off = (r & 1) * (tile_w / 2);
+        it.width = tile_w / 2;
       }
       it.k_begin = 0;
       it.k_end = p.k_iters;
@@ -120,7 +122,7 @@ template <int PN> struct PairWork {
       const long long seg_end = min(end, tile_begin + p.k_iters);
       it.tile = static_cast<int>(tile) + p.dp_tiles;
       it.n_off = 0;
-      it.width = PN;
+      it.width = tile_w;
       it.k_begin = static_cast<int>(cur - tile_begin);
       it.k_end = static_cast<int>(seg_end - tile_begin);
       cur = seg_end;
@@ -190,8 +192,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       tma_prefetch_desc(&tmap_a);
       tma_prefetch_desc(&tmap_b);
       // A panels are shared by every tile of a row group and read again by its
-      // later rounds; a B panel is finished with once the round that holds its
-      // column block has read it.
+      // later rounds: "evict last".  B panels keep the default policy: marking
+      // them "evict first" (hint 1) lets a panel leave L2 before the slower CTAs
+      // of the round have read it (8192^3 bf16, one launch: DRAM reads 2046 MB
+      // against 1083 MB without hints and 1040 MB with the hint on A alone).
       const uint64_t pol_a = p.l2_hints ? l2_policy_evict_last() : l2_policy_evict_normal();
       const uint64_t pol_b = p.l2_hints == 1 ? l2_policy_evict_first() : l2_policy_evict_normal();
       int stage = 0;
@@ -200,9 +204,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       PairWork<PN> work(p, pair_id, num_pairs);
       PairItem it;
       while (ok && work.next(it)) {
-        const bool half = it.width != PN;
+        const bool half = it.width != work.tile_w;
         const int m0 = it.mb * kPairM + static_cast<int>(rank) * kRows;
-        const int n0 = it.nb * kPairN + it.n_off + static_cast<int>(rank) * (it.width / 2);
+        const int n0 = it.nb * work.tile_w + it.n_off + static_cast<int>(rank) * (it.width / 2);
         const uint32_t stage_tx = 2 * (kABytes + (it.width / 2) * kBK * 2);
         for (int kb = it.k_begin; kb < it.k_end; ++kb) {
           if (!mbar_wait(&sh->empty[stage], phase ^ 1, abort_flag)) {
@@ -228,8 +232,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   } else if (warp == 1) {
     // ------------------------------------------- UMMA issuer (leader only)
     if (lane == 0 && leader) {
-      const uint32_t idesc_whole = umma_idesc_f16(kPairM, kPairN, p.in_type == WAVE_GEMM_IN_BF16 ? 1 : 0);
-      const uint32_t idesc_half = umma_idesc_f16(kPairM, kPairN / 2, p.in_type == WAVE_GEMM_IN_BF16 ? 1 : 0);
+      const int tile_w = PN == 256 ? p.pair_tile_n : PN;
+      const uint32_t idesc_whole = umma_idesc_f16(kPairM, tile_w, p.in_type == WAVE_GEMM_IN_BF16 ? 1 : 0);
+      const uint32_t idesc_half = umma_idesc_f16(kPairM, tile_w / 2, p.in_type == WAVE_GEMM_IN_BF16 ? 1 : 0);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -238,7 +243,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       PairWork<PN> work(p, pair_id, num_pairs);
       PairItem it;
       while (ok && work.next(it)) {
-        const uint32_t idesc = it.width != PN ? idesc_half : idesc_whole;
+        const uint32_t idesc = it.width != tile_w ? idesc_half : idesc_whole;
         if (!mbar_wait(&sh->tempty[acc], acc_phase ^ 1, abort_flag)) {
           pair_report(kStatusWaitTimeout, 1, 100 + acc);
           break;
@@ -289,7 +294,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     PairWork<PN> work(p, pair_id, num_pairs);
     PairItem it;
     while (work.next(it)) {
-      const int mb = it.mb, nb = it.nb, n_off = it.n_off, width = it.width;
+      const int mb = it.mb, n_off = it.n_off, width = it.width;
+      const int n_tile0 = it.nb * work.tile_w; // first column of the tile
       const bool whole = it.k_begin == 0 && it.k_end == p.k_iters;
       bool failed = !mbar_wait(&sh->tfull[acc], acc_phase, abort_flag);
       if (p.c_tma || p.streamk_workers > 0) {
@@ -321,7 +327,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int slot = streamk_slot(total_iters, p.streamk_workers, p.k_iters, pair_id, sk_tile);
         float *mine = p.scratch + ((static_cast<size_t>(pair_id) * 2 + slot) * 2 + rank) * (kRows * PN);
 #pragma unroll 1
-        for (int c = 0; c < PN; c += 32) {
+        for (int c = 0; c < width; c += 32) {
           uint32_t r[32];
           tmem_ld_32x32b_x32(taddr + c, r);
           tmem_ld_wait();
@@ -350,7 +356,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           // Fixed order: ascending owner id, starting from zero
           // (wave_matmul.py:9756-9784), so the result is run-to-run identical.
 #pragma unroll 1
-          for (int c = 0; c < PN; c += 32) {
+          for (int c = 0; c < width; c += 32) {
             float v[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j)
@@ -362,7 +368,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               for (int j = 0; j < 32; ++j)
                 v[j] += __ldcg(&src[(c + j) * kRows + row_in_tile]);
             }
-            store_row_chunk<T, 32>(p, m, nb * kPairN + c, v);
+            store_row_chunk<T, 32>(p, m, n_tile0 + c, v);
           }
           if (row_in_tile == 0)
             atomicAdd(counter, -parts); // back to zero for the next launch
@@ -381,8 +387,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           // 128-byte rows instead of 16 bytes per thread; the store clips at the
           // matrix edge).  Two tiles, so that a store reads one while the four
           // epilogue warps fill the other.
+          int c = 0;
 #pragma unroll 1
-          for (int c = 0; c < width; c += kStoreCols, ++store_n) {
+          for (; c + kStoreCols <= width; c += kStoreCols, ++store_n) {
             uint32_t r0[32], r1[32];
             tmem_ld_32x32b_x32(taddr + c, r0);
             tmem_ld_32x32b_x32(taddr + c + 32, r1);
@@ -411,10 +418,25 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             fence_proxy_async_smem();
             epilogue_barrier();
             if (warp == 2 && lane == 0) {
-              tma_store_2d_evict_first(&tmap_c, buf, nb * kPairN + n_off + c,
+              tma_store_2d_evict_first(&tmap_c, buf, n_tile0 + n_off + c,
                                        mb * kPairM + static_cast<int>(rank) * kRows);
               tma_store_commit();
             }
+          }
+          if (c < width) {
+            // Tile widths that are not a multiple of 64 leave 32 columns: per-thread stores.
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(taddr + c, r);
+            tmem_ld_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0)
+              mbar_arrive_cluster(tempty_leader[acc]);
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              v[j] = __uint_as_float(r[j]);
+            store_row_chunk<T, 32>(p, m, n_tile0 + n_off + c, v);
           }
           if (++acc == 2) {
             acc = 0;
@@ -432,7 +454,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
         for (int j = 0; j < 32; ++j)
           v[j] = __uint_as_float(r[j]);
-        store_row_chunk<T, 32>(p, m, nb * kPairN + n_off + c, v);
+        store_row_chunk<T, 32>(p, m, n_tile0 + n_off + c, v);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -491,8 +513,10 @@ int gemm_pair_tile_m() { return kPairM; }
 int gemm_pair_tile_n() { return 256; }
 int gemm_pair_box_rows() { return kRows; }
 
-// `grid` must be even: consecutive CTAs form the pairs.  `tile_n` is 256 or
-// 128; the tensor map of B must have a box of tile_n / 2 rows, `tmap_b_half`
+// `grid` must be even: consecutive CTAs form the pairs.  `tile_n` is 128 (the
+// narrow instantiation) or a multiple of 32 in (128, 256] (the wide one, whose
+// tiles are then p.pair_tile_n = tile_n columns wide); the tensor map of B must
+// have a box of tile_n / 2 rows, `tmap_b_half`
 // (read only when tile_n is 256 and p.split_from < p.num_tiles) one of 64 rows,
 // `tmap_c` (read only when p.c_tma is set) a box of 64 columns x 128 rows over
 // the row-major 16-bit output.  Rows of C a store may touch beyond M, and
@@ -500,10 +524,13 @@ int gemm_pair_box_rows() { return kRows; }
 cudaError_t launch_gemm_pair(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, const CUtensorMap &tmap_b_half,
                              const CUtensorMap &tmap_c, const GemmParams &p, int tile_n, int grid,
                              cudaStream_t stream) {
-  if (tile_n == 256)
-    return launch_pair_out<256>(tmap_a, tmap_b, tmap_b_half, tmap_c, p, grid, stream);
   if (tile_n == 128)
     return launch_pair_out<128>(tmap_a, tmap_b, tmap_b_half, tmap_c, p, grid, stream);
+  if (tile_n > 128 && tile_n <= 256 && tile_n % 32 == 0) {
+    GemmParams q = p;
+    q.pair_tile_n = tile_n;
+    return launch_pair_out<256>(tmap_a, tmap_b, tmap_b_half, tmap_c, q, grid, stream);
+  }
   return cudaErrorInvalidValue;
 }
 

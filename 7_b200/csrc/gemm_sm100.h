@@ -22,6 +22,7 @@ struct GemmParams {
   int num_m_blocks, num_n_blocks, num_tiles, k_iters;
   int group_m;
   int split_from;      // CTA-pair kernel: tiles [split_from, num_tiles) run as two half-width work items each
+  int pair_tile_n;     // CTA-pair kernel, 256-column instantiation: columns of a tile (a multiple of 32 in (128, 256])
   int dp_tiles;        // tiles [0, dp_tiles) are whole tiles dealt round-robin over the grid
   int streamk_workers; // >0: tiles [dp_tiles, num_tiles) are split Stream-K style over that many workers (= grid)
   float *scratch;      // Stream-K: [workers][2][128 x tile_n] f32 partial tiles

@@ -78,7 +78,11 @@ EnvKnobs read_env() {
   if (const char *v = getenv("WAVE_CUDA_GEMM_SPLIT_TAIL"))
     e.gemm_split_tail = strcmp(v, "0") != 0;
   if (const char *v = getenv("WAVE_CUDA_GEMM_STREAMK_TAIL"))
-    e.gemm_streamk_tail = strcmp(v, "0") != 0;
+    e.gemm_streamk_tail = !strcmp(v, "0") ? 0 : !strcmp(v, "force") ? 2 : 1;
+  if (const char *v = getenv("WAVE_CUDA_GEMM_PAIR_TILE_N")) {
+    const int n = atoi(v);
+    e.gemm_pair_tile_n = (n > 128 && n <= 256 && n % 32 == 0) ? n : 0;
+  }
   if (const char *v = getenv("WAVE_CUDA_GEMM_TMA_STORE"))
     e.gemm_tma_store = strcmp(v, "0") != 0;
   if (const char *v = getenv("WAVE_CUDA_GEMM_L2_HINTS"))
@@ -188,10 +192,28 @@ constexpr double kSingleRate = 0.915;
 constexpr double kHalfItemCost = 0.72;
 
 // What the Stream-K treatment of a partly filled last round costs on top of
-// its share of a round, in rounds: writing and re-reading the f32 partial
-// tiles and the second pipeline fill of a worker that finishes one tile and
-// starts another.
-constexpr double kStreamKTailOverhead = 0.10;
+// its share of a round, in rounds: every pair writes f32 partial tiles, and the
+// last arriver of a tile reads them all back and stores C after everybody else
+// has finished, so that latency is exposed at the end of the kernel.  Measured
+// on 8192 x {1024, 2048, 8192} x 8192 bf16 (54, 34 and 62 tail tiles on 74
+// pairs): 0.55 to 1.1 rounds.
+constexpr double kStreamKTailOverhead = 0.75;
+
+// Relative duration of a round of 256 x n tiles of the CTA-pair kernel (n = 256:
+// 1).  A narrower tile saves less time than columns: per flop it moves more
+// operand bytes from L2, and under the power cap time follows energy rather
+// than tensor-pipe cycles.  Measured on 8192 x 2048 x 8192 bf16, sustained and
+// interleaved: a round of 224-column tiles 0.93 to 0.99, of 192-column tiles
+// 0.90 to 0.92 of a round of 256-column ones; 128 (the narrow instantiation) 0.72.
+double pair_tile_cost(int n) {
+  switch (n) {
+  case 256: return 1.0;
+  case 224: return 0.95;
+  case 192: return 0.92;
+  case 160: return 0.88;
+  }
+  return 1.0;
+}
 
 // How the CTA-pair kernel treats a last round of `tail` whole tiles on `pairs`
 // CTA pairs, and what that round then costs in rounds of whole tiles.
@@ -200,19 +222,48 @@ struct PairTailChoice {
   PairTail how;
   double rounds;
 };
-PairTailChoice pair_tail_choice(long long tail, long long pairs, int k_iters, bool streamk_allowed,
+PairTailChoice pair_tail_choice(long long tail, long long pairs, int k_iters, int tile_n, bool streamk_allowed,
                                 const wave::EnvKnobs &env) {
   PairTailChoice best{PairTail::kWhole, tail > 0 ? 1.0 : 0.0};
   if (tail <= 0)
     return best;
   // twice as many half-width items, if those still fit one round
-  if (env.gemm_split_tail && 2 * tail <= pairs && kHalfItemCost < best.rounds)
+  if (env.gemm_split_tail && tile_n == 256 && 2 * tail <= pairs && kHalfItemCost < best.rounds)
     best = {PairTail::kHalfItems, kHalfItemCost};
   // the tail's K iterations dealt evenly over all pairs
   if (streamk_allowed && env.gemm_streamk_tail && k_iters >= 8 && tail * k_iters >= pairs) {
     const double cost = static_cast<double>(tail) / static_cast<double>(pairs) + kStreamKTailOverhead;
-    if (cost < best.rounds)
+    if (cost < best.rounds || env.gemm_streamk_tail == 2)
       best = {PairTail::kStreamK, cost};
+  }
+  return best;
+}
+
+// Tile width of the CTA-pair kernel for a problem of num_m x Nk in kernel
+// space: the multiple of 32 in (128, 256] whose rounds of tiles, weighted by
+// the cost of a tile of that width, are fewest.  Narrower tiles make more of
+// them, which can turn a badly filled last round into a full one: 8192 x 1024
+// (an eighth of the 8192-column problem) is 128 tiles of 256 columns, 1.73
+// rounds on 74 pairs, but exactly two rounds of 148 tiles of 224 columns.
+struct PairWidthChoice {
+  int tile_n;
+  double cost; // rounds of 256-column tiles
+  PairTailChoice tail;
+};
+PairWidthChoice pair_width_choice(long long num_m, int Nk, long long pairs, int k_iters, bool streamk_allowed,
+                                  const wave::EnvKnobs &env) {
+  PairWidthChoice best{256, 0.0, {PairTail::kWhole, 0.0}};
+  bool first = true;
+  for (int n = 256; n > 128; n -= 32) {
+    if (env.gemm_pair_tile_n && n != env.gemm_pair_tile_n)
+      continue;
+    const long long tiles = num_m * ((Nk + n - 1) / n);
+    const PairTailChoice tail = pair_tail_choice(tiles % pairs, pairs, k_iters, n, streamk_allowed, env);
+    const double cost = (static_cast<double>(tiles / pairs) + tail.rounds) * pair_tile_cost(n);
+    if (first || cost < best.cost * 0.97) { // a narrower tile must win by a margin
+      best = {n, cost, tail};
+      first = false;
+    }
   }
   return best;
 }
@@ -267,24 +318,30 @@ int make_plan(const wave_gemm_desc &d, int sms, bool have_workspace, GemmPlan *p
   if (p.pair) {
     p.tile_m = wave::gemm_pair_tile_m();
     p.tile_n = wave::gemm_pair_tile_n();
-    const long long wide = static_cast<long long>((p.Mk + 255) / 256) * ((p.Nk + 255) / 256);
+    const long long num_m = (p.Mk + 255) / 256;
     const long long pairs = sms / 2;
     const int k_iters = (d.K + tile_k - 1) / tile_k;
-    if (sms > 0)
-      tail_choice = pair_tail_choice(wide % pairs, pairs, k_iters, auto_streamk, env);
+    double rounds_wide = 0.0;
+    if (sms > 0) {
+      const PairWidthChoice w = pair_width_choice(num_m, p.Nk, pairs, k_iters, auto_streamk, env);
+      p.tile_n = w.tile_n;
+      tail_choice = w.tail;
+      rounds_wide = w.cost;
+    }
+    const long long wide = num_m * ((p.Nk + p.tile_n - 1) / p.tile_n);
     // WAVE_CUDA_GEMM_KERNEL=pair128 forces the narrow pair tile (never chosen
     // automatically: its 256 x 128 x 16 MMAs run at 0.69 of the wide tile's rate).
     if (env.gemm_kernel == 3) {
       p.tile_n = 128;
       tail_choice = {PairTail::kWhole, 1.0};
     } else if (sms > 0 && env.gemm_kernel != 2) {
-      // Choose between 256 x 256 pair tiles and the one-CTA kernel's 128 x 256
-      // tiles by how well each fills its last round of tiles, weighted by the
-      // one-CTA kernel's measured steady-state rate relative to the pair's.
+      // Choose between the pair tiles and the one-CTA kernel's 128 x 256 tiles
+      // by how well each fills its rounds of tiles, weighted by the one-CTA
+      // kernel's measured steady-state rate relative to the pair's.
+      const long long wide256 = num_m * ((p.Nk + 255) / 256);
       const long long single = static_cast<long long>((p.Mk + 127) / 128) * ((p.Nk + 255) / 256);
       const long long r_wide = (wide + pairs - 1) / pairs, r_single = (single + sms - 1) / sms;
-      const double rounds = static_cast<double>(wide / pairs) + tail_choice.rounds;
-      const double f_wide = static_cast<double>(wide) / (rounds * static_cast<double>(pairs));
+      const double f_wide = static_cast<double>(wide256) / (rounds_wide * static_cast<double>(pairs));
       const double f_single = kSingleRate * static_cast<double>(single) / static_cast<double>(r_single * sms);
       // A single round is all prologue and epilogue: the smaller tile's shorter tail wins there
       // (unless the pair kernel spreads that round's K iterations over every pair).
@@ -347,7 +404,7 @@ int make_plan(const wave_gemm_desc &d, int sms, bool have_workspace, GemmPlan *p
     p.grid = p.pair ? 2 * workers : workers;
     // per worker two partial tiles: 128 x tile_n f32 (one CTA) or 256 x 256 (a CTA pair);
     // one arrival counter per Stream-K tile (per CTA of the pair)
-    p.scratch_bytes = static_cast<size_t>(workers) * 2 * p.tile_m * p.tile_n * sizeof(float);
+    p.scratch_bytes = static_cast<size_t>(workers) * 2 * p.tile_m * (p.pair ? 256 : p.tile_n) * sizeof(float);
     p.counter_bytes = static_cast<size_t>(tiles - dp_tiles) * (p.pair ? 2 : 1) * sizeof(int);
   } else {
     p.streamk_workers = 0;
@@ -356,7 +413,7 @@ int make_plan(const wave_gemm_desc &d, int sms, bool have_workspace, GemmPlan *p
     p.split_from = static_cast<int>(tiles);
     if (p.pair) {
       long long items = tiles;
-      if (sms > 0 && p.tile_n == wave::gemm_pair_tile_n() && tail_choice.how == PairTail::kHalfItems) {
+      if (sms > 0 && p.tile_n == 256 && tail_choice.how == PairTail::kHalfItems) {
         p.split_from = static_cast<int>(tiles - tiles % (sms / 2));
         items += tiles % (sms / 2);
       }

@@ -242,8 +242,12 @@ class GemmWork:
                 "tolerance": "|d| <= 1e-2 + 2^-7*|exp| (bf16 output: one ulp in place of the runner's 1e-3 term)"}
 
     def check_host(self, oracle) -> float:
-        """The end-to-end call's host result against the device-resident run's bits."""
-        return float((self.host_result().view(self.torch.int16) != self.c.cpu().view(self.torch.int16)).sum().item())
+        """Elements of the end-to-end call's host result that are more than one
+        bf16 unit in the last place away from the device-resident run's (the
+        host call computes C by column blocks, which may group the f32 sums
+        differently; anything beyond a rounding step would be an error)."""
+        got, ref = self.host_result().float(), self.c.cpu().float()
+        return float(((got - ref).abs() > 2.0 ** -7 * ref.abs() + 1e-30).sum().item())
 
 
 class FaWork:
@@ -646,7 +650,7 @@ def measure_workload(torch, wc, sh, workload, rank, world, strong, steps, warmup
                   "d2h_bytes_per_step": work.d2h, "ms_per_step": e2e_ms,
                   "h2d_gbs_per_rank": work.h2d / (e2e_ms * 1e-3) / 1e9, "d2h_gbs_per_rank": work.d2h / (e2e_ms * 1e-3) / 1e9,
                   "host_link_gbs_all_ranks": (work.h2d + work.d2h) * world / (e2e_ms * 1e-3) / 1e9,
-                  "elements_differing_from_device_run": mismatched,
+                  "elements_beyond_one_ulp_of_device_run": mismatched,
                   "path": ("each rank copies M/N rows of A and its B block from pinned host memory, the ranks "
                            "all-gather A over NVLink, wave_cuda_gemm_host_a_resident computes and returns the C block"
                            if sharded and work.kind == "gemm" else

@@ -174,21 +174,23 @@ def test_pair_kernel_streamk_tail(cuda, wc, oracle, M, N, K, out_name, layout, k
     counters are zero afterwards; two runs on random inputs are bit-identical
     (fixed reduction order); and the same with the tail treatment switched off."""
     in_name = "f16" if out_name == "f16" else "bf16"
-    with env_knobs(wc, WAVE_CUDA_GEMM_KERNEL="pair"):
-        desc = wc.gemm_desc(M, N, K, in_type=wc.TYPE_BY_NAME[in_name], out_type=wc.TYPE_BY_NAME[out_name],
-                            out_layout=wc.LAYOUT_BY_NAME[layout], streamk_workers=0, **knobs)
-        plan = wc.gemm_plan(desc)
-        assert (plan["tile_m"], plan["tile_n"]) == (256, 256) and plan["streamk_workers"] == plan["grid"] // 2 > 1, plan
-    a, b = lcg_inputs(oracle, M, N, K, in_name, seed=M + 7)
-    got, counters = run_gemm(cuda, wc, a, b, in_name, out_name, layout, streamk=0, **knobs)
-    want = expected(oracle, a, b, in_name, out_name)
-    assert np.array_equal(got, want), f"max abs diff {np.nanmax(np.abs(got - want))}"
-    assert counters is not None and counters.size > 0 and not counters.any()
     t = oracle.F16 if in_name == "f16" else oracle.BF16
-    a = oracle.baseline_inputs((M, K), "normal", 9, 0, t)
-    b = oracle.baseline_inputs((N, K), "normal", 9, 1, t, scale=K ** -0.5)
-    r1, _ = run_gemm(cuda, wc, a, b, in_name, out_name, layout, streamk=0, **knobs)
-    r2, _ = run_gemm(cuda, wc, a, b, in_name, out_name, layout, streamk=0, **knobs)
+    # the planner takes this treatment only where its cost model says it pays; here it is forced
+    with env_knobs(wc, WAVE_CUDA_GEMM_STREAMK_TAIL="force", WAVE_CUDA_GEMM_PAIR_TILE_N="256"):
+        with env_knobs(wc, WAVE_CUDA_GEMM_KERNEL="pair"):
+            desc = wc.gemm_desc(M, N, K, in_type=wc.TYPE_BY_NAME[in_name], out_type=wc.TYPE_BY_NAME[out_name],
+                                out_layout=wc.LAYOUT_BY_NAME[layout], streamk_workers=0, **knobs)
+            plan = wc.gemm_plan(desc)
+            assert (plan["tile_m"], plan["tile_n"]) == (256, 256) and plan["streamk_workers"] == plan["grid"] // 2 > 1, plan
+        a, b = lcg_inputs(oracle, M, N, K, in_name, seed=M + 7)
+        got, counters = run_gemm(cuda, wc, a, b, in_name, out_name, layout, streamk=0, **knobs)
+        want = expected(oracle, a, b, in_name, out_name)
+        assert np.array_equal(got, want), f"max abs diff {np.nanmax(np.abs(got - want))}"
+        assert counters is not None and counters.size > 0 and not counters.any()
+        a = oracle.baseline_inputs((M, K), "normal", 9, 0, t)
+        b = oracle.baseline_inputs((N, K), "normal", 9, 1, t, scale=K ** -0.5)
+        r1, _ = run_gemm(cuda, wc, a, b, in_name, out_name, layout, streamk=0, **knobs)
+        r2, _ = run_gemm(cuda, wc, a, b, in_name, out_name, layout, streamk=0, **knobs)
     assert np.array_equal(r1, r2)
     ok, worst, nbad = runner_tolerance_ok(r1, expected(oracle, a, b, in_name, out_name), out_name)
     assert ok, f"{nbad} elements out of tolerance, worst {worst}"
@@ -196,6 +198,46 @@ def test_pair_kernel_streamk_tail(cuda, wc, oracle, M, N, K, out_name, layout, k
         whole, _ = run_gemm(cuda, wc, a, b, in_name, out_name, layout, streamk=0, **knobs)
     ok, worst, nbad = runner_tolerance_ok(r1, whole, out_name)
     assert ok, f"tail on/off differ beyond rounding: {nbad} elements, worst {worst}"
+
+
+@pytest.mark.parametrize("width", [224, 192, 160])
+@pytest.mark.parametrize("M,N,K,out_name,layout,knobs", [
+    (512, 1280, 192, "bf16", "row-major", PAIR_KNOBS),
+    (768, 1024, 128, "f32", "row-major", PAIR_KNOBS),          # last column tile narrower than the rest
+    (1024, 768, 256, "bf16", "column-major", PAIR_KNOBS),      # computed as C^T
+    (400, 464, 208, "f16", "row-major", dict(bm=1, bn=1, wave_m_tiles=25, wave_n_tiles=29)),  # ragged both ways
+])
+def test_pair_kernel_tile_widths(cuda, wc, oracle, width, M, N, K, out_name, layout, knobs):
+    """The CTA-pair kernel's tiles may be any multiple of 32 columns in
+    (128, 256] (the planner narrows them where that fills the last round of
+    tiles); widths that are not a multiple of 64 end in a 32-column chunk that
+    leaves by per-thread stores.  LCG inputs, bit-exact."""
+    in_name = "f16" if out_name == "f16" else "bf16"
+    a, b = lcg_inputs(oracle, M, N, K, in_name, seed=width + M)
+    with env_knobs(wc, WAVE_CUDA_GEMM_PAIR_TILE_N=width):
+        with env_knobs(wc, WAVE_CUDA_GEMM_KERNEL="pair"):
+            plan = wc.gemm_plan(wc.gemm_desc(M, N, K, in_type=wc.TYPE_BY_NAME[in_name],
+                                             out_type=wc.TYPE_BY_NAME[out_name],
+                                             out_layout=wc.LAYOUT_BY_NAME[layout], **knobs))
+            assert (plan["tile_m"], plan["tile_n"]) == (256, width), plan
+        got, _ = run_gemm(cuda, wc, a, b, in_name, out_name, layout, **knobs)
+    want = expected(oracle, a, b, in_name, out_name)
+    assert np.array_equal(got, want), f"max abs diff {np.nanmax(np.abs(got - want))}"
+
+
+def test_planner_narrows_tiles_for_column_shards(cuda, wc):
+    """An eighth of the 8192-column problem (column-major C, so the kernel sees
+    C^T: 1024 rows by 8192 columns) is 1.73 rounds of 256-column tiles on 74 CTA
+    pairs but exactly two full rounds of 224-column ones; a quarter keeps 256
+    (its sparse last round runs as half-width items), and so do half of it and
+    the whole problem."""
+    if cuda.cuda.get_device_properties(0).multi_processor_count != 148:
+        pytest.skip("the expected plans are those of a 148-SM part")
+    for n_local, want in ((1024, 224), (2048, 256), (4096, 256), (8192, 256)):
+        d = wc.gemm_desc(8192, n_local, 8192, in_type=wc.BF16, out_type=wc.BF16, out_layout=wc.COL_MAJOR,
+                         streamk_workers=0, **PAIR_KNOBS)
+        plan = wc.gemm_plan(d)
+        assert (plan["tile_m"], plan["tile_n"], plan["swapped"]) == (256, want, True), (n_local, plan)
 
 
 @pytest.mark.parametrize("kernel", ["pair", "single"])

@@ -46,10 +46,10 @@ def _worker(rank, world, port, tmpdir):
         full_cm = sh.all_gather_shards(local, dist).reshape(N, M).numpy()   # n*M + m
         assert np.array_equal(full_cm.T, oracle.gemm_ref(a, b, oracle.BF16))
         # the replicated A reaches every rank as row blocks exchanged by an all-gather
-        a_t = torch.from_numpy(a.view(np.int16))
+        a_t = torch.from_numpy(a.view(np.uint8).reshape(M, 2 * K))  # 16-bit patterns as bytes: gloo has no int16
         r0, r1 = sh.row_shard(M, world, rank)
         assert (r1 - r0) * world == M
-        a_rows = sh.all_gather_shards(a_t[r0:r1], dist).reshape(M, K)
+        a_rows = sh.all_gather_shards(a_t[r0:r1], dist).reshape(M, 2 * K)
         assert torch.equal(a_rows, a_t)
         # attention: (batch*head) slabs
         BH, S, D = 4, 32, 128
