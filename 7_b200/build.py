@@ -14,8 +14,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libwave_cuda.so")
-SOURCES = ["gemm_sm100.cu", "gemm_pair_sm100.cu", "gemm_noalloc_sm100.cu", "fa_sm100.cu", "fa_stream_sm100.cu", "wave_cuda_backend.cu",
-           "mgpu_runtime.cu"]
+SOURCES = ["gemm_sm100.cu", "gemm_pair_sm100.cu", "gemm_noalloc_sm100.cu", "fa_sm100.cu", "fa_stream_sm100.cu",
+           "fa_pair_sm100.cu", "wave_cuda_backend.cu", "mgpu_runtime.cu"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 
@@ -26,25 +26,22 @@ def _nvcc() -> str:
     raise RuntimeError("nvcc not found; set NVCC")
 
 
-def needs_build() -> bool:
-    if not os.path.exists(LIB):
+def needs_build(lib: str = LIB) -> bool:
+    if not os.path.exists(lib):
         return True
-    built = os.path.getmtime(LIB)
+    built = os.path.getmtime(lib)
     deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [
         os.path.join(HERE, "..", "include", "wave_cuda.h")]
     return any(os.path.getmtime(d) > built for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    if not force and not needs_build():
-        return LIB
+def _compile_and_link(lib: str, build_dir: str, extra_flags: list[str], verbose: bool) -> str:
     objs = []
     procs = []
-    build_dir = os.path.join(HERE, "build")
     os.makedirs(build_dir, exist_ok=True)
     for src in SOURCES:
         obj = os.path.join(build_dir, src.replace(".cu", ".o"))
-        cmd = [_nvcc(), *ARCH_FLAGS, "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
+        cmd = [_nvcc(), *ARCH_FLAGS, "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", *extra_flags,
                "-Xptxas", "-v" if verbose else "-warn-spills", "-c", os.path.join(CSRC, src), "-o", obj]
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
         objs.append(obj)
@@ -54,10 +51,35 @@ def build(force: bool = False, verbose: bool = False) -> str:
             sys.stderr.write(out)
         if proc.returncode != 0:
             raise RuntimeError(f"nvcc failed on {src}")
-    link = [_nvcc(), *ARCH_FLAGS, "-shared", "-o", LIB, *objs]
+    # link beside the target and rename: a reader never sees a half-written library
+    link = [_nvcc(), *ARCH_FLAGS, "-shared", "-o", lib + ".tmp", *objs]
     subprocess.run(link, check=True)
-    return LIB
+    os.replace(lib + ".tmp", lib)
+    return lib
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    if not force and not needs_build():
+        return LIB
+    return _compile_and_link(LIB, os.path.join(HERE, "build"), [], verbose)
+
+
+# A second build of the same sources for ONE test (tests/test_wait_unwind_gpu.py):
+# device-side waits give up after about a millisecond instead of a second, and
+# the one-CTA GEMM's producer can be told to leave out a K step, so that the
+# unwind of a wait that runs out (status word, abort flag, TMEM release) can be
+# watched without anything hanging.  The product library has neither.
+WAIT_TEST_LIB = os.path.join(HERE, "libwave_cuda_waittest.so")
+WAIT_TEST_FLAGS = ["-DWAVE_WAIT_TEST", "-DWAVE_WAIT_LIMIT_CYCLES=2000000"]
+
+
+def build_wait_test(force: bool = False, verbose: bool = False) -> str:
+    if not force and os.path.exists(WAIT_TEST_LIB) and not needs_build(WAIT_TEST_LIB):
+        return WAIT_TEST_LIB
+    return _compile_and_link(WAIT_TEST_LIB, os.path.join(HERE, "build_waittest"), WAIT_TEST_FLAGS, verbose)
 
 
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    if "--wait-test" in sys.argv:
+        print(build_wait_test(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

@@ -875,6 +875,12 @@ int launch_flash_attention(const FaParams &p, const void *Q, const void *K, cons
       ticket_launched(slot, stream);
       return rc;
     }
+    // WAVE_CUDA_FA_KERNEL=pair: the CTA-pair kernel (needs an even number of SMs).
+    if (env.fa_kernel == 3 && sm_count >= 2) {
+      const int rc = launch_flash_attention_pair(params, tq, K, tv, poly, sm_count, stream);
+      ticket_launched(slot, stream);
+      return rc;
+    }
   }
   if (poly < 0)
     poly = kDefaultPoly;
@@ -943,6 +949,12 @@ cudaError_t fa_read_status(int out[4], bool clear) {
     return err;
   int other[4];
   err = fa_stream_read_status(other, clear);
+  if (err == cudaSuccess && out[0] == 0 && other[0] != 0)
+    for (int i = 0; i < 4; ++i)
+      out[i] = other[i];
+  if (err != cudaSuccess)
+    return err;
+  err = fa_pair_read_status(other, clear);
   if (err == cudaSuccess && out[0] == 0 && other[0] != 0)
     for (int i = 0; i < 4; ++i)
       out[i] = other[i];

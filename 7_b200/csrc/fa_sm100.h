@@ -31,6 +31,12 @@ cudaError_t fa_read_status(int out[4], bool clear);
 int launch_flash_attention_stream(const FaParams &p, const CUtensorMap &tq, const CUtensorMap &tk,
                                   const CUtensorMap &tv, int poly, int sm_count, cudaStream_t stream);
 cudaError_t fa_stream_read_status(int out[4], bool clear);
+// The CTA-pair kernel (fa_pair_sm100.cu): 512-row work items on 2-CTA clusters,
+// tcgen05 cta_group::2.  `tq` / `tv` have boxes of 64 elements x 128 rows; K's
+// map (64 x 64) is built inside.  `p.ticket` as above.
+int launch_flash_attention_pair(const FaParams &p, const CUtensorMap &tq, const void *K, const CUtensorMap &tv, int poly,
+                                int sm_count, cudaStream_t stream);
+cudaError_t fa_pair_read_status(int out[4], bool clear);
 
 // Provided by the backend: rank-2/3 tensor map over 16-bit elements with the
 // 128-byte swizzle and zero fill outside the tensor.

@@ -161,7 +161,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       while (ok && work.next(seg)) {
         int mb, nb;
         tile_coords(seg.tile, p.num_m_blocks, p.num_n_blocks, p.group_m, mb, nb);
-        for (int kb = seg.k_begin; kb < seg.k_end; ++kb) {
+#ifdef WAVE_WAIT_TEST
+        const int k_stop = seg.k_end - (p.test_skip_last_k ? 1 : 0);
+#else
+        const int k_stop = seg.k_end;
+#endif
+        for (int kb = seg.k_begin; kb < k_stop; ++kb) {
           if (!mbar_wait(&sh->empty[stage], phase ^ 1, abort_flag)) {
             report(kStatusWaitTimeout, 0, stage);
             ok = false;

@@ -34,6 +34,10 @@ struct GemmParams {
   int c_tma; // whole tiles leave through TMA stores (row-major 16-bit C, tiles of at least 64 columns)
   // L2 eviction hints on the operand loads: 0 none, 1 A "evict last" + B "evict first", 2 A "evict last" only
   int l2_hints;
+  // Test builds only (-DWAVE_WAIT_TEST): the one-CTA kernel's producer leaves out
+  // the last K step of every segment, so that the UMMA thread's wait for it runs
+  // out and the bounded-wait unwind can be observed.  Always 0 in the product.
+  int test_skip_last_k;
 };
 
 int gemm_tile_m();

@@ -73,24 +73,32 @@ bool is_host_pointer(const void *ptr) {
   return attr.type == cudaMemoryTypeHost || attr.type == cudaMemoryTypeUnregistered;
 }
 
-// Dense extent in bytes of a strided memref descriptor and its first byte.
-// {allocated, aligned, offset, sizes[rank], strides[rank]}; the region from the
-// first to the last addressed element is registered, whatever the strides.
+// The range of bytes a strided memref descriptor addresses:
+// {allocated, aligned, offset, sizes[rank], strides[rank]}.  Element (i_0, ...)
+// lies at aligned + (offset + sum i_d * stride_d) * elem, so a dimension with a
+// negative stride reaches BELOW the element at index zero: the lowest and the
+// highest addressed element are found separately and the region between them
+// is what gets registered.
 void memref_region(int64_t rank, void *descriptor, int64_t elem, char **first, size_t *bytes) {
   char **ptrs = static_cast<char **>(descriptor);
   const int64_t *ints = reinterpret_cast<const int64_t *>(ptrs + 2);
   const int64_t offset = ints[0];
   const int64_t *sizes = ints + 1, *strides = ints + 1 + rank;
-  int64_t last = 0;
+  int64_t lowest = 0, highest = 0; // element offsets relative to the element at index zero
   bool empty = false;
   for (int64_t i = 0; i < rank; ++i) {
-    if (sizes[i] <= 0)
+    if (sizes[i] <= 0) {
       empty = true;
+      continue;
+    }
+    const int64_t reach = (sizes[i] - 1) * strides[i];
+    if (reach < 0)
+      lowest += reach;
     else
-      last += (sizes[i] - 1) * (strides[i] < 0 ? -strides[i] : strides[i]);
+      highest += reach;
   }
-  *first = ptrs[1] + offset * elem;
-  *bytes = empty ? 0 : static_cast<size_t>(last + 1) * static_cast<size_t>(elem);
+  *first = ptrs[1] + (offset + (empty ? 0 : lowest)) * elem;
+  *bytes = empty ? 0 : static_cast<size_t>(highest - lowest + 1) * static_cast<size_t>(elem);
 }
 
 } // namespace
@@ -98,6 +106,15 @@ void memref_region(int64_t rank, void *descriptor, int64_t elem, char **first, s
 extern "C" {
 
 int wave_cuda_mgpu_status(void) { return g_first_failure.exchange(0); }
+
+int wave_cuda_memref_region(int64_t rank, void *descriptor, int64_t elem_bytes, void **first, size_t *bytes) {
+  if (rank < 0 || !descriptor || elem_bytes <= 0 || !first || !bytes)
+    return WAVE_E_INVALID;
+  char *lo = nullptr;
+  memref_region(rank, descriptor, elem_bytes, &lo, bytes);
+  *first = lo;
+  return WAVE_OK;
+}
 
 int wave_cuda_module_blob_bytes(uint32_t kind, size_t *bytes) {
   const size_t d = desc_bytes_of(kind);

@@ -15,8 +15,14 @@
 
 namespace wave {
 
-// ~1 s at 2 GHz.  A healthy kernel waits microseconds.
+// ~1 s at 2 GHz.  A healthy kernel waits microseconds.  (A test build of the
+// library shortens the limit with -DWAVE_WAIT_LIMIT_CYCLES=<cycles> so that a
+// wait can be made to run out within a millisecond.)
+#ifdef WAVE_WAIT_LIMIT_CYCLES
+constexpr long long kWaitLimitCycles = WAVE_WAIT_LIMIT_CYCLES;
+#else
 constexpr long long kWaitLimitCycles = 1ll << 31;
+#endif
 
 // Status words written by kernels (device global, read back by the host).
 enum StatusCode : int {

@@ -753,6 +753,10 @@ int wave_cuda_gemm(const wave_gemm_desc *d, const void *A, const void *B, void *
     p.tp_wnt = d->wave_n_tiles;
     p.tp_n_blocks = (d->N / 16) / (d->bn * d->wave_n_tiles);
   }
+#ifdef WAVE_WAIT_TEST
+  if (const char *v = getenv("WAVE_CUDA_TEST_SKIP_LAST_K")) // test builds only; read on every launch
+    p.test_skip_last_k = strcmp(v, "1") == 0 ? 1 : 0;
+#endif
   p.streamk_workers = plan.streamk_workers;
   p.dp_tiles = plan.dp_tiles;
   p.scratch = static_cast<float *>(workspace);

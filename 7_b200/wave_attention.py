@@ -34,6 +34,22 @@ def make_runner_inputs(batch: int, heads: int, sequence: int, *, seed: int = 0, 
     return tuple(input_bits(x, io_type).reshape(shape) for x in (q, k, v))
 
 
+def generate_flash_attention_f32_inputs(block_m: int, head_dim: int, seq_n: int, *, random_seed: int = 0):
+    """Inputs of the toy kernel `flash_attention_f32` as f16 bit patterns
+    (python/mlir/dialects/wave_attention.py:225-245; C++ twin
+    tools/wave-fa-calibrate/wave-fa-calibrate-runner.cpp:183-206): Q [block_m, d]
+    from LCG stream 0 x0.0625, multiplied by log2(e)/sqrt(d) in double precision
+    and rounded straight to f16; K and V [seq_n, d] from streams 1 (x0.0625) and
+    2 (x0.125)."""
+    q = deterministic_random_values(block_m * head_dim, seed=random_seed, stream=0, scale=0.0625)
+    k = deterministic_random_values(seq_n * head_dim, seed=random_seed, stream=1, scale=0.0625)
+    v = deterministic_random_values(seq_n * head_dim, seed=random_seed, stream=2, scale=0.125)
+    scale = math.log2(math.e) / math.sqrt(head_dim)
+    f16 = lambda x: np.asarray(x, np.float64).astype(np.float16).view(np.uint16)
+    return (f16(q.astype(np.float64) * scale).reshape(block_m, head_dim), f16(k).reshape(seq_n, head_dim),
+            f16(v).reshape(seq_n, head_dim))
+
+
 def flops(batch: int, heads: int, sequence: int, head_dim: int = HEAD_DIM, causal: bool = False) -> float:
     """4*B*H*S^2*D (wave_flash_attention.py:138-139); for causal, the unmasked pairs only."""
     pairs = sequence * (sequence + 1) / 2 if causal else float(sequence) * sequence

@@ -53,7 +53,7 @@ EXPORTS = [
     "wave_cuda_flash_attention_fwd_host", "wave_cuda_module_get_function", "wave_cuda_launch",
     "wave_cuda_function_release", "wave_cuda_check_device_status",
     # include/wave_mgpu.h: the wrappers a host module lowered by gpu-to-llvm calls
-    "wave_cuda_module_blob_bytes", "wave_cuda_module_blob_write", "wave_cuda_mgpu_status",
+    "wave_cuda_module_blob_bytes", "wave_cuda_module_blob_write", "wave_cuda_mgpu_status", "wave_cuda_memref_region",
     "mgpuModuleLoad", "mgpuModuleUnload", "mgpuModuleGetFunction", "mgpuLaunchKernel", "mgpuStreamCreate",
     "mgpuStreamDestroy", "mgpuStreamSynchronize", "mgpuStreamWaitEvent", "mgpuEventCreate", "mgpuEventDestroy",
     "mgpuEventSynchronize", "mgpuEventRecord", "mgpuMemAlloc", "mgpuMemFree", "mgpuMemcpy", "mgpuMemset32",
@@ -103,6 +103,7 @@ def lib() -> C.CDLL:
     L.wave_cuda_module_blob_bytes.argtypes = [C.c_uint32, C.POINTER(sz)]
     L.wave_cuda_module_blob_write.argtypes = [C.c_uint32, vp, vp, sz]
     L.wave_cuda_mgpu_status.argtypes = []
+    L.wave_cuda_memref_region.argtypes = [ll, vp, ll, C.POINTER(vp), C.POINTER(sz)]
     for name, res, args in [
             ("mgpuModuleLoad", vp, [vp, sz]), ("mgpuModuleUnload", None, [vp]),
             ("mgpuModuleGetFunction", vp, [vp, C.c_char_p]),

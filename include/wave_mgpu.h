@@ -56,6 +56,13 @@ typedef struct wave_cuda_module_blob {
 int wave_cuda_module_blob_bytes(uint32_t kind, size_t *bytes);
 int wave_cuda_module_blob_write(uint32_t kind, const void *desc, void *out, size_t out_bytes);
 int wave_cuda_mgpu_status(void);
+/* The host range mgpuMemHostRegisterMemRef / ...UnregisterMemRef act on for a
+ * ranked memref descriptor {allocated, aligned, offset, sizes[rank],
+ * strides[rank]} of `elem_bytes`-byte elements: from the lowest to the highest
+ * addressed element (strides may be negative), `bytes` = 0 for an empty
+ * memref.  Needs no GPU.  (MLIR's own wrapper, mgpuMemHostRegisterMemRef in
+ * mlir/lib/ExecutionEngine/CudaRuntimeWrappers.cpp, assumes dense row-major.) */
+int wave_cuda_memref_region(int64_t rank, void *descriptor, int64_t elem_bytes, void **first, size_t *bytes);
 
 /* ---- MLIR's wrapper API (names and argument lists as gpu-to-llvm emits them) */
 void *mgpuModuleLoad(void *data, size_t gpuBlobSize);

@@ -26,13 +26,20 @@ _f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
 _i32p = np.ctypeslib.ndpointer(np.int32, flags="C_CONTIGUOUS")
 
 
+def reference_root() -> str:
+    """Where the reference checkout lies, if there is one: the
+    WAVE_REFERENCE_ROOT environment variable, else a directory named
+    `reference` beside this repository (the Makefile uses the same rule)."""
+    return os.environ.get("WAVE_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
 def build(force: bool = False) -> None:
     """Compile the oracle (and the reference shim when a checkout is present)."""
     lib = os.path.join(HERE, "libwave_oracle.so")
     src = os.path.join(HERE, "wave_oracle.c")
     if force or not os.path.exists(lib) or os.path.getmtime(lib) < os.path.getmtime(src):
         subprocess.run(["make", "-C", HERE, "-B"], check=True, capture_output=True)
-    elif os.path.isdir("/root/reference") and not os.path.exists(
+    elif os.path.isdir(reference_root()) and not os.path.exists(
         os.path.join(HERE, "_ref", "libwave_ref.so")
     ):
         subprocess.run(["make", "-C", HERE, "ref"], check=True, capture_output=True)

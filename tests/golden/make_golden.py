@@ -94,7 +94,8 @@ FA_CASES = [
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("WAVE_REFERENCE_ROOT"), required="WAVE_REFERENCE_ROOT" not in os.environ,
+                    help="path of the reference checkout (or set WAVE_REFERENCE_ROOT)")
     args = ap.parse_args()
     wm, wa = _load_reference(args.reference)
 

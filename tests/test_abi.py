@@ -157,3 +157,32 @@ def test_compute_without_a_device_fails_loudly(wc):
     with pytest.raises(wc.WaveCudaError) as err:
         wc.gemm_host(wc.gemm_desc(16, 16, 16, bn=1), a.ctypes.data, a.ctypes.data, c.ctypes.data)
     assert err.value.code == wc.E_CUDA
+
+
+def test_memref_region_with_any_strides(wc):
+    """The host range behind a ranked memref descriptor, which is what the
+    mgpuMemHostRegisterMemRef wrapper registers: from the lowest to the highest
+    addressed element.  A negative stride reaches below the element at index
+    zero, so the range must start there, not at aligned + offset."""
+    lib = wc.lib()
+
+    def region(offset, sizes, strides, elem):
+        rank = len(sizes)
+        buf = (C.c_int64 * (3 + 2 * rank))()
+        base = 1 << 20
+        buf[0], buf[1], buf[2] = base, base, offset
+        for i, (sz, st) in enumerate(zip(sizes, strides)):
+            buf[3 + i], buf[3 + rank + i] = sz, st
+        first, nbytes = C.c_void_p(), C.c_size_t()
+        assert lib.wave_cuda_memref_region(rank, buf, elem, C.byref(first), C.byref(nbytes)) == wc.OK
+        return (first.value or 0) - base, nbytes.value
+
+    assert region(0, [4, 8], [8, 1], 2) == (0, 64)               # dense row-major 4 x 8 f16
+    assert region(5, [10], [1], 4) == (20, 40)                   # a window at an offset
+    assert region(0, [4, 8], [16, 2], 2) == (0, (3 * 16 + 7 * 2 + 1) * 2)   # strided, with holes
+    assert region(9, [10], [-1], 4) == (0, 40)                   # reversed vector: lowest byte below index zero
+    assert region(31, [4, 8], [-8, -1], 2) == (0, 64)            # both dimensions reversed
+    assert region(24, [4, 8], [-8, 1], 2) == (0, 64)             # rows reversed only
+    assert region(3, [0, 8], [8, 1], 2) == (6, 0)                # empty
+    assert region(7, [], [], 8) == (56, 8)                       # rank 0: one element
+    assert lib.wave_cuda_memref_region(1, None, 4, None, None) == wc.E_INVALID

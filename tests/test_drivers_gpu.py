@@ -113,3 +113,36 @@ def test_attention_calibrate_runner(cuda):
     assert "head_dim must be a multiple of 16 between 16 and 128" in err
     _, err = run("wave_fa_gfx950.py", "--qk-max-abs=2", "--input-scale=2", expect=1)
     assert "qk_max_abs fixed reference exceeds BF16 range" in err
+
+
+def test_toy_attention_calibrate_tool(cuda):
+    """The drop-in for tools/wave-fa-calibrate/wave-fa-calibrate.py: the toy
+    kernel `flash_attention_f32` by name, the runner's keys and its 3e-3 check
+    (wave-fa-calibrate-runner.cpp:250-292; the configurations of
+    test/Integration/wave_flash_attention.mlir)."""
+    out, _ = run("wave_fa_calibrate.py", "--iters=5", "--warmup=1")
+    for key in ("kernel: flash_attention_f32", "shape: block_m=16 block_n=16 seq_n=16 head_dim=32 seed=0", "iters: 5",
+                "total_ms: ", "per_launch_us: ", "per_launch_cycles_wallclock: ", "output_check: passed max_abs_diff="):
+        assert key in out, out
+    assert out.count("variant: ") == 2  # baseline and scheduled, like the reference's default
+    out, _ = run("wave_fa_calibrate.py", "--head-dim=64", "--seq-n=512", "--seed=7", "--iters=3", "--warmup=1", "--repeats=3",
+                 "--variants=scheduled", "--target-waves=2")
+    assert "seq_n=512 head_dim=64 seed=7" in out and "output_check: passed" in out and "median_per_launch_us: " in out
+    out, _ = run("wave_fa_calibrate.py", "--head-dim=128", "--seq-n=256", "--skip-hw")
+    assert "grid: 1,1,1" in out and "per_launch_us" not in out
+    _, err = run("wave_fa_calibrate.py", "--seq-n=24", expect=2)
+    assert "seq-n must be a multiple of block-n" in err
+
+
+def test_perf_sweep_selected_kernels_and_shapes(cuda, tmp_path):
+    """--kernels / --m / --n / --k-values / --fa-* pick what the sweep runs
+    (wave-matmul-perf-sweep.py:864-992); the CSV keeps the reference's columns."""
+    csv_path = tmp_path / "sweep.csv"
+    out, _ = run("wave_matmul_perf_sweep.py", "--kernels=f16,f16-streamk,fa", "--m=512", "--n=768", "--k-values=256,512",
+                 "--streamk-workers=24", "--fa-batch=1", "--fa-heads=2", "--fa-sequence=512", "--fa-modes=adaptive",
+                 "--fa-causal=no", "--iters=3", "--warmup=1", "--repeats=2", "--check", f"--csv={csv_path}")
+    lines = [ln for ln in out.splitlines() if ln.startswith("| f") ]
+    assert len(lines) == 5 and all("passed" in ln for ln in lines), out
+    assert "| f16-gemm-streamk | 512x768x512 |" in out and "| fa-bf16-adaptive | B=1 H=2 S=512 D=128 |" in out
+    header = csv_path.read_text().splitlines()[0].split(",")
+    assert header[:5] == ["kernel", "profile", "m", "n", "k"] and header[-1] == "waves" and len(header) == 22

@@ -18,11 +18,11 @@ from _util import env_knobs, to_device_bits
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(params=["pingpong", "stream"], autouse=True)
+@pytest.fixture(params=["pingpong", "stream", "pair"], autouse=True)
 def fa_kernel(request, wc):
-    """Every test runs on both attention kernels (two Q tiles ping-ponging; one
-    Q tile with double-buffered scores).  Left alone, the library picks one by
-    the key sequence length."""
+    """Every test runs on all three attention kernels (two Q tiles ping-ponging;
+    one Q tile with double-buffered scores; CTA pairs on 512-row work items).
+    Left alone, the library picks one by the shape."""
     with env_knobs(wc, WAVE_CUDA_FA_KERNEL=request.param):
         yield request.param
 

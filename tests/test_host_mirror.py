@@ -101,3 +101,41 @@ def test_attention_runner_inputs_match_oracle(oracle):
     assert np.array_equal(k.reshape(-1), oracle.fa_input_bits(n, oracle.BF16, 9, 1, 0.125))
     assert np.array_equal(v.reshape(-1), oracle.fa_input_bits(n, oracle.BF16, 9, 2, 0.25))
     assert wa.flops(2, 64, 8192) == 4.0 * 2 * 64 * 8192 * 8192 * 128
+
+
+def test_perf_sweep_selectors_dry_run():
+    """The sweep's selectors and their validation need no GPU
+    (tools/wave-matmul-calibrate/wave-matmul-perf-sweep.py:864-1058)."""
+    import subprocess
+    import sys
+    tool = os.path.join(os.path.dirname(os.path.abspath(__file__)), "drivers", "wave_matmul_perf_sweep.py")
+
+    def sweep(*args):
+        return subprocess.run([sys.executable, tool, "--dry-run", *args], capture_output=True, text=True, timeout=120)
+    p = sweep("--kernels=f16-4wave,fa", "--m=2048", "--n=1024", "--k-values=1024", "--fa-sequence=4096",
+              "--fa-modes=bounded", "--fa-causal=no", "--variants=scheduled", "--hpl" if False else "--seed=3")
+    assert p.returncode == 0, p.stderr
+    assert "--m 2048 --n 1024 --k 1024" in p.stdout and "--sequence 4096" in p.stdout and "--qk-max-abs 1" in p.stdout
+    assert p.stdout.count("wave_matmul_calibrate.py") == 1 and p.stdout.count("wave_fa_gfx950.py") == 1
+    p = sweep()  # default: K sweep + the two 8192^3 points for f16 and bf16, four attention rows
+    assert p.stdout.count("wave_matmul_calibrate.py") == 16 and p.stdout.count("wave_fa_gfx950.py") == 4
+    for bad, message in ((["--kernels=mxfp4"], "outside this backend"),
+                         (["--kernels=f16", "--streamk-workers=8"], "--streamk-workers requires --kernels=f16-streamk"),
+                         (["--kernels=fa", "--rand-int"], "FA sweep supports random floating-point inputs only"),
+                         (["--kernels=fa", "--variants=baseline"], "FA sweep supports only --variants=scheduled"),
+                         (["--m=0"], "--m must be positive"),
+                         (["--kernels=fa", "--fa-qk-max-abs=0"], "--fa-qk-max-abs must be finite and positive")):
+        p = sweep(*bad)
+        assert p.returncode != 0 and message in p.stderr, (bad, p.stderr)
+
+
+def test_toy_attention_inputs_match_oracle(oracle):
+    """The product-side generator of the toy attention inputs against the oracle's
+    restatement of python/mlir/dialects/wave_attention.py:225-245."""
+    import importlib
+    wa = importlib.import_module("7_b200.wave_attention")
+    from test_oracle import toy_fa_inputs
+    for bm, hd, sn, seed in ((16, 32, 16, 0), (16, 64, 512, 7), (16, 128, 256, 91)):
+        q, k, v = wa.generate_flash_attention_f32_inputs(bm, hd, sn, random_seed=seed)
+        wq, wk, wv = toy_fa_inputs(oracle, bm, hd, sn, seed)
+        assert np.array_equal(q, wq[0]) and np.array_equal(k, wk[0]) and np.array_equal(v, wv[0])
