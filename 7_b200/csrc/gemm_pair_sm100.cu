@@ -422,6 +422,29 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                                        mb * kPairM + static_cast<int>(rank) * kRows);
               tma_store_commit();
             }
+            if (p.n_extra > 0) {
+              // The same 128 x 64 piece to every further copy of C (peer GPUs'
+              // memory when the column blocks are being gathered): the four warps
+              // read the staging tile back, un-swizzled, and write whole 128-byte
+              // rows -- a warp covers four rows per store instruction.  Plain
+              // stores; they drain over NVLink while the next tile is computed.
+              const int et = row_in_tile;            // 0..127
+              const int chunk = et & 7;              // 16-byte chunk of the 128-byte row
+              const int col = n_tile0 + n_off + c + chunk * 8;
+              if (col < p.N) {
+#pragma unroll 1
+                for (int i = 0; i < 8; ++i) {
+                  const int r = (et >> 3) + 16 * i;  // row of the staging tile
+                  const int gm = mb * kPairM + static_cast<int>(rank) * kRows + r;
+                  if (gm >= p.M)
+                    break;
+                  const uint4 v = *reinterpret_cast<const uint4 *>(buf + r * (kStoreCols * 2) + ((chunk ^ (r & 7)) << 4));
+                  const long long off = static_cast<long long>(gm) * p.stride_m + col;
+                  for (int x = 0; x < p.n_extra; ++x)
+                    *reinterpret_cast<uint4 *>(reinterpret_cast<T *>(p.extra_c[x]) + off) = v;
+                }
+              }
+            }
           }
           if (c < width) {
             // Tile widths that are not a multiple of 64 leave 32 columns: per-thread stores.
@@ -437,6 +460,20 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             for (int j = 0; j < 32; ++j)
               v[j] = __uint_as_float(r[j]);
             store_row_chunk<T, 32>(p, m, n_tile0 + n_off + c, v);
+            if (p.n_extra > 0 && m < p.M) {
+              T tmp[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                store_elem(&tmp[j], v[j]);
+              const int col = n_tile0 + n_off + c;
+              const long long off = static_cast<long long>(m) * p.stride_m + col;
+              for (int x = 0; x < p.n_extra; ++x)
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                  if (col + 8 * q < p.N)
+                    reinterpret_cast<uint4 *>(reinterpret_cast<T *>(p.extra_c[x]) + off)[q] =
+                        reinterpret_cast<const uint4 *>(tmp)[q];
+            }
           }
           if (++acc == 2) {
             acc = 0;

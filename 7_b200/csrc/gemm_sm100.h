@@ -34,6 +34,13 @@ struct GemmParams {
   int c_tma; // whole tiles leave through TMA stores (row-major 16-bit C, tiles of at least 64 columns)
   // L2 eviction hints on the operand loads: 0 none, 1 A "evict last" + B "evict first", 2 A "evict last" only
   int l2_hints;
+  // CTA-pair kernel, TMA-store epilogue: every finished 128 x 64 piece of C is
+  // also written, with plain 16-byte stores from the staging tile, to the same
+  // place in `n_extra` further buffers (other GPUs' copies of C, mapped into
+  // this process: the all-gather of the column blocks happens tile by tile
+  // while the kernel computes).  Same strides as C.
+  int n_extra;
+  void *extra_c[7];
   // Test builds only (-DWAVE_WAIT_TEST): the one-CTA kernel's producer leaves out
   // the last K step of every segment, so that the UMMA thread's wait for it runs
   // out and the bounded-wait unwind can be observed.  Always 0 in the product.

@@ -664,8 +664,36 @@ int wave_cuda_gemm_plan(const wave_gemm_desc *d, int *tile_m, int *tile_n, int *
   return WAVE_OK;
 }
 
+} // extern "C"
+
+namespace {
+int gemm_launch(const wave_gemm_desc *d, const void *A, const void *B, void *C, void *workspace, void *stream,
+                void *const *extra_c, int n_extra);
+}
+
+extern "C" {
+
 int wave_cuda_gemm(const wave_gemm_desc *d, const void *A, const void *B, void *C, void *workspace,
                    void *stream) {
+  return gemm_launch(d, A, B, C, workspace, stream, nullptr, 0);
+}
+
+int wave_cuda_gemm_multi_output(const wave_gemm_desc *d, const void *A, const void *B, void *const *C_targets,
+                                int n_targets, void *stream) {
+  if (!C_targets || n_targets < 1 || n_targets > 8)
+    return fail(WAVE_E_INVALID, "n_targets must be between 1 and 8; got %d", n_targets);
+  for (int i = 0; i < n_targets; ++i)
+    if (!C_targets[i] || (reinterpret_cast<uintptr_t>(C_targets[i]) & 15))
+      return fail(WAVE_E_INVALID, "every output target must be a non-null, 16-byte aligned device pointer");
+  return gemm_launch(d, A, B, C_targets[0], nullptr, stream, C_targets + 1, n_targets - 1);
+}
+
+} // extern "C"
+
+namespace {
+
+int gemm_launch(const wave_gemm_desc *d, const void *A, const void *B, void *C, void *workspace, void *stream,
+                void *const *extra_c, int n_extra) {
   int rc = wave_cuda_gemm_validate(d);
   if (rc != WAVE_OK)
     return rc;
@@ -778,16 +806,22 @@ int wave_cuda_gemm(const wave_gemm_desc *d, const void *A, const void *B, void *
       return rc;
     p.c_tma = 1;
   }
+  if (n_extra > 0) {
+    // Further copies of C are written from the TMA-store epilogue of the CTA-pair kernel only.
+    if (!plan.pair || !p.c_tma || plan.streamk_workers > 0)
+      return fail(WAVE_E_UNSUPPORTED,
+                  "several output targets need the CTA-pair kernel's TMA-store epilogue: 16-bit C, row-major or "
+                  "column-major, M and N of at least 256 and tiling knobs asking for 256 x 256 tiles");
+    p.n_extra = n_extra;
+    for (int i = 0; i < n_extra; ++i)
+      p.extra_c[i] = extra_c[i];
+  }
   cudaError_t err = plan.pair ? wave::launch_gemm_pair(ta, tb, tbh, tc, p, plan.tile_n, plan.grid, static_cast<cudaStream_t>(stream))
                               : wave::launch_gemm(ta, tb, tc, p, plan.tile_n, plan.grid, static_cast<cudaStream_t>(stream));
   if (err != cudaSuccess)
     return cuda_fail(err, "gemm launch");
   return WAVE_OK;
 }
-
-} // extern "C"
-
-namespace {
 
 // Host-buffer GEMM.  `A` is a host pointer, or with `a_on_device` a device
 // pointer whose contents are ready on `stream` (a rank of a sharded problem

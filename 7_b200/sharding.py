@@ -82,3 +82,35 @@ def sharded_gemm_host(wc, desc_shard, a_full_dev, a_host, b_host_shard, c_host_s
     gather_replicated_rows(a_full_dev, a_host, dist, rank, world, group)
     wc.gemm_host_a_resident(desc_shard, a_full_dev.data_ptr(), b_host_shard.data_ptr(), c_host_shard.data_ptr(),
                             stream)
+
+
+class PeerMappedOutput:
+    """Every rank's copy of a full output tensor, allocated so that each rank
+    can address all of them (torch's symmetric memory: the ranks' buffers are
+    mapped into one another's address space over NVLink).  It is what
+    wave_cuda_gemm_multi_output writes the column blocks into: rank r passes
+    `block_targets(r, offset)` -- the place of ITS block inside every rank's
+    copy, its own copy first -- and the all-gather happens inside the GEMM
+    kernel.  `settle(stream_tensor)` is the barrier after which a rank may read
+    its copy: a one-element all-reduce ordered on the current stream behind the
+    kernel (no host synchronisation)."""
+
+    def __init__(self, shape, dtype, dist, rank: int, world: int, device=None):
+        import torch
+        import torch.distributed._symmetric_memory as symm
+        self.dist, self.rank, self.world = dist, rank, world
+        self.local = symm.empty(*tuple(shape), dtype=dtype,
+                                device=device or torch.device("cuda", torch.cuda.current_device()))
+        self.handle = symm.rendezvous(self.local, dist.group.WORLD)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        if len(self.ptrs) != world or self.ptrs[rank] != self.local.data_ptr():
+            raise RuntimeError("symmetric memory returned an unexpected set of buffer addresses")
+        self._token = torch.zeros(1, device=self.local.device, dtype=torch.float32)
+
+    def block_targets(self, offset_bytes: int) -> list[int]:
+        """Addresses `offset_bytes` into every rank's copy, this rank's first."""
+        order = [self.rank] + [r for r in range(self.world) if r != self.rank]
+        return [self.ptrs[r] + offset_bytes for r in order]
+
+    def settle(self) -> None:
+        self.dist.all_reduce(self._token)

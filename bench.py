@@ -48,7 +48,7 @@ NVLINK_PEER_GBS = 770.0  # measured peer copy per direction on this pool (nomina
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the single-GPU
 # workload from one ncu capture of the same kernel (summaries under
 # profiles/, each captured at the workload's full size).
-NCU_TRAFFIC_BYTES = {"gemm": 1203.57e6, "fa": None, "skinny": 477.11e6, "fa_published": 1055.49e6}
+NCU_TRAFFIC_BYTES = {"gemm": 1167.68e6, "fa": 2135.65e6, "skinny": 477.11e6, "fa_published": 1055.49e6}
 
 WORKLOADS = {
     "gemm": dict(name="gemm_bf16_8192x8192x8192_f32acc_bf16out", M=8192, N=8192, K=8192),
@@ -397,6 +397,55 @@ def time_gather(torch, sh, work, dist, stream, world) -> tuple[dict, object]:
             "frac_of_nvlink_peer_copy": recv_gbs / NVLINK_PEER_GBS, "nvlink_peer_copy_gbs": NVLINK_PEER_GBS}, full
 
 
+def time_fused_gather(torch, wc, sh, work, dist, stream, rank, world, oracle) -> dict:
+    """The all-gather fused into the GEMM: every rank writes its column block
+    straight into every rank's copy of the full C (peer-mapped memory, plain
+    stores out of the epilogue, tile by tile while the next tile is computed),
+    followed by a one-element all-reduce as the barrier after which the copies
+    may be read.  Timed as one step, max over ranks; rank 0's copy is then
+    checked against the oracle on rows that span every rank's columns."""
+    try:
+        out = sh.PeerMappedOutput((work.N, work.M), torch.bfloat16, dist, rank, world)
+    except Exception as err:  # no symmetric memory on this system: say so, the NCCL gather stands
+        return {"unavailable": f"{type(err).__name__}: {err}"[:300]}
+    out.local.fill_(float("nan"))
+    torch.cuda.synchronize()
+    dist.barrier()
+    targets = out.block_targets(work.n0 * work.M * 2)
+    desc = wc.gemm_desc(work.M, work.nl, work.K, in_type=wc.BF16, out_type=wc.BF16, out_layout=wc.COL_MAJOR,
+                        streamk_workers=1, bm=4, bn=4, wave_m_tiles=4, wave_n_tiles=4)
+
+    def step():
+        wc.gemm_multi_output(desc, work.a.data_ptr(), work.b.data_ptr(), targets, stream.cuda_stream)
+        out.settle()
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    iters = 20
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(iters):
+        step()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    wc.check_device_status()
+    t = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    res = {"kernel": "wave_cuda_gemm_multi_output: the column block written to every rank's C from the GEMM epilogue "
+                     "over NVLink (peer-mapped memory, plain stores), then a one-element all-reduce as barrier",
+           "ms_per_step": ms, "tflops": work.flops / (ms * 1e-3) / 1e12, "launches": iters + 3,
+           "bytes_sent_per_rank": (world - 1) * work.nl * work.M * 2,
+           "sent_gbs_per_rank": (world - 1) * work.nl * work.M * 2 / (ms * 1e-3) / 1e9}
+    if rank == 0:
+        res["parity"] = work.check(oracle, out.local)
+    dist.barrier()
+    del out
+    return res
+
+
 def sustained_leg(torch, work, stream, sampler, seconds, pk) -> dict:
     """Back-to-back launches for about `seconds` (the power-capped regime a
     short burst never reaches), with the SM clock sampled meanwhile."""
@@ -639,6 +688,12 @@ def measure_workload(torch, wc, sh, workload, rank, world, strong, steps, warmup
         oracle.build()
         res["parity"] = work.check(oracle, gathered)
     del gathered
+    if sharded and want_gather and work.kind == "gemm":
+        res["fused_gather"] = time_fused_gather(torch, wc, sh, work, dist, stream, rank, world, oracle)
+        counters["launches"] += res["fused_gather"].get("launches", 0)
+        if "ms_per_step" in res["fused_gather"]:  # compute + NCCL gather against the fused kernel
+            res["fused_gather"]["speedup_over_compute_plus_nccl_gather"] = \
+                res["ms_per_step_with_gather"] / res["fused_gather"]["ms_per_step"]
 
     # end to end: host buffers in, host buffers out
     work.prepare_host()
@@ -767,6 +822,7 @@ def main() -> None:
             "gpu_launches": counters["launches"], "clocks": main_res.get("clocks"),
             "parity_worst_over_tolerance": main_res["parity"]["worst_over_tolerance"], "parity": main_res["parity"],
             "gather": main_res.get("gather"), "value_with_gather": main_res.get("tflops_with_gather"),
+            "fused_gather": main_res.get("fused_gather"),
             "sustained": main_res.get("sustained"), "vs_cublas": main_res.get("vs_cublas"), "also": also or None,
         }
         print(json.dumps(line), flush=True)

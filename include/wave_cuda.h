@@ -134,6 +134,25 @@ int wave_cuda_gemm_workspace_bytes(const wave_gemm_desc *desc, size_t *scratch_b
 int wave_cuda_gemm(const wave_gemm_desc *desc, const void *A, const void *B, void *C, void *workspace,
                    void *stream);
 
+/* No counterpart in the reference, which is single-device.  The GEMM with its
+ * result written to several buffers at once: C_targets[0] exactly as
+ * wave_cuda_gemm writes C, and every finished 128 x 64 piece of it also, with
+ * plain 16-byte stores out of the epilogue's staging tile, to
+ * C_targets[1 .. n_targets-1] at the same offsets and leading dimension.  This
+ * is the all-gather of an N-column-sharded GEMM fused into the kernel: rank r
+ * of a job whose ranks hold peer-mapped copies of the full C (column-major:
+ * rank r's block starts n_begin * ldc elements in) passes the address of ITS
+ * block inside every rank's copy, its own first, and the blocks travel over
+ * NVLink tile by tile while the tensor cores work on the next tile, instead of
+ * in a collective after the kernel.  The stores are complete when the kernel
+ * is; another GPU may read its copy once it has synchronised with this stream
+ * (a barrier across the ranks).  1 <= n_targets <= 8.  Needs the CTA-pair
+ * kernel's TMA-store epilogue: 16-bit C, row- or column-major, M and N of at
+ * least 256, tiling knobs asking for 256 x 256 tiles; otherwise
+ * WAVE_E_UNSUPPORTED.  Uses no workspace. */
+int wave_cuda_gemm_multi_output(const wave_gemm_desc *desc, const void *A, const void *B, void *const *C_targets,
+                                int n_targets, void *stream);
+
 /* Host-buffer form (what the mlir-runner host main does with host-registered
  * memrefs, wave_matmul.py:6926-6937): copies A and B to the device, runs,
  * copies C back, all on `stream`, then synchronises it.  Device staging

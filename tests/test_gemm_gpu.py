@@ -444,6 +444,54 @@ def test_host_buffer_call_with_device_resident_a(cuda, wc, oracle, pkg, M, N, K)
     assert np.array_equal(got, expected(oracle, a, b, "bf16", "bf16"))
 
 
+@pytest.mark.parametrize("M,N,K,out_name,layout,ldc,width", [
+    (512, 768, 256, "bf16", "row-major", 0, 0),
+    (1024, 512, 320, "bf16", "column-major", 0, 0),       # computed as C^T
+    (2048, 512, 128, "f16", "column-major", 2304, 0),     # a column block inside a wider C
+    (400, 464, 208, "f16", "row-major", 0, 0),            # ragged edges: the copies clip like the TMA store
+    (768, 1024, 192, "bf16", "row-major", 0, 224),        # 224-column tiles: the 32-column remainder chunk
+])
+def test_multi_output_writes_every_target(cuda, wc, oracle, M, N, K, out_name, layout, ldc, width):
+    """wave_cuda_gemm_multi_output: the result lands in every target buffer (on
+    one GPU: three local buffers stand in for peer GPUs' copies of C), bit for
+    bit what wave_cuda_gemm writes, and nothing outside the block is touched."""
+    in_name = "f16" if out_name == "f16" else "bf16"
+    a_bits, b_bits = lcg_inputs(oracle, M, N, K, in_name, seed=M + 3)
+    knobs = PAIR_KNOBS if M % 256 == 0 and N % 256 == 0 else dict(bm=1, bn=1, wave_m_tiles=M // 16, wave_n_tiles=N // 16)
+    desc = wc.gemm_desc(M, N, K, in_type=wc.TYPE_BY_NAME[in_name], out_type=wc.TYPE_BY_NAME[out_name],
+                        out_layout=wc.LAYOUT_BY_NAME[layout], ldc=ldc, **knobs)
+    a, b = to_device_bits(cuda, a_bits), to_device_bits(cuda, b_bits)
+    ld = ldc or (N if layout == "row-major" else M)
+    outer = M if layout == "row-major" else N
+    inner = N if layout == "row-major" else M
+    targets = [device_out(cuda, ld * outer, out_name) for _ in range(3)]
+    env = dict(WAVE_CUDA_GEMM_KERNEL="pair")
+    if width:
+        env["WAVE_CUDA_GEMM_PAIR_TILE_N"] = width
+    with env_knobs(wc, **env):
+        wc.gemm_multi_output(desc, a.data_ptr(), b.data_ptr(), [t.data_ptr() for t in targets],
+                             cuda.cuda.current_stream().cuda_stream)
+    wc.check_device_status()
+    want = expected(oracle, a_bits, b_bits, in_name, out_name)
+    for t in targets:
+        full = out_to_f32(cuda, t).reshape(outer, ld)
+        got = full[:, :inner] if layout == "row-major" else full[:, :inner].T
+        assert np.array_equal(got, want), f"max abs diff {np.nanmax(np.abs(got - want))}"
+        assert np.isnan(full[:, inner:]).all()
+
+
+def test_multi_output_refuses_what_it_cannot_do(cuda, wc):
+    x = cuda.zeros(256 * 256, dtype=cuda.float16, device="cuda")
+    c = cuda.zeros(256 * 256, dtype=cuda.float32, device="cuda")
+    with pytest.raises(wc.WaveCudaError) as err:  # f32 output has no TMA-store epilogue
+        wc.gemm_multi_output(wc.gemm_desc(256, 256, 256, **PAIR_KNOBS), x.data_ptr(), x.data_ptr(),
+                             [c.data_ptr(), c.data_ptr()])
+    assert err.value.code == wc.E_UNSUPPORTED
+    with pytest.raises(wc.WaveCudaError) as err:
+        wc.gemm_multi_output(wc.gemm_desc(256, 256, 256, out_type=wc.F16, **PAIR_KNOBS), x.data_ptr(), x.data_ptr(), [])
+    assert err.value.code == wc.E_INVALID
+
+
 def test_name_based_launch_facade(cuda, wc, oracle):
     """Same call shape as the reference runner: look a kernel up by name, then
     launch with an array of pointers to the argument values
