@@ -440,8 +440,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     break;
                   const uint4 v = *reinterpret_cast<const uint4 *>(buf + r * (kStoreCols * 2) + ((chunk ^ (r & 7)) << 4));
                   const long long off = static_cast<long long>(gm) * p.stride_m + col;
-                  for (int x = 0; x < p.n_extra; ++x)
-                    *reinterpret_cast<uint4 *>(reinterpret_cast<T *>(p.extra_c[x]) + off) = v;
+                  if (p.extra_multimem)
+                    multimem_st_16B(reinterpret_cast<T *>(p.extra_c[0]) + off, v);
+                  else
+                    for (int x = 0; x < p.n_extra; ++x)
+                      *reinterpret_cast<uint4 *>(reinterpret_cast<T *>(p.extra_c[x]) + off) = v;
                 }
               }
             }
@@ -470,9 +473,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               for (int x = 0; x < p.n_extra; ++x)
 #pragma unroll
                 for (int q = 0; q < 4; ++q)
-                  if (col + 8 * q < p.N)
-                    reinterpret_cast<uint4 *>(reinterpret_cast<T *>(p.extra_c[x]) + off)[q] =
-                        reinterpret_cast<const uint4 *>(tmp)[q];
+                  if (col + 8 * q < p.N) {
+                    uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<T *>(p.extra_c[x]) + off) + q;
+                    if (p.extra_multimem)
+                      multimem_st_16B(dst, reinterpret_cast<const uint4 *>(tmp)[q]);
+                    else
+                      *dst = reinterpret_cast<const uint4 *>(tmp)[q];
+                  }
             }
           }
           if (++acc == 2) {

@@ -41,6 +41,9 @@ struct GemmParams {
   // while the kernel computes).  Same strides as C.
   int n_extra;
   void *extra_c[7];
+  // extra_c[0] is an NVLink multicast address (one store reaches every GPU bound
+  // to the multicast object, replicated in the switch): written with multimem.st.
+  int extra_multimem;
   // Test builds only (-DWAVE_WAIT_TEST): the one-CTA kernel's producer leaves out
   // the last K step of every segment, so that the UMMA thread's wait for it runs
   // out and the bounded-wait unwind can be observed.  Always 0 in the product.

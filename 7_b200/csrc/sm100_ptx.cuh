@@ -434,6 +434,15 @@ __device__ __forceinline__ void umma_ss_pair(uint32_t tmem_d, uint64_t desc_a, u
                : "memory");
 }
 
+// 16-byte store to an NVLink multicast address: the switch delivers it to the
+// same offset in every GPU's memory bound to the multicast object.  The bits
+// travel unchanged (a store, not a reduction).
+__device__ __forceinline__ void multimem_st_16B(void *mc_addr, const uint4 &v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(__uint_as_float(v.x)),
+               "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+               : "memory");
+}
+
 // Burn a bounded amount of time (used only on the abort path so that copies
 // already in flight can land before the CTA leaves).
 __device__ __forceinline__ void bounded_delay(long long cycles) {

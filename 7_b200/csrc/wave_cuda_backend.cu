@@ -668,7 +668,7 @@ int wave_cuda_gemm_plan(const wave_gemm_desc *d, int *tile_m, int *tile_n, int *
 
 namespace {
 int gemm_launch(const wave_gemm_desc *d, const void *A, const void *B, void *C, void *workspace, void *stream,
-                void *const *extra_c, int n_extra);
+                void *const *extra_c, int n_extra, bool extra_multimem = false);
 }
 
 extern "C" {
@@ -688,12 +688,20 @@ int wave_cuda_gemm_multi_output(const wave_gemm_desc *d, const void *A, const vo
   return gemm_launch(d, A, B, C_targets[0], nullptr, stream, C_targets + 1, n_targets - 1);
 }
 
+int wave_cuda_gemm_multicast_output(const wave_gemm_desc *d, const void *A, const void *B, void *C_local,
+                                    void *C_multicast, void *stream) {
+  if (!C_multicast || (reinterpret_cast<uintptr_t>(C_multicast) & 15))
+    return fail(WAVE_E_INVALID, "the multicast target must be a non-null, 16-byte aligned address");
+  void *const extra[1] = {C_multicast};
+  return gemm_launch(d, A, B, C_local, nullptr, stream, extra, 1, true);
+}
+
 } // extern "C"
 
 namespace {
 
 int gemm_launch(const wave_gemm_desc *d, const void *A, const void *B, void *C, void *workspace, void *stream,
-                void *const *extra_c, int n_extra) {
+                void *const *extra_c, int n_extra, bool extra_multimem) {
   int rc = wave_cuda_gemm_validate(d);
   if (rc != WAVE_OK)
     return rc;
@@ -813,6 +821,7 @@ int gemm_launch(const wave_gemm_desc *d, const void *A, const void *B, void *C, 
                   "several output targets need the CTA-pair kernel's TMA-store epilogue: 16-bit C, row-major or "
                   "column-major, M and N of at least 256 and tiling knobs asking for 256 x 256 tiles");
     p.n_extra = n_extra;
+    p.extra_multimem = extra_multimem ? 1 : 0;
     for (int i = 0; i < n_extra; ++i)
       p.extra_c[i] = extra_c[i];
   }

@@ -105,6 +105,8 @@ class PeerMappedOutput:
         self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
         if len(self.ptrs) != world or self.ptrs[rank] != self.local.data_ptr():
             raise RuntimeError("symmetric memory returned an unexpected set of buffer addresses")
+        # 0 where the system has no NVLink multicast (NVLS) for this group
+        self.multicast_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0)
         self._token = torch.zeros(1, device=self.local.device, dtype=torch.float32)
 
     def block_targets(self, offset_bytes: int) -> list[int]:

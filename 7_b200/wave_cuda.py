@@ -49,7 +49,8 @@ EXPORTS = [
     "_mlir_ciface_wave_memref_to_ptr_global_bf16", "_mlir_ciface_wave_memref_to_ptr_global_i64",
     "_mlir_ciface_wave_memref_to_ptr_global_f64",
     "wave_cuda_gemm_desc_init", "wave_cuda_gemm_validate", "wave_cuda_gemm_workspace_bytes", "wave_cuda_gemm",
-    "wave_cuda_gemm_host", "wave_cuda_gemm_host_a_resident", "wave_cuda_gemm_multi_output", "wave_cuda_gemm_plan", "wave_cuda_gemm_streamk_static", "wave_cuda_fa_validate", "wave_cuda_flash_attention_fwd",
+    "wave_cuda_gemm_host", "wave_cuda_gemm_host_a_resident", "wave_cuda_gemm_multi_output", "wave_cuda_gemm_multicast_output",
+    "wave_cuda_gemm_plan", "wave_cuda_gemm_streamk_static", "wave_cuda_fa_validate", "wave_cuda_flash_attention_fwd",
     "wave_cuda_flash_attention_fwd_host", "wave_cuda_module_get_function", "wave_cuda_launch",
     "wave_cuda_function_release", "wave_cuda_check_device_status",
     # include/wave_mgpu.h: the wrappers a host module lowered by gpu-to-llvm calls
@@ -90,6 +91,7 @@ def lib() -> C.CDLL:
     L.wave_cuda_gemm_host.argtypes = [C.POINTER(GemmDesc), vp, vp, vp, vp]
     L.wave_cuda_gemm_host_a_resident.argtypes = [C.POINTER(GemmDesc), vp, vp, vp, vp]
     L.wave_cuda_gemm_multi_output.argtypes = [C.POINTER(GemmDesc), vp, vp, C.POINTER(vp), C.c_int, vp]
+    L.wave_cuda_gemm_multicast_output.argtypes = [C.POINTER(GemmDesc), vp, vp, vp, vp, vp]
     L.wave_cuda_gemm_streamk_static.argtypes = [C.POINTER(GemmDesc), vp, vp, vp, vp]
     L.wave_cuda_gemm_plan.argtypes = [C.POINTER(GemmDesc), ip, ip, ip, ip, ip]
     L.wave_cuda_fa_validate.argtypes = [C.POINTER(FaDesc)]
@@ -192,6 +194,14 @@ def gemm_multi_output(desc: GemmDesc, a_ptr: int, b_ptr: int, c_ptrs, stream: in
     column-sharded GEMM when the others are peer GPUs' copies of C."""
     arr = (C.c_void_p * len(c_ptrs))(*c_ptrs)
     check(lib().wave_cuda_gemm_multi_output(C.byref(desc), a_ptr, b_ptr, arr, len(c_ptrs), stream or None))
+
+
+def gemm_multicast_output(desc: GemmDesc, a_ptr: int, b_ptr: int, c_local_ptr: int, c_multicast_ptr: int,
+                          stream: int = 0) -> None:
+    """The GEMM with C also written through an NVLink multicast address (NVLS): every GPU bound to
+    the multicast object receives each finished tile."""
+    check(lib().wave_cuda_gemm_multicast_output(C.byref(desc), a_ptr, b_ptr, c_local_ptr, c_multicast_ptr,
+                                                stream or None))
 
 
 def gemm_host_a_resident(desc: GemmDesc, a_dev_ptr: int, b_ptr: int, c_ptr: int, stream: int = 0) -> None:

@@ -408,40 +408,58 @@ def time_fused_gather(torch, wc, sh, work, dist, stream, rank, world, oracle) ->
         out = sh.PeerMappedOutput((work.N, work.M), torch.bfloat16, dist, rank, world)
     except Exception as err:  # no symmetric memory on this system: say so, the NCCL gather stands
         return {"unavailable": f"{type(err).__name__}: {err}"[:300]}
-    out.local.fill_(float("nan"))
-    torch.cuda.synchronize()
-    dist.barrier()
     targets = out.block_targets(work.n0 * work.M * 2)
     desc = wc.gemm_desc(work.M, work.nl, work.K, in_type=wc.BF16, out_type=wc.BF16, out_layout=wc.COL_MAJOR,
                         streamk_workers=1, bm=4, bn=4, wave_m_tiles=4, wave_n_tiles=4)
 
-    def step():
+    offset = work.n0 * work.M * 2
+    iters = 20
+
+    def timed(step):
+        out.local.fill_(float("nan"))
+        torch.cuda.synchronize()
+        dist.barrier()
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(iters):
+            step()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        wc.check_device_status()
+        t = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        entry = {"ms_per_step": ms, "tflops": work.flops / (ms * 1e-3) / 1e12}
+        if rank == 0:
+            entry["parity"] = work.check(oracle, out.local)
+        dist.barrier()
+        return entry
+
+    def unicast():
         wc.gemm_multi_output(desc, work.a.data_ptr(), work.b.data_ptr(), targets, stream.cuda_stream)
         out.settle()
-    for _ in range(3):
-        step()
-    torch.cuda.synchronize()
-    dist.barrier()
-    torch.cuda.synchronize()
-    iters = 20
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for _ in range(iters):
-        step()
-    e1.record(stream)
-    torch.cuda.synchronize()
-    wc.check_device_status()
-    t = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda", dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
-    res = {"kernel": "wave_cuda_gemm_multi_output: the column block written to every rank's C from the GEMM epilogue "
-                     "over NVLink (peer-mapped memory, plain stores), then a one-element all-reduce as barrier",
-           "ms_per_step": ms, "tflops": work.flops / (ms * 1e-3) / 1e12, "launches": iters + 3,
-           "bytes_sent_per_rank": (world - 1) * work.nl * work.M * 2,
-           "sent_gbs_per_rank": (world - 1) * work.nl * work.M * 2 / (ms * 1e-3) / 1e9}
-    if rank == 0:
-        res["parity"] = work.check(oracle, out.local)
-    dist.barrier()
+
+    def multicast():
+        wc.gemm_multicast_output(desc, work.a.data_ptr(), work.b.data_ptr(), out.ptrs[rank] + offset,
+                                 out.multicast_ptr + offset, stream.cuda_stream)
+        out.settle()
+    res = timed(unicast)
+    res.update({"kernel": "wave_cuda_gemm_multi_output: the column block written to every rank's C from the GEMM "
+                          "epilogue over NVLink (peer-mapped memory, plain stores), then a one-element all-reduce as barrier",
+                "launches": 2 * (iters + 3), "bytes_sent_per_rank": (world - 1) * work.nl * work.M * 2,
+                "sent_gbs_per_rank": (world - 1) * work.nl * work.M * 2 / (res["ms_per_step"] * 1e-3) / 1e9})
+    if out.multicast_ptr:
+        res["multicast"] = timed(multicast)
+        res["multicast"]["kernel"] = ("wave_cuda_gemm_multicast_output: every tile stored once to an NVLink multicast "
+                                      "address (multimem.st), replicated to all ranks in the switch")
+        res["multicast"]["bytes_sent_per_rank"] = work.nl * work.M * 2
+    else:
+        res["multicast"] = {"unavailable": "the symmetric-memory handle has no multicast address (no NVLS for this group)"}
     del out
     return res
 
@@ -691,9 +709,12 @@ def measure_workload(torch, wc, sh, workload, rank, world, strong, steps, warmup
     if sharded and want_gather and work.kind == "gemm":
         res["fused_gather"] = time_fused_gather(torch, wc, sh, work, dist, stream, rank, world, oracle)
         counters["launches"] += res["fused_gather"].get("launches", 0)
-        if "ms_per_step" in res["fused_gather"]:  # compute + NCCL gather against the fused kernel
-            res["fused_gather"]["speedup_over_compute_plus_nccl_gather"] = \
-                res["ms_per_step_with_gather"] / res["fused_gather"]["ms_per_step"]
+        if "ms_per_step" in res["fused_gather"]:  # compute + NCCL gather against the fused kernels
+            fg = res["fused_gather"]
+            fg["speedup_over_compute_plus_nccl_gather"] = res["ms_per_step_with_gather"] / fg["ms_per_step"]
+            if "ms_per_step" in fg.get("multicast", {}):
+                fg["multicast"]["speedup_over_compute_plus_nccl_gather"] = \
+                    res["ms_per_step_with_gather"] / fg["multicast"]["ms_per_step"]
 
     # end to end: host buffers in, host buffers out
     work.prepare_host()

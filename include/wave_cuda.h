@@ -153,6 +153,16 @@ int wave_cuda_gemm(const wave_gemm_desc *desc, const void *A, const void *B, voi
 int wave_cuda_gemm_multi_output(const wave_gemm_desc *desc, const void *A, const void *B, void *const *C_targets,
                                 int n_targets, void *stream);
 
+/* The same with the other copies reached through ONE NVLink multicast address
+ * (NVLS): `C_multicast` is the block's place inside a multicast mapping of the
+ * ranks' copies of C (every GPU bound to the multicast object receives each
+ * store, replicated in the switch, this GPU's own copy included), so a tile
+ * leaves the GPU once instead of once per peer.  Written with multimem.st from
+ * the epilogue; `C_local` is written as wave_cuda_gemm writes C.  Same limits
+ * as wave_cuda_gemm_multi_output; no counterpart in the reference. */
+int wave_cuda_gemm_multicast_output(const wave_gemm_desc *desc, const void *A, const void *B, void *C_local,
+                                    void *C_multicast, void *stream);
+
 /* Host-buffer form (what the mlir-runner host main does with host-registered
  * memrefs, wave_matmul.py:6926-6937): copies A and B to the device, runs,
  * copies C back, all on `stream`, then synchronises it.  Device staging
