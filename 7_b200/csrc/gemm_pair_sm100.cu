@@ -320,9 +320,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const int m = mb * kPairM + static_cast<int>(rank) * kRows + row_in_tile;
       if (!whole) {
         // Stream-K partial: this CTA's 128 rows of the raw f32 accumulator go to its
-        // half of the pair's scratch slot, element (row, col) at col*128 + row so
-        // that a warp writes 128 contiguous bytes.  Then the arrival is counted;
-        // the last arriver of this (tile, CTA rank) reduces.
+        // half of the pair's scratch slot.  Then the arrival is counted; the last
+        // arriver of this (tile, CTA rank) reduces.
         const int sk_tile = it.tile - p.dp_tiles;
         const int slot = streamk_slot(total_iters, p.streamk_workers, p.k_iters, pair_id, sk_tile);
         float *mine = p.scratch + ((static_cast<size_t>(pair_id) * 2 + slot) * 2 + rank) * (kRows * PN);
@@ -331,9 +330,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           uint32_t r[32];
           tmem_ld_32x32b_x32(taddr + c, r);
           tmem_ld_wait();
+          // groups of four columns: element (row, col) at ((col / 4) * 128 + row) * 4 + col % 4,
+          // so a warp's 16-byte stores (and the reducer's loads) cover 512 contiguous bytes
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            mine[(c + j) * kRows + row_in_tile] = __uint_as_float(r[j]);
+          for (int k = 0; k < 8; ++k)
+            reinterpret_cast<float4 *>(mine)[((c >> 2) + k) * kRows + row_in_tile] =
+                make_float4(__uint_as_float(r[4 * k]), __uint_as_float(r[4 * k + 1]), __uint_as_float(r[4 * k + 2]),
+                            __uint_as_float(r[4 * k + 3]));
         }
         tc_fence_before_sync();
         __syncwarp();
@@ -361,12 +364,40 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
             for (int j = 0; j < 32; ++j)
               v[j] = 0.0f;
-            for (int owner = first_owner; owner <= last_owner; ++owner) {
-              const int oslot = streamk_slot(total_iters, p.streamk_workers, p.k_iters, owner, sk_tile);
-              const float *src = p.scratch + ((static_cast<size_t>(owner) * 2 + oslot) * 2 + rank) * (kRows * PN);
+            // two owners' partials in flight at a time, added in ascending owner order
+            for (int owner = first_owner; owner <= last_owner; owner += 2) {
+              const bool two = owner + 1 <= last_owner;
+              const int slot0 = streamk_slot(total_iters, p.streamk_workers, p.k_iters, owner, sk_tile);
+              const int slot1 = two ? streamk_slot(total_iters, p.streamk_workers, p.k_iters, owner + 1, sk_tile) : 0;
+              const float4 *src0 = reinterpret_cast<const float4 *>(
+                  p.scratch + ((static_cast<size_t>(owner) * 2 + slot0) * 2 + rank) * (kRows * PN));
+              const float4 *src1 = reinterpret_cast<const float4 *>(
+                  p.scratch + ((static_cast<size_t>(two ? owner + 1 : owner) * 2 + slot1) * 2 + rank) * (kRows * PN));
+              float4 x0[8], x1[8];
 #pragma unroll
-              for (int j = 0; j < 32; ++j)
-                v[j] += __ldcg(&src[(c + j) * kRows + row_in_tile]);
+              for (int k = 0; k < 8; ++k)
+                x0[k] = __ldcg(src0 + ((c >> 2) + k) * kRows + row_in_tile);
+              if (two) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                  x1[k] = __ldcg(src1 + ((c >> 2) + k) * kRows + row_in_tile);
+              }
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                v[4 * k] += x0[k].x;
+                v[4 * k + 1] += x0[k].y;
+                v[4 * k + 2] += x0[k].z;
+                v[4 * k + 3] += x0[k].w;
+              }
+              if (two) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                  v[4 * k] += x1[k].x;
+                  v[4 * k + 1] += x1[k].y;
+                  v[4 * k + 2] += x1[k].z;
+                  v[4 * k + 3] += x1[k].w;
+                }
+              }
             }
             store_row_chunk<T, 32>(p, m, n_tile0 + c, v);
           }

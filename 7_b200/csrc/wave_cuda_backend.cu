@@ -496,8 +496,8 @@ HostPipeline *host_pipeline(DeviceHostState &st) {
 // and copy back in one piece: worth it only when the copies are large, and the
 // block must keep the descriptor's tiling rules valid (a multiple of
 // 16*bn*wave_n_tiles) and fill whole 256-column tiles.
-int host_pipeline_chunk(const wave_gemm_desc &d, size_t copy_bytes) {
-  if (copy_bytes < (64u << 20) || is_tile_packed(d.out_layout) || d.ldc != 0 || d.streamk_workers > 1)
+int host_pipeline_chunk(const wave_gemm_desc &d, size_t copy_bytes, size_t min_bytes = 64u << 20) {
+  if (copy_bytes < min_bytes || is_tile_packed(d.out_layout) || d.ldc != 0 || d.streamk_workers > 1)
     return 0;
   const int unit = 16 * d.bn * d.wave_n_tiles;
   for (int parts : {8, 6, 4, 3, 2}) {
@@ -871,7 +871,10 @@ int gemm_host_impl(const wave_gemm_desc *d, const void *A, bool a_on_device, con
   // being computed, block i+1 of B is on its way to the device and block i-1
   // of C on its way back (PCIe is full duplex), so the call costs about
   // "copy A + copy B" instead of "copy A + copy B + compute + copy C".
-  const int chunk = host_pipeline_chunk(*d, b_bytes + c_bytes);
+  // (With A already on the device -- a rank's block of a sharded problem -- the
+  // copies are smaller and the pipeline pays from 16 MB on: B can start on its
+  // way while the caller's stream is still producing A.)
+  const int chunk = host_pipeline_chunk(*d, b_bytes + c_bytes, a_on_device ? (16u << 20) : (64u << 20));
   if (chunk > 0) {
     HostPipeline *hp = host_pipeline(*state);
     if (!hp)
@@ -892,7 +895,8 @@ int gemm_host_impl(const wave_gemm_desc *d, const void *A, bool a_on_device, con
     if (!failed) {
       check(cudaEventRecord(ev_start, s), "record");
       for (cudaStream_t q : {hp->h2d, hp->compute, hp->d2h})
-        check(cudaStreamWaitEvent(q, ev_start, 0), "order after the caller's stream");
+        if (!(a_on_device && q == hp->h2d)) // B comes from the host: it need not wait for the caller's A
+          check(cudaStreamWaitEvent(q, ev_start, 0), "order after the caller's stream");
       if (!a_on_device)
         check(cudaMemcpyAsync(dev, A_host, a_bytes, cudaMemcpyHostToDevice, hp->h2d), "copy A to device");
       check(cudaEventRecord(ev_a, hp->h2d), "record");
