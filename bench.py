@@ -674,6 +674,10 @@ def measure_workload(torch, wc, sh, workload, rank, world, strong, steps, warmup
     from oracle import oracle
     work = make_work(torch, wc, sh, workload, rank, world, strong)
     sharded = work.strong and world > 1
+    # Every workload starts its timed loop from an idle GPU, like the first one: the legs that ran
+    # before it (sustained loops, the cuBLAS comparison) leave the part at a power-capped clock.
+    torch.cuda.synchronize()
+    time.sleep(1.5)
     ms = time_steps(torch, work, steps, warmup, stream, dist) / steps
     clocks = sampler.window(work.t_begin, work.t_end) if sampler is not None else None
     wc.check_device_status()
