@@ -278,8 +278,13 @@ int snap_tile_n(int want) {
 
 // `sms` <= 0 means "unknown" (no device query): only legal when the
 // descriptor does not ask for automatic Stream-K.
-int make_plan(const wave_gemm_desc &d, int sms, bool have_workspace, GemmPlan *plan) {
-  const wave::EnvKnobs env = wave::env_knobs();
+// `need_pair`: the caller needs the CTA-pair kernel's epilogue (output to
+// several buffers); the size heuristic is then not allowed to pick the
+// one-CTA kernel.
+int make_plan(const wave_gemm_desc &d, int sms, bool have_workspace, GemmPlan *plan, bool need_pair = false) {
+  wave::EnvKnobs env = wave::env_knobs();
+  if (need_pair && env.gemm_kernel != 3)
+    env.gemm_kernel = 2;
   const int tile_m = wave::gemm_tile_m(), tile_k = wave::gemm_tile_k();
   const int want_m = 16 * d.bm * d.wave_m_tiles, want_n = 16 * d.bn * d.wave_n_tiles;
   GemmPlan p{};
@@ -713,7 +718,7 @@ int gemm_launch(const wave_gemm_desc *d, const void *A, const void *B, void *C, 
   if ((rc = sm_count(&sms)) != WAVE_OK)
     return rc;
   GemmPlan plan;
-  if ((rc = make_plan(*d, sms, workspace != nullptr, &plan)) != WAVE_OK)
+  if ((rc = make_plan(*d, sms, workspace != nullptr, &plan, n_extra > 0)) != WAVE_OK)
     return rc;
   if (plan.streamk_workers > 0 && !workspace)
     return fail(WAVE_E_INVALID, "Stream-K with %d workers needs a workspace of %zu + %zu bytes",

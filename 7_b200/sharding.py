@@ -68,7 +68,10 @@ def gather_replicated_rows(a_full_dev, a_host, dist, rank: int, world: int, grou
         raise ValueError(f"M must be a multiple of {16 * world} for an even row exchange; got {m_total}")
     r0, r1 = row_shard(m_total, world, rank)
     a_full_dev[r0:r1].copy_(a_host[r0:r1], non_blocking=True)
-    dist.all_gather_into_tensor(a_full_dev.reshape(-1), a_full_dev[r0:r1].reshape(-1), group=group)
+    # bytes, so that 16-bit patterns held in any torch dtype travel (NCCL has no int16)
+    import torch
+    dist.all_gather_into_tensor(a_full_dev.reshape(-1).view(torch.uint8), a_full_dev[r0:r1].reshape(-1).view(torch.uint8),
+                                group=group)
 
 
 def sharded_gemm_host(wc, desc_shard, a_full_dev, a_host, b_host_shard, c_host_shard, dist, rank: int, world: int,
