@@ -645,6 +645,34 @@ int wave_cuda_gemm_workspace_bytes(const wave_gemm_desc *d, size_t *scratch_byte
   return WAVE_OK;
 }
 
+int wave_cuda_gemm_plan_for_sms(const wave_gemm_desc *d, int sm_count, int have_workspace, int *tile_m, int *tile_n,
+                                int *grid, int *streamk_workers, int *swapped, size_t *scratch_bytes,
+                                size_t *counter_bytes) {
+  int rc = wave_cuda_gemm_validate(d);
+  if (rc != WAVE_OK)
+    return rc;
+  if (sm_count < 2)
+    return fail(WAVE_E_INVALID, "sm_count must be at least 2; got %d", sm_count);
+  GemmPlan plan;
+  if ((rc = make_plan(*d, sm_count, have_workspace != 0, &plan)) != WAVE_OK)
+    return rc;
+  if (tile_m)
+    *tile_m = plan.tile_m;
+  if (tile_n)
+    *tile_n = plan.tile_n;
+  if (grid)
+    *grid = plan.grid;
+  if (streamk_workers)
+    *streamk_workers = plan.streamk_workers;
+  if (swapped)
+    *swapped = plan.swapped ? 1 : 0;
+  if (scratch_bytes)
+    *scratch_bytes = plan.scratch_bytes;
+  if (counter_bytes)
+    *counter_bytes = plan.counter_bytes;
+  return WAVE_OK;
+}
+
 int wave_cuda_gemm_plan(const wave_gemm_desc *d, int *tile_m, int *tile_n, int *grid, int *streamk_workers,
                         int *swapped) {
   int rc = wave_cuda_gemm_validate(d);

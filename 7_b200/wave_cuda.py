@@ -50,7 +50,7 @@ EXPORTS = [
     "_mlir_ciface_wave_memref_to_ptr_global_f64",
     "wave_cuda_gemm_desc_init", "wave_cuda_gemm_validate", "wave_cuda_gemm_workspace_bytes", "wave_cuda_gemm",
     "wave_cuda_gemm_host", "wave_cuda_gemm_host_a_resident", "wave_cuda_gemm_multi_output", "wave_cuda_gemm_multicast_output",
-    "wave_cuda_gemm_plan", "wave_cuda_gemm_streamk_static", "wave_cuda_fa_validate", "wave_cuda_flash_attention_fwd",
+    "wave_cuda_gemm_plan", "wave_cuda_gemm_plan_for_sms", "wave_cuda_gemm_streamk_static", "wave_cuda_fa_validate", "wave_cuda_flash_attention_fwd",
     "wave_cuda_flash_attention_fwd_host", "wave_cuda_module_get_function", "wave_cuda_launch",
     "wave_cuda_function_release", "wave_cuda_check_device_status",
     # include/wave_mgpu.h: the wrappers a host module lowered by gpu-to-llvm calls
@@ -94,6 +94,8 @@ def lib() -> C.CDLL:
     L.wave_cuda_gemm_multicast_output.argtypes = [C.POINTER(GemmDesc), vp, vp, vp, vp, vp]
     L.wave_cuda_gemm_streamk_static.argtypes = [C.POINTER(GemmDesc), vp, vp, vp, vp]
     L.wave_cuda_gemm_plan.argtypes = [C.POINTER(GemmDesc), ip, ip, ip, ip, ip]
+    L.wave_cuda_gemm_plan_for_sms.argtypes = [C.POINTER(GemmDesc), C.c_int, C.c_int, ip, ip, ip, ip, ip,
+                                              C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]
     L.wave_cuda_fa_validate.argtypes = [C.POINTER(FaDesc)]
     L.wave_cuda_flash_attention_fwd.argtypes = [C.POINTER(FaDesc), vp, vp, vp, vp, vp, vp]
     L.wave_cuda_flash_attention_fwd_host.argtypes = [C.POINTER(FaDesc), vp, vp, vp, vp, vp]
@@ -169,6 +171,16 @@ def gemm_plan(desc: GemmDesc) -> dict:
     check(lib().wave_cuda_gemm_plan(C.byref(desc), *[C.byref(x) for x in v]))
     return dict(tile_m=v[0].value, tile_n=v[1].value, grid=v[2].value, streamk_workers=v[3].value,
                 swapped=bool(v[4].value))
+
+
+def gemm_plan_for_sms(desc: GemmDesc, sm_count: int, have_workspace: bool = True) -> dict:
+    """The launch the backend would choose on a GPU of `sm_count` SMs (no device needed)."""
+    v = [C.c_int(0) for _ in range(5)]
+    s, c = C.c_size_t(0), C.c_size_t(0)
+    check(lib().wave_cuda_gemm_plan_for_sms(C.byref(desc), sm_count, int(have_workspace), *[C.byref(x) for x in v],
+                                            C.byref(s), C.byref(c)))
+    return dict(tile_m=v[0].value, tile_n=v[1].value, grid=v[2].value, streamk_workers=v[3].value,
+                swapped=bool(v[4].value), scratch_bytes=s.value, counter_bytes=c.value)
 
 
 def gemm(desc: GemmDesc, a_ptr: int, b_ptr: int, c_ptr: int, workspace_ptr: int = 0, stream: int = 0) -> None:

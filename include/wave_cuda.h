@@ -204,6 +204,13 @@ int wave_cuda_gemm_streamk_static(const wave_gemm_desc *desc, const void *A, con
 int wave_cuda_gemm_plan(const wave_gemm_desc *desc, int *tile_m, int *tile_n, int *grid, int *streamk_workers,
                         int *swapped);
 
+/* The same for a GPU of `sm_count` SMs that need not be present (no device is
+ * asked for anything): what the backend would launch there, with or without a
+ * workspace, and the workspace it would want.  For planning tools and tests. */
+int wave_cuda_gemm_plan_for_sms(const wave_gemm_desc *desc, int sm_count, int have_workspace, int *tile_m, int *tile_n,
+                                int *grid, int *streamk_workers, int *swapped, size_t *scratch_bytes,
+                                size_t *counter_bytes);
+
 /* ---- flash-attention forward ------------------------------------------- *
  * O = softmax(scale * Q K^T [+ causal mask]) V per (batch, head).  Layout
  * (B, H, S, D) contiguous, the same bytes as the gfx950 runner's [B*H][S][D]

@@ -186,3 +186,73 @@ def test_memref_region_with_any_strides(wc):
     assert region(3, [0, 8], [8, 1], 2) == (6, 0)                # empty
     assert region(7, [], [], 8) == (56, 8)                       # rank 0: one element
     assert lib.wave_cuda_memref_region(1, None, 4, None, None) == wc.E_INVALID
+
+
+PAIR = dict(bm=4, bn=4, wave_m_tiles=4, wave_n_tiles=4)
+
+
+@pytest.mark.parametrize("shape,kwargs,sms,workspace,want", [
+    # the benchmark's GEMM and its N-column shards on a 148-SM part (column-major C runs as C^T: swapped)
+    ((8192, 8192, 8192), dict(in_type=1, out_type=1, out_layout=1, streamk_workers=0, **PAIR), 148, True,
+     dict(tile_m=256, tile_n=256, grid=148, streamk_workers=0, swapped=True)),
+    ((8192, 4096, 8192), dict(in_type=1, out_type=1, out_layout=1, streamk_workers=0, **PAIR), 148, True,
+     dict(tile_m=256, tile_n=256, grid=148, streamk_workers=0, swapped=True)),
+    ((8192, 2048, 8192), dict(in_type=1, out_type=1, out_layout=1, streamk_workers=0, **PAIR), 148, True,
+     dict(tile_m=256, tile_n=256, streamk_workers=0, swapped=True)),      # 3 rounds + 34 tiles as 68 half-width items
+    ((8192, 1024, 8192), dict(in_type=1, out_type=1, out_layout=1, streamk_workers=0, **PAIR), 148, True,
+     dict(tile_m=256, tile_n=224, grid=148, streamk_workers=0, swapped=True)),   # 148 tiles of 224 columns: two full rounds
+    # row-major, same problem: not swapped
+    ((8192, 8192, 8192), dict(in_type=1, out_type=1, **PAIR), 148, False,
+     dict(tile_m=256, tile_n=256, grid=148, streamk_workers=0, swapped=False)),
+    # knobs that ask for 128-row tiles stay on the one-CTA kernel
+    ((8192, 8192, 8192), dict(bm=4, bn=4, wave_m_tiles=2, wave_n_tiles=4), 148, False,
+     dict(tile_m=128, tile_n=256, grid=148, streamk_workers=0, swapped=False)),
+    # one round of tiles either way: the one-CTA kernel's shorter tail
+    ((2048, 2048, 4096), PAIR, 148, False, dict(tile_m=128, tile_n=256, swapped=False)),
+    # the decode-shaped GEMM: operands swapped, K split over every SM when there is a workspace
+    ((16, 28672, 8192), dict(in_type=1, bn=1, streamk_workers=0), 148, True,
+     dict(tile_m=128, tile_n=16, grid=148, streamk_workers=148, swapped=True, scratch_bytes=148 * 2 * 128 * 16 * 4,
+          counter_bytes=224 * 4)),
+    ((16, 28672, 8192), dict(in_type=1, bn=1, streamk_workers=0), 148, False,
+     dict(tile_m=128, tile_n=16, streamk_workers=0, swapped=True, scratch_bytes=0)),
+    # explicit worker counts are pure Stream-K on the one-CTA kernel, whatever the part
+    ((512, 768, 1024), dict(bm=4, bn=4, wave_m_tiles=2, wave_n_tiles=4, streamk_workers=5), 132, True,
+     dict(tile_m=128, tile_n=256, grid=5, streamk_workers=5, scratch_bytes=5 * 2 * 128 * 256 * 4, counter_bytes=12 * 4)),
+    # a smaller part: 66 pairs
+    ((8192, 8192, 8192), dict(in_type=1, out_type=1, **PAIR), 132, False, dict(tile_m=256, tile_n=256, grid=132)),
+])
+def test_gemm_planner_without_a_device(wc, shape, kwargs, sms, workspace, want):
+    """What the backend would launch on a part of a given SM count: kernel
+    (one CTA per 128-row tile, or CTA pairs on 256-row tiles), tile width,
+    grid, Stream-K workers and workspace -- decided on the host, testable here."""
+    plan = wc.gemm_plan_for_sms(wc.gemm_desc(*shape, **kwargs), sms, workspace)
+    for key, value in want.items():
+        assert plan[key] == value, (key, plan)
+
+
+def test_gemm_planner_follows_the_environment_knobs(wc):
+    import os
+    desc = wc.gemm_desc(8192, 1024, 8192, in_type=1, out_type=1, out_layout=1, streamk_workers=0, **PAIR)
+    old = {k: os.environ.get(k) for k in ("WAVE_CUDA_GEMM_PAIR_TILE_N", "WAVE_CUDA_GEMM_STREAMK_TAIL",
+                                          "WAVE_CUDA_GEMM_KERNEL", "WAVE_CUDA_GEMM_COL_SWAP")}
+    try:
+        os.environ["WAVE_CUDA_GEMM_PAIR_TILE_N"] = "256"
+        wc.reload_env()
+        assert wc.gemm_plan_for_sms(desc, 148)["tile_n"] == 256
+        os.environ.update(WAVE_CUDA_GEMM_STREAMK_TAIL="force", WAVE_CUDA_GEMM_KERNEL="pair")
+        wc.reload_env()
+        plan = wc.gemm_plan_for_sms(desc, 148)  # 74 whole tiles, then 54 tiles' K iterations over 74 pairs
+        assert plan["streamk_workers"] == 74 and plan["grid"] == 148
+        assert plan["scratch_bytes"] == 74 * 2 * 256 * 256 * 4 and plan["counter_bytes"] == 54 * 2 * 4
+        assert wc.gemm_plan_for_sms(desc, 148, have_workspace=False)["streamk_workers"] == 0
+        os.environ["WAVE_CUDA_GEMM_COL_SWAP"] = "0"
+        wc.reload_env()
+        assert wc.gemm_plan_for_sms(desc, 148)["swapped"] is False
+    finally:
+        for k, v in old.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v
+        wc.reload_env()
+    assert wc.gemm_plan_for_sms(desc, 148)["tile_n"] == 224
