@@ -1,5 +1,8 @@
 // Device helpers shared by the flash-attention forward kernels.
 #pragma once
+#include "fa_sm100.h"
+#include "sm100_ptx.cuh"
+
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <stdint.h>
@@ -45,6 +48,19 @@ __device__ __forceinline__ float2 exp2_poly2(float2 x) {
 // every 8, spread evenly so that FMA-pipe and special-function work interleave.
 template <int kPoly> __device__ __forceinline__ constexpr bool pair_uses_poly(int i) {
   return ((i + 1) * kPoly) / 8 > (i * kPoly) / 8;
+}
+
+// The epilogue's 16-byte store of a piece of O repeated into the further output
+// buffers of a launch (peer GPUs' copies of O, or one multicast address).
+// `ex` must be a __grid_constant__ kernel parameter (its array is indexed in place).
+__device__ __forceinline__ void store_extra_16B(const FaExtra &ex, size_t byte_offset, const uint4 &v) {
+  if (ex.multimem) {
+    multimem_st_16B(static_cast<uint8_t *>(ex.o[0]) + byte_offset, v);
+    return;
+  }
+#pragma unroll 1
+  for (int x = 0; x < ex.n; ++x)
+    *reinterpret_cast<uint4 *>(static_cast<uint8_t *>(ex.o[x]) + byte_offset) = v;
 }
 
 __device__ __forceinline__ uint32_t pack2(float lo, float hi, bool bf16) {

@@ -200,10 +200,12 @@ __device__ __forceinline__ void umma_ts_halves_pair(uint32_t tmem_d, uint32_t tm
   }
 }
 
-template <int kPoly, bool kBf16>
+// kExtra: the epilogue also writes O to the launch's further output buffers
+// (FaExtra); compiled out of the ordinary kernels.
+template <int kPoly, bool kBf16, bool kExtra>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 fa_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-               const __grid_constant__ CUtensorMap tm_v, const FaParams p) {
+               const __grid_constant__ CUtensorMap tm_v, const FaParams p, const __grid_constant__ FaExtra ex) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t *tiles = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t *q_smem = tiles;                                   // 2 tiles
@@ -622,9 +624,14 @@ fa_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 float4 *dst = reinterpret_cast<float4 *>(out_row + cc * 4);
 #pragma unroll
                 for (int v = 0; v < 8; ++v)
-                  if (cc + 4 * v < p.head_dim) // head_dim is a multiple of 16
-                    dst[v] = make_float4(__uint_as_float(o[4 * v]) * inv, __uint_as_float(o[4 * v + 1]) * inv,
-                                         __uint_as_float(o[4 * v + 2]) * inv, __uint_as_float(o[4 * v + 3]) * inv);
+                  if (cc + 4 * v < p.head_dim) { // head_dim is a multiple of 16
+                    const float4 f = make_float4(__uint_as_float(o[4 * v]) * inv, __uint_as_float(o[4 * v + 1]) * inv,
+                                                 __uint_as_float(o[4 * v + 2]) * inv, __uint_as_float(o[4 * v + 3]) * inv);
+                    dst[v] = f;
+                    if constexpr (kExtra)
+                      store_extra_16B(ex, static_cast<size_t>(out_row - static_cast<uint8_t *>(p.O)) + (cc + 4 * v) * 4,
+                                      make_uint4(__float_as_uint(f.x), __float_as_uint(f.y), __float_as_uint(f.z), __float_as_uint(f.w)));
+                  }
               }
             } else {
               uint32_t wv[16];
@@ -635,8 +642,12 @@ fa_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 uint4 *dst = reinterpret_cast<uint4 *>(out_row + cc * 2);
 #pragma unroll
                 for (int v = 0; v < 4; ++v)
-                  if (cc + 8 * v < p.head_dim)
-                    dst[v] = make_uint4(wv[4 * v], wv[4 * v + 1], wv[4 * v + 2], wv[4 * v + 3]);
+                  if (cc + 8 * v < p.head_dim) {
+                    const uint4 u = make_uint4(wv[4 * v], wv[4 * v + 1], wv[4 * v + 2], wv[4 * v + 3]);
+                    dst[v] = u;
+                    if constexpr (kExtra)
+                      store_extra_16B(ex, static_cast<size_t>(out_row - static_cast<uint8_t *>(p.O)) + (cc + 8 * v) * 2, u);
+                  }
               }
             }
           }
@@ -669,8 +680,8 @@ fa_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
 // `tq` and `tv`: boxes of 64 elements x 128 rows over Q and V; K gets a map of
 // its own here (64 elements x 64 rows: a CTA loads half of a block's keys).
-int launch_flash_attention_pair(const FaParams &p, const CUtensorMap &tq, const void *K, const CUtensorMap &tv,
-                                int poly, int sm_count, cudaStream_t stream) {
+int launch_flash_attention_pair(const FaParams &p, const FaExtra &extra, const CUtensorMap &tq, const void *K,
+                                const CUtensorMap &tv, int poly, int sm_count, cudaStream_t stream) {
   CUtensorMap tk;
   {
     const uint64_t hd = static_cast<uint64_t>(p.head_dim), row_bytes = hd * 2;
@@ -698,17 +709,21 @@ int launch_flash_attention_pair(const FaParams &p, const CUtensorMap &tq, const 
       unsafe_budget = true;
       return;
     }
-    kernel<<<grid, kThreads, kSmemBytes, stream>>>(tq, tk, tv, p);
+    kernel<<<grid, kThreads, kSmemBytes, stream>>>(tq, tk, tv, p, extra);
     err = cudaGetLastError();
   };
   auto dispatch = [&](auto bf16_tag) {
     constexpr bool B = decltype(bf16_tag)::value;
+    if (extra.n > 0) { // further output buffers: the kernel variant whose epilogue writes them (default polynomial share)
+      launch(fa_pair_kernel<kDefaultPoly, B, true>);
+      return;
+    }
     switch (poly) {
-    case 1: launch(fa_pair_kernel<1, B>); break;
-    case 2: launch(fa_pair_kernel<2, B>); break;
-    case 3: launch(fa_pair_kernel<3, B>); break;
-    case 4: launch(fa_pair_kernel<4, B>); break;
-    default: launch(fa_pair_kernel<kDefaultPoly, B>); break;
+    case 1: launch(fa_pair_kernel<1, B, false>); break;
+    case 2: launch(fa_pair_kernel<2, B, false>); break;
+    case 3: launch(fa_pair_kernel<3, B, false>); break;
+    case 4: launch(fa_pair_kernel<4, B, false>); break;
+    default: launch(fa_pair_kernel<kDefaultPoly, B, false>); break;
     }
   };
   if (p.is_bf16)

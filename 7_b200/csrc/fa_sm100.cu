@@ -157,10 +157,12 @@ __device__ __noinline__ void fa_report(int code, int role, int detail) {
   }
 }
 
-template <int kPoly, bool kBf16>
+// kExtra: the epilogue also writes O to the launch's further output buffers
+// (FaExtra); compiled out of the ordinary kernels.
+template <int kPoly, bool kBf16, bool kExtra>
 __global__ void __launch_bounds__(kThreads, 1)
 fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-              const __grid_constant__ CUtensorMap tm_v, const FaParams p) {
+              const __grid_constant__ CUtensorMap tm_v, const FaParams p, const __grid_constant__ FaExtra ex) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t *tiles = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t *q_smem = tiles;              // 2 tiles
@@ -655,9 +657,14 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
               float4 *dst = reinterpret_cast<float4 *>(out_row + cc * 4);
 #pragma unroll
               for (int v = 0; v < 8; ++v)
-                if (cc + 4 * v < p.head_dim) // head_dim is a multiple of 16
-                  dst[v] = make_float4(__uint_as_float(o[4 * v]) * inv, __uint_as_float(o[4 * v + 1]) * inv,
-                                       __uint_as_float(o[4 * v + 2]) * inv, __uint_as_float(o[4 * v + 3]) * inv);
+                if (cc + 4 * v < p.head_dim) { // head_dim is a multiple of 16
+                  const float4 f = make_float4(__uint_as_float(o[4 * v]) * inv, __uint_as_float(o[4 * v + 1]) * inv,
+                                               __uint_as_float(o[4 * v + 2]) * inv, __uint_as_float(o[4 * v + 3]) * inv);
+                  dst[v] = f;
+                  if constexpr (kExtra)
+                    store_extra_16B(ex, static_cast<size_t>(out_row - static_cast<uint8_t *>(p.O)) + (cc + 4 * v) * 4,
+                                    make_uint4(__float_as_uint(f.x), __float_as_uint(f.y), __float_as_uint(f.z), __float_as_uint(f.w)));
+                }
             }
           } else {
             uint32_t w[16];
@@ -668,8 +675,12 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
               uint4 *dst = reinterpret_cast<uint4 *>(out_row + cc * 2);
 #pragma unroll
               for (int v = 0; v < 4; ++v)
-                if (cc + 8 * v < p.head_dim)
-                  dst[v] = make_uint4(w[4 * v], w[4 * v + 1], w[4 * v + 2], w[4 * v + 3]);
+                if (cc + 8 * v < p.head_dim) {
+                  const uint4 u = make_uint4(w[4 * v], w[4 * v + 1], w[4 * v + 2], w[4 * v + 3]);
+                  dst[v] = u;
+                  if constexpr (kExtra)
+                    store_extra_16B(ex, static_cast<size_t>(out_row - static_cast<uint8_t *>(p.O)) + (cc + 8 * v) * 2, u);
+                }
             }
           }
         }
@@ -802,8 +813,8 @@ void ticket_launched(const TicketSlot &s, cudaStream_t stream) {
 
 } // namespace
 
-int launch_flash_attention(const FaParams &p, const void *Q, const void *K, const void *V, int sm_count,
-                           cudaStream_t stream) {
+int launch_flash_attention(const FaParams &p, const FaExtra &extra, const void *Q, const void *K, const void *V,
+                           int sm_count, cudaStream_t stream) {
   if (p.head_dim < 16 || p.head_dim > kD || p.head_dim % 16)
     return WAVE_E_UNSUPPORTED;
   CUtensorMap tq, tk, tv;
@@ -871,13 +882,13 @@ int launch_flash_attention(const FaParams &p, const void *Q, const void *K, cons
     const bool stream_kernel = env.fa_kernel ? env.fa_kernel == 2
                                              : p.seq_k >= (p.fixed_ref ? kStreamFromSeqKFixedRef : kStreamFromSeqK);
     if (stream_kernel) {
-      const int rc = launch_flash_attention_stream(params, tq, tk, tv, poly, sm_count, stream);
+      const int rc = launch_flash_attention_stream(params, extra, tq, tk, tv, poly, sm_count, stream);
       ticket_launched(slot, stream);
       return rc;
     }
     // WAVE_CUDA_FA_KERNEL=pair: the CTA-pair kernel (needs an even number of SMs).
     if (env.fa_kernel == 3 && sm_count >= 2) {
-      const int rc = launch_flash_attention_pair(params, tq, K, tv, poly, sm_count, stream);
+      const int rc = launch_flash_attention_pair(params, extra, tq, K, tv, poly, sm_count, stream);
       ticket_launched(slot, stream);
       return rc;
     }
@@ -897,18 +908,22 @@ int launch_flash_attention(const FaParams &p, const void *Q, const void *K, cons
       unsafe_budget = true;
       return;
     }
-    kernel<<<grid, kThreads, kSmemBytes, stream>>>(tq, tk, tv, params);
+    kernel<<<grid, kThreads, kSmemBytes, stream>>>(tq, tk, tv, params, extra);
     err = cudaGetLastError();
   };
   auto dispatch = [&](auto bf16_tag) {
     constexpr bool B = decltype(bf16_tag)::value;
+    if (extra.n > 0) { // further output buffers: the kernel variant whose epilogue writes them (default polynomial share)
+      launch(fa_fwd_kernel<kDefaultPoly, B, true>);
+      return;
+    }
     switch (poly) {
-    case 0: launch(fa_fwd_kernel<0, B>); break;
-    case 1: launch(fa_fwd_kernel<1, B>); break;
-    case 2: launch(fa_fwd_kernel<2, B>); break;
-    case 3: launch(fa_fwd_kernel<3, B>); break;
-    case 4: launch(fa_fwd_kernel<4, B>); break;
-    default: launch(fa_fwd_kernel<kDefaultPoly, B>); break;
+    case 0: launch(fa_fwd_kernel<0, B, false>); break;
+    case 1: launch(fa_fwd_kernel<1, B, false>); break;
+    case 2: launch(fa_fwd_kernel<2, B, false>); break;
+    case 3: launch(fa_fwd_kernel<3, B, false>); break;
+    case 4: launch(fa_fwd_kernel<4, B, false>); break;
+    default: launch(fa_fwd_kernel<kDefaultPoly, B, false>); break;
     }
   };
   if (p.is_bf16)

@@ -21,21 +21,33 @@ struct FaParams {
   unsigned int *ticket; // device counter, zero at launch: the persistent CTAs draw work items from it
 };
 
+// Further output buffers of a launch: every 16 bytes of O the epilogue stores
+// go, at the same offset, to `n` more buffers too (other GPUs' copies of the
+// full O when the (batch, head) slabs of a sharded problem are gathered inside
+// the kernel); with `multimem`, o[0] is an NVLink multicast address and one
+// multimem.st reaches every GPU.  The log-sum-exp is written locally only.
+// A kernel parameter of its own, and only of the kernel variants that use it:
+// the ordinary kernels' parameter block and code are unchanged by it.
+struct FaExtra {
+  int n, multimem;
+  void *o[7];
+};
+
 // Builds the tensor maps and launches.  Returns a WAVE_* code (0 = ok).
-int launch_flash_attention(const FaParams &p, const void *Q, const void *K, const void *V, int sm_count,
-                           cudaStream_t stream);
+int launch_flash_attention(const FaParams &p, const FaExtra &extra, const void *Q, const void *K, const void *V,
+                           int sm_count, cudaStream_t stream);
 cudaError_t fa_read_status(int out[4], bool clear);
 // The streaming kernel (fa_stream_sm100.cu): one 128-row Q tile per CTA, score
 // and probability buffers double-buffered in tensor memory.  `p.ticket` must
 // point at a zeroed work-item counter.
-int launch_flash_attention_stream(const FaParams &p, const CUtensorMap &tq, const CUtensorMap &tk,
+int launch_flash_attention_stream(const FaParams &p, const FaExtra &extra, const CUtensorMap &tq, const CUtensorMap &tk,
                                   const CUtensorMap &tv, int poly, int sm_count, cudaStream_t stream);
 cudaError_t fa_stream_read_status(int out[4], bool clear);
 // The CTA-pair kernel (fa_pair_sm100.cu): 512-row work items on 2-CTA clusters,
 // tcgen05 cta_group::2.  `tq` / `tv` have boxes of 64 elements x 128 rows; K's
 // map (64 x 64) is built inside.  `p.ticket` as above.
-int launch_flash_attention_pair(const FaParams &p, const CUtensorMap &tq, const void *K, const CUtensorMap &tv, int poly,
-                                int sm_count, cudaStream_t stream);
+int launch_flash_attention_pair(const FaParams &p, const FaExtra &extra, const CUtensorMap &tq, const void *K,
+                                const CUtensorMap &tv, int poly, int sm_count, cudaStream_t stream);
 cudaError_t fa_pair_read_status(int out[4], bool clear);
 
 // Provided by the backend: rank-2/3 tensor map over 16-bit elements with the

@@ -128,10 +128,12 @@ __device__ __noinline__ void fas_report(int code, int role, int detail) {
   }
 }
 
-template <int kPoly, bool kBf16>
+// kExtra: the epilogue also writes O to the launch's further output buffers
+// (FaExtra); compiled out of the ordinary kernels.
+template <int kPoly, bool kBf16, bool kExtra>
 __global__ void __launch_bounds__(kThreads, 1)
 fa_stream_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                 const __grid_constant__ CUtensorMap tm_v, const FaParams p) {
+                 const __grid_constant__ CUtensorMap tm_v, const FaParams p, const __grid_constant__ FaExtra ex) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t *tiles = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t *q_smem = tiles;             // 2 slots
@@ -670,9 +672,14 @@ fa_stream_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             float4 *dst = reinterpret_cast<float4 *>(out_row + cc * 4);
 #pragma unroll
             for (int v = 0; v < 8; ++v)
-              if (cc + 4 * v < p.head_dim) // head_dim is a multiple of 16
-                dst[v] = make_float4(__uint_as_float(o[4 * v]) * inv, __uint_as_float(o[4 * v + 1]) * inv,
-                                     __uint_as_float(o[4 * v + 2]) * inv, __uint_as_float(o[4 * v + 3]) * inv);
+              if (cc + 4 * v < p.head_dim) { // head_dim is a multiple of 16
+                const float4 f = make_float4(__uint_as_float(o[4 * v]) * inv, __uint_as_float(o[4 * v + 1]) * inv,
+                                             __uint_as_float(o[4 * v + 2]) * inv, __uint_as_float(o[4 * v + 3]) * inv);
+                dst[v] = f;
+                if constexpr (kExtra)
+                  store_extra_16B(ex, static_cast<size_t>(out_row - static_cast<uint8_t *>(p.O)) + (cc + 4 * v) * 4,
+                                  make_uint4(__float_as_uint(f.x), __float_as_uint(f.y), __float_as_uint(f.z), __float_as_uint(f.w)));
+              }
           }
         } else {
           uint32_t wd[16];
@@ -683,8 +690,12 @@ fa_stream_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             uint4 *dst = reinterpret_cast<uint4 *>(out_row + cc * 2);
 #pragma unroll
             for (int v = 0; v < 4; ++v)
-              if (cc + 8 * v < p.head_dim)
-                dst[v] = make_uint4(wd[4 * v], wd[4 * v + 1], wd[4 * v + 2], wd[4 * v + 3]);
+              if (cc + 8 * v < p.head_dim) {
+                const uint4 u = make_uint4(wd[4 * v], wd[4 * v + 1], wd[4 * v + 2], wd[4 * v + 3]);
+                dst[v] = u;
+                if constexpr (kExtra)
+                  store_extra_16B(ex, static_cast<size_t>(out_row - static_cast<uint8_t *>(p.O)) + (cc + 8 * v) * 2, u);
+              }
           }
         }
       }
@@ -742,7 +753,7 @@ extern "C" int wave_cuda_fas_trace_read(long long *out, int clear) {
 }
 #endif
 
-int launch_flash_attention_stream(const FaParams &p, const CUtensorMap &tq, const CUtensorMap &tk,
+int launch_flash_attention_stream(const FaParams &p, const FaExtra &extra, const CUtensorMap &tq, const CUtensorMap &tk,
                                   const CUtensorMap &tv, int poly, int sm_count, cudaStream_t stream) {
   const long long total_items = static_cast<long long>(p.batch_heads) * ((p.seq_q + kBlockM - 1) / kBlockM);
   const unsigned grid = static_cast<unsigned>(total_items < sm_count ? total_items : sm_count);
@@ -760,19 +771,23 @@ int launch_flash_attention_stream(const FaParams &p, const CUtensorMap &tq, cons
       unsafe_budget = true;
       return;
     }
-    kernel<<<grid, kThreads, kSmemBytes, stream>>>(tq, tk, tv, p);
+    kernel<<<grid, kThreads, kSmemBytes, stream>>>(tq, tk, tv, p, extra);
     err = cudaGetLastError();
   };
   auto dispatch = [&](auto bf16_tag) {
     constexpr bool B = decltype(bf16_tag)::value;
+    if (extra.n > 0) { // further output buffers: the kernel variant whose epilogue writes them (default polynomial share)
+      launch(fa_stream_kernel<2, B, true>);
+      return;
+    }
     // A quarter of the exponentials on the FMA pipe is this kernel's measured
     // best (causal B=2 H=64 S=8192, sustained: 893 -> 1049 TFLOP/s); `poly` < 0 asks for it.
     switch (poly) {
-    case 0: launch(fa_stream_kernel<0, B>); break;
-    case 1: launch(fa_stream_kernel<1, B>); break;
-    case 3: launch(fa_stream_kernel<3, B>); break;
-    case 4: launch(fa_stream_kernel<4, B>); break;
-    default: launch(fa_stream_kernel<2, B>); break;
+    case 0: launch(fa_stream_kernel<0, B, false>); break;
+    case 1: launch(fa_stream_kernel<1, B, false>); break;
+    case 3: launch(fa_stream_kernel<3, B, false>); break;
+    case 4: launch(fa_stream_kernel<4, B, false>); break;
+    default: launch(fa_stream_kernel<2, B, false>); break;
     }
   };
   if (p.is_bf16)

@@ -1046,8 +1046,44 @@ int wave_cuda_fa_validate(const wave_fa_desc *d) {
   return WAVE_OK;
 }
 
+} // extern "C"
+
+namespace {
+int fa_launch(const wave_fa_desc *d, const void *Q, const void *K, const void *V, void *O, float *lse, void *stream,
+              void *const *extra_o, int n_extra, bool extra_multimem);
+}
+
+extern "C" {
+
 int wave_cuda_flash_attention_fwd(const wave_fa_desc *d, const void *Q, const void *K, const void *V, void *O,
                                   float *lse, void *stream) {
+  return fa_launch(d, Q, K, V, O, lse, stream, nullptr, 0, false);
+}
+
+int wave_cuda_flash_attention_fwd_multi_output(const wave_fa_desc *d, const void *Q, const void *K, const void *V,
+                                               void *const *O_targets, int n_targets, float *lse, void *stream) {
+  if (!O_targets || n_targets < 1 || n_targets > 8)
+    return fail(WAVE_E_INVALID, "n_targets must be between 1 and 8; got %d", n_targets);
+  for (int i = 0; i < n_targets; ++i)
+    if (!O_targets[i] || (reinterpret_cast<uintptr_t>(O_targets[i]) & 15))
+      return fail(WAVE_E_INVALID, "every output target must be a non-null, 16-byte aligned device pointer");
+  return fa_launch(d, Q, K, V, O_targets[0], lse, stream, O_targets + 1, n_targets - 1, false);
+}
+
+int wave_cuda_flash_attention_fwd_multicast_output(const wave_fa_desc *d, const void *Q, const void *K, const void *V,
+                                                   void *O_local, void *O_multicast, float *lse, void *stream) {
+  if (!O_multicast || (reinterpret_cast<uintptr_t>(O_multicast) & 15))
+    return fail(WAVE_E_INVALID, "the multicast target must be a non-null, 16-byte aligned address");
+  void *const extra[1] = {O_multicast};
+  return fa_launch(d, Q, K, V, O_local, lse, stream, extra, 1, true);
+}
+
+} // extern "C"
+
+namespace {
+
+int fa_launch(const wave_fa_desc *d, const void *Q, const void *K, const void *V, void *O, float *lse, void *stream,
+              void *const *extra_o, int n_extra, bool extra_multimem) {
   int rc = wave_cuda_fa_validate(d);
   if (rc != WAVE_OK)
     return rc;
@@ -1071,12 +1107,21 @@ int wave_cuda_flash_attention_fwd(const wave_fa_desc *d, const void *Q, const vo
   p.ref_log2 = p.fixed_ref ? static_cast<float>(fa_log2_score_bound(*d)) : 0.0f;
   p.O = O;
   p.lse = lse;
+  wave::FaExtra extra{};
+  extra.n = n_extra;
+  extra.multimem = extra_multimem ? 1 : 0;
+  for (int i = 0; i < n_extra; ++i)
+    extra.o[i] = extra_o[i];
   int sms = 0;
   if ((rc = sm_count(&sms)) != WAVE_OK)
     return rc;
-  rc = wave::launch_flash_attention(p, Q, K, V, sms, static_cast<cudaStream_t>(stream));
+  rc = wave::launch_flash_attention(p, extra, Q, K, V, sms, static_cast<cudaStream_t>(stream));
   return rc;
 }
+
+} // namespace
+
+extern "C" {
 
 int wave_cuda_flash_attention_fwd_host(const wave_fa_desc *d, const void *Q_host, const void *K_host,
                                        const void *V_host, void *O_host, void *stream) {

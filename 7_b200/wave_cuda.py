@@ -51,6 +51,7 @@ EXPORTS = [
     "wave_cuda_gemm_desc_init", "wave_cuda_gemm_validate", "wave_cuda_gemm_workspace_bytes", "wave_cuda_gemm",
     "wave_cuda_gemm_host", "wave_cuda_gemm_host_a_resident", "wave_cuda_gemm_multi_output", "wave_cuda_gemm_multicast_output",
     "wave_cuda_gemm_plan", "wave_cuda_gemm_plan_for_sms", "wave_cuda_gemm_streamk_static", "wave_cuda_fa_validate", "wave_cuda_flash_attention_fwd",
+    "wave_cuda_flash_attention_fwd_multi_output", "wave_cuda_flash_attention_fwd_multicast_output",
     "wave_cuda_flash_attention_fwd_host", "wave_cuda_module_get_function", "wave_cuda_launch",
     "wave_cuda_function_release", "wave_cuda_check_device_status",
     # include/wave_mgpu.h: the wrappers a host module lowered by gpu-to-llvm calls
@@ -99,6 +100,8 @@ def lib() -> C.CDLL:
     L.wave_cuda_fa_validate.argtypes = [C.POINTER(FaDesc)]
     L.wave_cuda_flash_attention_fwd.argtypes = [C.POINTER(FaDesc), vp, vp, vp, vp, vp, vp]
     L.wave_cuda_flash_attention_fwd_host.argtypes = [C.POINTER(FaDesc), vp, vp, vp, vp, vp]
+    L.wave_cuda_flash_attention_fwd_multi_output.argtypes = [C.POINTER(FaDesc), vp, vp, vp, C.POINTER(vp), C.c_int, vp, vp]
+    L.wave_cuda_flash_attention_fwd_multicast_output.argtypes = [C.POINTER(FaDesc), vp, vp, vp, vp, vp, vp, vp]
     L.wave_cuda_module_get_function.argtypes = [C.c_char_p, vp, C.POINTER(vp)]
     L.wave_cuda_launch.argtypes = [vp, C.POINTER(vp), vp]
     L.wave_cuda_function_release.argtypes = [vp]
@@ -235,6 +238,23 @@ def flash_attention_fwd(desc: FaDesc, q_ptr: int, k_ptr: int, v_ptr: int, o_ptr:
                         stream: int = 0) -> None:
     check(lib().wave_cuda_flash_attention_fwd(C.byref(desc), q_ptr, k_ptr, v_ptr, o_ptr, lse_ptr or None,
                                               stream or None))
+
+
+def flash_attention_fwd_multi_output(desc: FaDesc, q_ptr: int, k_ptr: int, v_ptr: int, o_ptrs, lse_ptr: int = 0,
+                                     stream: int = 0) -> None:
+    """The forward with O written to every buffer of `o_ptrs` (the first as usual, the others 16 bytes
+    at a time out of the epilogue): the gather of (batch, head)-sharded attention inside the kernel
+    when the others are peer GPUs' copies of O."""
+    arr = (C.c_void_p * len(o_ptrs))(*o_ptrs)
+    check(lib().wave_cuda_flash_attention_fwd_multi_output(C.byref(desc), q_ptr, k_ptr, v_ptr, arr, len(o_ptrs),
+                                                           lse_ptr or None, stream or None))
+
+
+def flash_attention_fwd_multicast_output(desc: FaDesc, q_ptr: int, k_ptr: int, v_ptr: int, o_local_ptr: int,
+                                         o_multicast_ptr: int, lse_ptr: int = 0, stream: int = 0) -> None:
+    """The same through one NVLink multicast address (multimem.st)."""
+    check(lib().wave_cuda_flash_attention_fwd_multicast_output(C.byref(desc), q_ptr, k_ptr, v_ptr, o_local_ptr,
+                                                               o_multicast_ptr, lse_ptr or None, stream or None))
 
 
 def flash_attention_fwd_host(desc: FaDesc, q_ptr: int, k_ptr: int, v_ptr: int, o_ptr: int, stream: int = 0) -> None:

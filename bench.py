@@ -398,22 +398,31 @@ def time_gather(torch, sh, work, dist, stream, world) -> tuple[dict, object]:
 
 
 def time_fused_gather(torch, wc, sh, work, dist, stream, rank, world, oracle) -> dict:
-    """The all-gather fused into the GEMM: every rank writes its column block
-    straight into every rank's copy of the full C (peer-mapped memory, plain
-    stores out of the epilogue, tile by tile while the next tile is computed),
-    followed by a one-element all-reduce as the barrier after which the copies
-    may be read.  Timed as one step, max over ranks; rank 0's copy is then
-    checked against the oracle on rows that span every rank's columns."""
+    """The all-gather fused into the kernel: every rank writes its block (GEMM:
+    N-column block of C; attention: (batch, head) slab of O) straight into every
+    rank's copy of the full output -- peer-mapped memory, plain stores out of
+    the epilogue while the kernel computes on, or one multimem.st per 16 bytes to
+    an NVLink multicast address -- followed by a one-element all-reduce as the
+    barrier after which the copies may be read.  Timed as one step, max over
+    ranks; rank 0's copy is then checked against the oracle on a sample that
+    spans every rank's part."""
+    gemm = work.kind == "gemm"
+    shape = (work.N, work.M) if gemm else (work.B * work.H, work.S, work.D)
     try:
-        out = sh.PeerMappedOutput((work.N, work.M), torch.bfloat16, dist, rank, world)
+        out = sh.PeerMappedOutput(shape, torch.bfloat16, dist, rank, world)
     except Exception as err:  # no symmetric memory on this system: say so, the NCCL gather stands
         return {"unavailable": f"{type(err).__name__}: {err}"[:300]}
-    targets = out.block_targets(work.n0 * work.M * 2)
-    desc = wc.gemm_desc(work.M, work.nl, work.K, in_type=wc.BF16, out_type=wc.BF16, out_layout=wc.COL_MAJOR,
-                        streamk_workers=1, bm=4, bn=4, wave_m_tiles=4, wave_n_tiles=4)
-
-    offset = work.n0 * work.M * 2
-    iters = 20
+    if gemm:
+        offset = work.n0 * work.M * 2
+        block_bytes = work.nl * work.M * 2
+        desc = wc.gemm_desc(work.M, work.nl, work.K, in_type=wc.BF16, out_type=wc.BF16, out_layout=wc.COL_MAJOR,
+                            streamk_workers=1, bm=4, bn=4, wave_m_tiles=4, wave_n_tiles=4)
+    else:
+        offset = work.h0 * work.S * work.D * 2
+        block_bytes = work.hl * work.S * work.D * 2
+        desc = work.desc
+    targets = out.block_targets(offset)
+    iters = 20 if gemm else 10
 
     def timed(step):
         out.local.fill_(float("nan"))
@@ -441,23 +450,33 @@ def time_fused_gather(torch, wc, sh, work, dist, stream, rank, world, oracle) ->
         return entry
 
     def unicast():
-        wc.gemm_multi_output(desc, work.a.data_ptr(), work.b.data_ptr(), targets, stream.cuda_stream)
+        if gemm:
+            wc.gemm_multi_output(desc, work.a.data_ptr(), work.b.data_ptr(), targets, stream.cuda_stream)
+        else:
+            wc.flash_attention_fwd_multi_output(desc, work.q.data_ptr(), work.k.data_ptr(), work.v.data_ptr(), targets,
+                                                0, stream.cuda_stream)
         out.settle()
 
     def multicast():
-        wc.gemm_multicast_output(desc, work.a.data_ptr(), work.b.data_ptr(), out.ptrs[rank] + offset,
-                                 out.multicast_ptr + offset, stream.cuda_stream)
+        if gemm:
+            wc.gemm_multicast_output(desc, work.a.data_ptr(), work.b.data_ptr(), out.ptrs[rank] + offset,
+                                     out.multicast_ptr + offset, stream.cuda_stream)
+        else:
+            wc.flash_attention_fwd_multicast_output(desc, work.q.data_ptr(), work.k.data_ptr(), work.v.data_ptr(),
+                                                    out.ptrs[rank] + offset, out.multicast_ptr + offset, 0,
+                                                    stream.cuda_stream)
         out.settle()
     res = timed(unicast)
-    res.update({"kernel": "wave_cuda_gemm_multi_output: the column block written to every rank's C from the GEMM "
+    entry = "wave_cuda_gemm_multi_output" if gemm else "wave_cuda_flash_attention_fwd_multi_output"
+    res.update({"kernel": f"{entry}: this rank's block written to every rank's copy of the output from the kernel's "
                           "epilogue over NVLink (peer-mapped memory, plain stores), then a one-element all-reduce as barrier",
-                "launches": 2 * (iters + 3), "bytes_sent_per_rank": (world - 1) * work.nl * work.M * 2,
-                "sent_gbs_per_rank": (world - 1) * work.nl * work.M * 2 / (res["ms_per_step"] * 1e-3) / 1e9})
+                "launches": 2 * (iters + 3), "bytes_sent_per_rank": (world - 1) * block_bytes,
+                "sent_gbs_per_rank": (world - 1) * block_bytes / (res["ms_per_step"] * 1e-3) / 1e9})
     if out.multicast_ptr:
         res["multicast"] = timed(multicast)
-        res["multicast"]["kernel"] = ("wave_cuda_gemm_multicast_output: every tile stored once to an NVLink multicast "
-                                      "address (multimem.st), replicated to all ranks in the switch")
-        res["multicast"]["bytes_sent_per_rank"] = work.nl * work.M * 2
+        res["multicast"]["kernel"] = (entry.replace("multi_output", "multicast_output") + ": every 16 bytes stored once "
+                                      "to an NVLink multicast address (multimem.st), replicated to all ranks in the switch")
+        res["multicast"]["bytes_sent_per_rank"] = block_bytes
     else:
         res["multicast"] = {"unavailable": "the symmetric-memory handle has no multicast address (no NVLS for this group)"}
     del out
@@ -710,7 +729,7 @@ def measure_workload(torch, wc, sh, workload, rank, world, strong, steps, warmup
         oracle.build()
         res["parity"] = work.check(oracle, gathered)
     del gathered
-    if sharded and want_gather and work.kind == "gemm":
+    if sharded and want_gather:
         res["fused_gather"] = time_fused_gather(torch, wc, sh, work, dist, stream, rank, world, oracle)
         counters["launches"] += res["fused_gather"].get("launches", 0)
         if "ms_per_step" in res["fused_gather"]:  # compute + NCCL gather against the fused kernels

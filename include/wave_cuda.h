@@ -266,6 +266,21 @@ int wave_cuda_fa_validate(const wave_fa_desc *desc);
 int wave_cuda_flash_attention_fwd(const wave_fa_desc *desc, const void *Q, const void *K, const void *V, void *O,
                                   float *lse_or_null, void *stream);
 
+/* No counterpart in the reference (single-device).  The forward with O written
+ * to several buffers at once, for the gather of (batch, head)-sharded attention
+ * inside the kernel: O_targets[0] as above, and every 16 bytes of O the epilogue
+ * stores also to O_targets[1 .. n_targets-1] at the same offset (other ranks'
+ * copies of the full O, mapped into this process; rank r passes the address of
+ * ITS slab inside each copy).  The multicast form sends each piece once to an
+ * NVLink multicast address (multimem.st) that reaches every rank's copy.  The
+ * log-sum-exp goes to `lse_or_null` only.  Stores are complete when the kernel
+ * is; synchronise the ranks before reading a copy.  1 <= n_targets <= 8. */
+int wave_cuda_flash_attention_fwd_multi_output(const wave_fa_desc *desc, const void *Q, const void *K, const void *V,
+                                               void *const *O_targets, int n_targets, float *lse_or_null, void *stream);
+int wave_cuda_flash_attention_fwd_multicast_output(const wave_fa_desc *desc, const void *Q, const void *K,
+                                                   const void *V, void *O_local, void *O_multicast,
+                                                   float *lse_or_null, void *stream);
+
 int wave_cuda_flash_attention_fwd_host(const wave_fa_desc *desc, const void *Q_host, const void *K_host,
                                        const void *V_host, void *O_host, void *stream);
 

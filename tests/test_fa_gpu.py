@@ -301,6 +301,36 @@ def test_more_queued_launches_than_ticket_counters(cuda, wc, oracle):
     assert np.array_equal(got, np.broadcast_to(want, got.shape))
 
 
+@pytest.mark.parametrize("BH,S,D,causal,out_f32", [
+    (6, 512, 128, True, False),
+    (3, 384, 64, False, False),     # head dimension below 128: only the first 64 columns exist
+    (2, 272, 128, True, True),      # ragged length, f32 output
+])
+def test_multi_output_writes_every_target(cuda, wc, oracle, BH, S, D, causal, out_f32):
+    """wave_cuda_flash_attention_fwd_multi_output: O lands in every target (on
+    one GPU: three local buffers stand in for peer GPUs' copies), each bit for
+    bit what the plain call writes; here the slab sits in the middle of a larger
+    buffer, as a rank's (batch, head) slab sits inside the gathered O, and the
+    rest of that buffer must stay untouched."""
+    t = oracle.BF16
+    q, k, v = normal_qkv(oracle, BH, S, S, D, t, seed=53)
+    want = run_fa(cuda, wc, q, k, v, "bf16", 1, BH, causal, out_f32=out_f32)
+    desc = wc.fa_desc(1, BH, S, S, D, causal=causal, io_type=wc.BF16, out_f32=out_f32)
+    dq, dk, dv = (to_device_bits(cuda, x) for x in (q, k, v))
+    dt = cuda.float32 if out_f32 else cuda.bfloat16
+    pad = 2 * S * D  # elements before and after the slab
+    targets = [cuda.full((pad + BH * S * D + pad,), float("nan"), dtype=dt, device="cuda") for _ in range(3)]
+    esize = 4 if out_f32 else 2
+    wc.flash_attention_fwd_multi_output(desc, dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                        [x.data_ptr() + pad * esize for x in targets], 0,
+                                        cuda.cuda.current_stream().cuda_stream)
+    wc.check_device_status()
+    for x in targets:
+        got = x.float().cpu().numpy()
+        assert np.array_equal(got[pad:pad + BH * S * D].reshape(BH, S, D), want)
+        assert np.isnan(got[:pad]).all() and np.isnan(got[pad + BH * S * D:]).all()
+
+
 def _operator_case(cuda, oracle, q_bits, k_bits, v_bits, **kwargs):
     """Runs the torch-tensor operator (the mirror of the reference's
     `attention`, integrations/tlx/workloads/amd_fa_wave.py:1671-1720) on

@@ -2,7 +2,8 @@
 blocks gathered three ways -- ncclAllGather after the kernel, peer stores out
 of the kernel's epilogue (wave_cuda_gemm_multi_output) and NVLink multicast
 stores (wave_cuda_gemm_multicast_output) -- must all leave the oracle's full C
-on every rank, and the sharded host-buffer call must return each rank's block.
+on every rank, the sharded host-buffer call must return each rank's block, and
+the (batch, head)-sharded attention must gather its slabs the same three ways.
 Skipped on a machine with fewer than two GPUs (the single-GPU tests cover the
 epilogue's copy logic with local buffers standing in for peers, and the gloo
 test the host arithmetic)."""
@@ -80,6 +81,36 @@ def _worker(rank, world, port, tmpdir):
         wc.check_device_status()
         got = oracle.from_bits(c_host.numpy().view(np.uint16), oracle.BF16).reshape(n1 - n0, M).T
         assert np.array_equal(got, want[:, n0:n1])
+        # 4. attention: (batch, head) slabs, gathered by NCCL and inside the kernel (both forms)
+        BH, S, D = 8, 512, 128
+        q, k, v = (oracle.baseline_inputs((BH, S, D), "normal", 9, i, oracle.BF16) for i in range(3))
+        want_o = None
+        h0, h1 = sh.head_shard(BH, world, rank)
+        fd = wc.fa_desc(1, h1 - h0, S, S, D, causal=True, io_type=wc.BF16)
+        dq, dk, dv = (dev(x[h0:h1]) for x in (q, k, v))
+        o_slab = torch.full((h1 - h0, S, D), float("nan"), dtype=torch.bfloat16, device="cuda")
+        wc.flash_attention_fwd(fd, dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), o_slab.data_ptr(), 0, stream)
+        want_o = sh.all_gather_shards(o_slab, dist).reshape(BH, S, D).float().cpu().numpy()
+        ref = oracle.fa_ref(q, k, v, oracle.BF16, 1.0 / np.sqrt(D), causal=True)
+        assert np.abs(want_o - ref).max() <= 3.0e-2
+        full_o = sh.PeerMappedOutput((BH, S, D), torch.bfloat16, dist, rank, world)
+        o_off = h0 * S * D * 2
+        forms = [lambda: wc.flash_attention_fwd_multi_output(fd, dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                                              full_o.block_targets(o_off), 0, stream)]
+        if full_o.multicast_ptr:
+            forms.append(lambda: wc.flash_attention_fwd_multicast_output(
+                fd, dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), full_o.ptrs[rank] + o_off,
+                full_o.multicast_ptr + o_off, 0, stream))
+        for form in forms:
+            full_o.local.fill_(float("nan"))
+            torch.cuda.synchronize()
+            dist.barrier()
+            form()
+            full_o.settle()
+            torch.cuda.synchronize()
+            wc.check_device_status()
+            assert np.array_equal(full_o.local.float().cpu().numpy(), want_o)  # the plain call's bits, from every rank
+            dist.barrier()
         open(os.path.join(tmpdir, f"ok{rank}"), "w").close()
     finally:
         dist.destroy_process_group()
