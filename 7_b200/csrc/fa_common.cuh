@@ -63,6 +63,37 @@ __device__ __forceinline__ void store_extra_16B(const FaExtra &ex, size_t byte_o
     *reinterpret_cast<uint4 *>(static_cast<uint8_t *>(ex.o[x]) + byte_offset) = v;
 }
 
+// Bytes of shared memory the kernel variants with further output buffers add:
+// a 2 KB slot per softmax warp (eight of them) for store_extra_chunk_16bit.
+constexpr int kExtraStageBytes = 8 * 2048;
+
+// One 32-column chunk of 16-bit O (64 bytes per row) of a warp's 32 consecutive
+// rows to the further output buffers, coalesced: every lane parks its row's 64
+// bytes in the warp's shared-memory slot and the warp reads them back so that
+// four lanes cover one row -- a store instruction then writes eight whole
+// 64-byte pieces instead of thirty-two scattered 16-byte ones, which is what
+// NVLink (and the multicast path through the switch) needs to run at speed.
+// `first_row_offset`: byte offset of (the warp's first row, the chunk's first
+// column) inside O; rows >= rows_live and bytes >= bytes_live do not exist.
+__device__ __forceinline__ void store_extra_chunk_16bit(const FaExtra &ex, uint8_t *slot, int lane,
+                                                        const uint32_t (&w)[16], size_t first_row_offset,
+                                                        size_t row_bytes, int rows_live, int bytes_live) {
+  uint4 *mine = reinterpret_cast<uint4 *>(slot) + lane * 4;
+#pragma unroll
+  for (int v = 0; v < 4; ++v)
+    mine[v] = make_uint4(w[4 * v], w[4 * v + 1], w[4 * v + 2], w[4 * v + 3]);
+  __syncwarp();
+  const int piece = lane & 3;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = (lane >> 2) + 8 * i;
+    if (r < rows_live && piece * 16 < bytes_live)
+      store_extra_16B(ex, first_row_offset + static_cast<size_t>(r) * row_bytes + piece * 16,
+                      reinterpret_cast<const uint4 *>(slot)[r * 4 + piece]);
+  }
+  __syncwarp();
+}
+
 __device__ __forceinline__ uint32_t pack2(float lo, float hi, bool bf16) {
   if (bf16) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);

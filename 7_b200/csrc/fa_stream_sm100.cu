@@ -141,6 +141,9 @@ fa_stream_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   uint8_t *v_smem = tiles + 4 * kTile; // 2 stages
   StreamShared *sh = reinterpret_cast<StreamShared *>(tiles + kSmemTiles);
   volatile int *abort_flag = &sh->abort_flag;
+  // the variants with further output buffers: 2 KB per softmax warp behind everything else
+  uint8_t *extra_stage = tiles + (kSmemBytes - 1024);
+  (void)extra_stage;
 #ifdef WAVE_FA_TRACE
   volatile unsigned int *fa_trace_smem =
       reinterpret_cast<volatile unsigned int *>(tiles + kSmemTiles + kSharedStateBytes);
@@ -691,11 +694,15 @@ fa_stream_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll
             for (int v = 0; v < 4; ++v)
               if (cc + 8 * v < p.head_dim) {
-                const uint4 u = make_uint4(wd[4 * v], wd[4 * v + 1], wd[4 * v + 2], wd[4 * v + 3]);
-                dst[v] = u;
-                if constexpr (kExtra)
-                  store_extra_16B(ex, static_cast<size_t>(out_row - static_cast<uint8_t *>(p.O)) + (cc + 8 * v) * 2, u);
+                dst[v] = make_uint4(wd[4 * v], wd[4 * v + 1], wd[4 * v + 2], wd[4 * v + 3]);
               }
+          }
+          if constexpr (kExtra) {
+            const int first_row = q_row - lane; // a warp's 32 rows are consecutive
+            store_extra_chunk_16bit(ex, extra_stage + (warp - 4) * 2048, lane, wd,
+                                    (static_cast<size_t>(w.bh) * p.seq_q + first_row) * p.head_dim * 2 + static_cast<size_t>(cc) * 2,
+                                    static_cast<size_t>(p.head_dim) * 2, min(32, max(0, p.seq_q - first_row)),
+                                    min(64, (p.head_dim - cc) * 2));
           }
         }
       }
@@ -764,14 +771,15 @@ int launch_flash_attention_stream(const FaParams &p, const FaExtra &extra, const
     // compiler actually gave it; refuse to launch rather than risk a grow
     // request that can never be satisfied.
     KernelInfo info;
-    err = prepare_kernel(kernel, kSmemBytes, &info);
+    const int smem_bytes = kSmemBytes + (extra.n > 0 ? kExtraStageBytes : 0);
+    err = prepare_kernel(kernel, smem_bytes, &info);
     if (err != cudaSuccess)
       return;
     if ((info.num_regs - kIssueRegs) * 128 < (kSoftmaxRegs - info.num_regs) * 256 || info.num_regs * kThreads > 65536) {
       unsafe_budget = true;
       return;
     }
-    kernel<<<grid, kThreads, kSmemBytes, stream>>>(tq, tk, tv, p, extra);
+    kernel<<<grid, kThreads, smem_bytes, stream>>>(tq, tk, tv, p, extra);
     err = cudaGetLastError();
   };
   auto dispatch = [&](auto bf16_tag) {
