@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libwave_cuda.so")
 SOURCES = ["gemm_sm100.cu", "gemm_pair_sm100.cu", "gemm_noalloc_sm100.cu", "fa_sm100.cu", "fa_stream_sm100.cu",
-           "fa_pair_sm100.cu", "wave_cuda_backend.cu", "mgpu_runtime.cu"]
+           "fa_pair_sm100.cu", "fa_decoupled_sm100.cu", "wave_cuda_backend.cu", "mgpu_runtime.cu"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

@@ -94,8 +94,6 @@ constexpr int kTmemCols = 512;
 // S/P hand-offs between the softmax warps and the tensor core, not by the
 // special-function unit, so the default keeps every exponential on it.
 constexpr int kDefaultPoly = 0;
-constexpr int kStreamFromSeqK = 6144; // key sequence length from which the streaming kernel is used
-constexpr int kStreamFromSeqKFixedRef = 2048; // the same with a fixed softmax reference
 constexpr int kFixedRefStagger = 900;
 constexpr float kRescaleThreshold = 8.0f;
 // setmaxnreg budget.  The kernel starts with kLaunchRegs per thread (12 warps,
@@ -872,29 +870,33 @@ int launch_flash_attention(const FaParams &p, const FaExtra &extra, const void *
   if (int rc = ticket_acquire(stream, &slot); rc != WAVE_OK)
     return rc;
   params.ticket = slot.counter;
-  // WAVE_CUDA_FA_KERNEL=stream|pingpong picks the kernel (a knob for
-  // measurements; results are the same).
-  // Which kernel: the streaming one pays more per work item (an epilogue and a
-  // hand-over of the row sums per 128 rows) and less per K/V block, so it wins
-  // on long sequences.  Measured back to back under the power cap, the kernels
-  // taking turns (causal / non-causal TFLOP/s, ping-pong against streaming):
-  // S=1024 (B=32 H=32) 571/841 against 535/811; S=2048 (B=8 H=32) 739/963
-  // against 724/951; S=4096 (B=16 H=32) 925/1049 against 926/1056; S=8192 (B=2
-  // H=64) 995/1085 against 1049/1111.  With a fixed softmax reference the
-  // streaming kernel's warpgroups no longer hand the row maximum to each other
-  // and it wins from 2048 keys on (the same shapes, ping-pong against streaming:
-  // 599/857 against 580/843; 760/967 against 774/988; 927/1064 against 962/1093;
-  // 998/1089 against 1072/1151).
+  // Which kernel.  Left alone the launcher takes the decoupled kernel
+  // (fa_decoupled_sm100.cu) for every shape; WAVE_CUDA_FA_KERNEL=
+  // pingpong|stream|pair|decoupled forces one (a knob for measurements and the
+  // tests; results agree to rounding).  Measured on one B200, inputs uniform in
+  // [-1, 1), TFLOP/s sustained with the kernels taking turns / in 10-launch
+  // bursts from idle, ping-pong | streaming | decoupled:
+  //   causal, adaptive   S=1024 551|542|625 / 668|624|704   S=2048 723|735|800 / 859|842|906
+  //                      S=4096 886|928|985 / 1095|1036|1113  S=8192 952|1051|1069 / 1184|1151|1213
+  //   full, adaptive     S=1024 821|819|874 / 1004|942|993   S=2048 938|975|980 / 1140|1089|1125
+  //                      S=4096 1010|1085|1085 / 1244|1196|1238  S=8192 1045|1155|1135 / 1299|1251|1290
+  //   causal, fixed ref  S=1024 572|590|633 / 699|686|725   S=4096 873|1026|1040 / 1125|1127|1171
+  //   full, fixed ref    S=2048 924|1076|1049 / 1163|1174|1199  S=8192 1031|1213|1246 / 1330|1331|1396
+  // (B*H = 1024, 256, 512, 128 heads for the four lengths).
   {
-    const bool stream_kernel = env.fa_kernel ? env.fa_kernel == 2
-                                             : p.seq_k >= (p.fixed_ref ? kStreamFromSeqKFixedRef : kStreamFromSeqK);
-    if (stream_kernel) {
+    const int kernel = env.fa_kernel ? env.fa_kernel : 4;
+    if (kernel == 2) {
       const int rc = launch_flash_attention_stream(params, extra, tq, tk, tv, poly, sm_count, stream);
       ticket_launched(slot, stream);
       return rc;
     }
-    // WAVE_CUDA_FA_KERNEL=pair: the CTA-pair kernel (needs an even number of SMs).
-    if (env.fa_kernel == 3 && sm_count >= 2) {
+    if (kernel == 4) {
+      const int rc = launch_flash_attention_decoupled(params, extra, tq, K, V, poly, env.fa_stagger, sm_count, stream);
+      ticket_launched(slot, stream);
+      return rc;
+    }
+    // The CTA-pair kernel needs an even number of SMs.
+    if (kernel == 3 && sm_count >= 2) {
       const int rc = launch_flash_attention_pair(params, extra, tq, K, tv, poly, sm_count, stream);
       ticket_launched(slot, stream);
       return rc;
@@ -978,6 +980,12 @@ cudaError_t fa_read_status(int out[4], bool clear) {
   if (err != cudaSuccess)
     return err;
   err = fa_pair_read_status(other, clear);
+  if (err == cudaSuccess && out[0] == 0 && other[0] != 0)
+    for (int i = 0; i < 4; ++i)
+      out[i] = other[i];
+  if (err != cudaSuccess)
+    return err;
+  err = fa_decoupled_read_status(other, clear);
   if (err == cudaSuccess && out[0] == 0 && other[0] != 0)
     for (int i = 0; i < 4; ++i)
       out[i] = other[i];

@@ -49,6 +49,14 @@ cudaError_t fa_stream_read_status(int out[4], bool clear);
 int launch_flash_attention_pair(const FaParams &p, const FaExtra &extra, const CUtensorMap &tq, const void *K,
                                 const CUtensorMap &tv, int poly, int sm_count, cudaStream_t stream);
 cudaError_t fa_pair_read_status(int out[4], bool clear);
+// The decoupled kernel (fa_decoupled_sm100.cu): 256-row work items, 80-key
+// blocks, P beside S in tensor memory so that Q*K^T of a tile's next block runs
+// during its softmax.  `tq` has boxes of 64 elements x 128 rows; K's and V's
+// maps (64 x 80) are built inside.  `stagger_cycles` < 0: the kernel's own
+// default (it replaces p.stagger).  `p.ticket` as above.
+int launch_flash_attention_decoupled(const FaParams &p, const FaExtra &extra, const CUtensorMap &tq, const void *K,
+                                     const void *V, int poly, int stagger_cycles, int sm_count, cudaStream_t stream);
+cudaError_t fa_decoupled_read_status(int out[4], bool clear);
 
 // Provided by the backend: rank-2/3 tensor map over 16-bit elements with the
 // 128-byte swizzle and zero fill outside the tensor.

@@ -90,7 +90,7 @@ EnvKnobs read_env() {
   if (const char *v = getenv("WAVE_CUDA_GEMM_COL_SWAP"))
     e.gemm_col_swap = strcmp(v, "0") != 0;
   if (const char *v = getenv("WAVE_CUDA_FA_KERNEL"))
-    e.fa_kernel = !strcmp(v, "pingpong") ? 1 : !strcmp(v, "stream") ? 2 : !strcmp(v, "pair") ? 3 : 0;
+    e.fa_kernel = !strcmp(v, "pingpong") ? 1 : !strcmp(v, "stream") ? 2 : !strcmp(v, "pair") ? 3 : !strcmp(v, "decoupled") ? 4 : 0;
   if (const char *v = getenv("WAVE_CUDA_FA_POLY"))
     e.fa_poly = atoi(v);
   if (const char *v = getenv("WAVE_CUDA_FA_STAGGER")) {

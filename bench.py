@@ -48,7 +48,7 @@ NVLINK_PEER_GBS = 770.0  # measured peer copy per direction on this pool (nomina
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the single-GPU
 # workload from one ncu capture of the same kernel (summaries under
 # profiles/, each captured at the workload's full size).
-NCU_TRAFFIC_BYTES = {"gemm": 1167.68e6, "fa": 2135.65e6, "skinny": 477.11e6, "fa_published": 1055.49e6}
+NCU_TRAFFIC_BYTES = {"gemm": 1167.68e6, "fa": 2137.99e6, "skinny": 477.11e6, "fa_published": 1059.24e6}
 
 WORKLOADS = {
     "gemm": dict(name="gemm_bf16_8192x8192x8192_f32acc_bf16out", M=8192, N=8192, K=8192),
@@ -769,8 +769,7 @@ def measure_workload(torch, wc, sh, workload, rank, world, strong, steps, warmup
         cpu = cpu_baseline(workload)
         res["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
     res["plan"] = wc.gemm_plan(work.desc) if work.kind == "gemm" else {
-        "work_item_rows": 128 if (WORKLOADS[workload]["S"] >= 6144 or WORKLOADS[workload].get("qk_max_abs")) else 256,
-        "heads_per_gpu": work.hl}
+        "work_item_rows": 256, "keys_per_block": 80, "heads_per_gpu": work.hl}
     del work
     torch.cuda.empty_cache()
     return res

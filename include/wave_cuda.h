@@ -220,14 +220,15 @@ int wave_cuda_gemm_plan_for_sms(const wave_gemm_desc *desc, int sm_count, int ha
  * (wave_flash_attention.py:596-600), probabilities rounded to io_type before
  * P*V, output rounded once to io_type.  `causal` keeps key <= query (top-left
  * aligned; an extension, the reference's Wave kernel is non-causal).
- * Two kernels compute it (256-row work items with two Q tiles ping-ponging,
- * or 128-row work items with double-buffered scores); the library picks by the
- * key sequence length (the second from 6144 keys on, from 2048 with qk_max_abs),
- * WAVE_CUDA_FA_KERNEL=pingpong|stream overrides,
+ * Four kernels compute it: 256-row work items whose two Q tiles take K/V in
+ * blocks of 80 keys with scores and probabilities side by side in tensor
+ * memory (the one the library uses); the same tiles ping-ponging over 128-key
+ * blocks; 128-row work items with double-buffered scores; CTA pairs on 512-row
+ * work items.  WAVE_CUDA_FA_KERNEL=decoupled|pingpong|stream|pair forces one,
  * WAVE_CUDA_FA_POLY=0..4 sets the eighths of the exponentials evaluated as a
  * polynomial on the FMA pipe, WAVE_CUDA_FA_STAGGER=<cycles> the one-off offset
- * between the streaming kernel's two softmax warpgroups in fixed-reference mode
- * (measurement knobs; the results agree within the rounding of the exponential).
+ * between the two softmax warpgroups (measurement knobs; the results agree
+ * within the rounding of the exponential and of the running maximum's steps).
  * Launches in flight: each launch draws its work items from one of 64 device
  * counters per GPU, handed out in turn.  The launch that comes round to a
  * counter is ordered (by an event) behind the launch that used it 64 launches

@@ -18,11 +18,12 @@ from _util import env_knobs, to_device_bits
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(params=["pingpong", "stream", "pair"], autouse=True)
+@pytest.fixture(params=["pingpong", "stream", "pair", "decoupled"], autouse=True)
 def fa_kernel(request, wc):
-    """Every test runs on all three attention kernels (two Q tiles ping-ponging;
-    one Q tile with double-buffered scores; CTA pairs on 512-row work items).
-    Left alone, the library picks one by the shape."""
+    """Every test runs on all four attention kernels (two Q tiles ping-ponging;
+    one Q tile with double-buffered scores; CTA pairs on 512-row work items;
+    80-key blocks with P beside S in tensor memory).  Left alone, the library
+    takes the last one."""
     with env_knobs(wc, WAVE_CUDA_FA_KERNEL=request.param):
         yield request.param
 
