@@ -165,7 +165,9 @@ def run(cmd, dry_run):
     text = proc.stdout
     us = re.search(r"^median_per_launch_us: ([0-9.]+)", text, re.M) or re.search(r"^per_launch_us: ([0-9.]+)", text, re.M)
     tf = re.search(r"^median_tflops: ([0-9.]+)", text, re.M) or re.search(r"^tflops: ([0-9.]+)", text, re.M)
-    check = "passed" if "output_check: passed" in text else ("skipped" if "--no-check" in cmd else "failed")
+    # the GEMM tool checks unless told not to; the attention tool checks when asked
+    asked = "--check" in cmd if any("wave_fa_gfx950" in c for c in cmd) else "--no-check" not in cmd
+    check = "passed" if "output_check: passed" in text else ("failed" if asked else "skipped")
     return (float(us.group(1)) if us else float("nan"), float(tf.group(1)) if tf else float("nan"), check,
             proc.returncode, proc.stderr)
 
