@@ -103,8 +103,14 @@ def test_normal_inputs_config_shape_small(cuda, wc, oracle, causal):
 
 
 @pytest.mark.parametrize("Sq,Sk,causal", [(144, 400, False), (272, 272, True), (16, 16, True), (128, 128, False),
-                                          (400, 144, False)])
+                                          (400, 144, False),
+                                          # around multiples of 80 keys (the decoupled kernel's block) and of 128
+                                          (80, 80, True), (96, 96, True), (176, 160, False), (336, 336, True),
+                                          (640, 640, True), (256, 1040, False)])
 def test_ragged_lengths(cuda, wc, oracle, Sq, Sk, causal):
+    """Lengths that are not whole numbers of K/V blocks or Q tiles, for every
+    kernel: the last block is partly past the end of K, the causal diagonal
+    crosses blocks at every offset, a work item may have one tile only."""
     t = oracle.BF16
     q, k, v = normal_qkv(oracle, 3, Sq, Sk, 128, t, seed=Sq + Sk)
     got = run_fa(cuda, wc, q, k, v, "bf16", 1, 3, causal)
