@@ -80,7 +80,12 @@ constexpr int kSoftmaxRegs = 216;
 static_assert((kLaunchRegs - kIssueRegs) * 128 >= (kSoftmaxRegs - kLaunchRegs) * 256,
               "setmaxnreg.inc would wait forever: warpgroup 0 does not release enough registers");
 static_assert(kIssueRegs % 8 == 0 && kSoftmaxRegs % 8 == 0, "setmaxnreg takes multiples of 8");
-static_assert(kSmemBytes + kExtraStageBytes <= 227 * 1024, "does not fit the shared memory of an SM");
+// The variants with further output buffers add a staging area behind everything
+// else: one Q tile's worth of 16-bit O (also used as eight 2 KB per-warp slots
+// by the paths that store to the further buffers from registers).
+constexpr int kStageBytes = kBlockM * kD * 2;
+static_assert(kStageBytes >= kExtraStageBytes, "the per-warp slots live in the staging area");
+static_assert(kSmemBytes + kStageBytes <= 227 * 1024, "does not fit the shared memory of an SM");
 
 struct FaShared {
   uint64_t item_full[2], item_empty[2]; // work-item hand-off from the Q/K loader to the other roles
@@ -91,6 +96,8 @@ struct FaShared {
   uint64_t p_full[2];  // probabilities are in tensor memory
   uint64_t pv_done[2]; // P*V has run: P may be overwritten, O is at rest
   uint64_t o_free[2];  // the epilogue has read O out
+  uint64_t stg_full;   // further outputs: a tile's O is in the staging area (one arrival per warp of the tile)
+  uint64_t stg_free;   // ... and the bulk copies to the further buffers have read it
   uint32_t tmem_base;
   int abort_flag;
   int item_idx[2];
@@ -203,6 +210,8 @@ fa_decoupled_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       mbar_init(&sh->pv_done[s], 1);
       mbar_init(&sh->o_free[s], 4);
     }
+    mbar_init(&sh->stg_full, 4);
+    mbar_init(&sh->stg_free, 1);
     sh->abort_flag = 0;
     fence_barrier_init();
   }
@@ -443,6 +452,13 @@ fa_decoupled_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     constexpr bool bf16 = kBf16;
     uint32_t blk_n = 0; // blocks this tile has taken so far (s_full / pv_done phases)
     bool ok = true;
+    // Further outputs in the 16-bit type through plain addresses: a tile's O is
+    // staged in shared memory and sent to every further buffer with bulk copies
+    // (the tile's rows are one contiguous piece of O), so that no softmax thread
+    // waits for stores that cross NVLink.  The two tiles take turns on the one
+    // staging area, in the order tile 0, tile 1 of each item.
+    const bool bulk_out = kExtra && !ex.multimem && !p.out_f32;
+    uint32_t stage_uses = 0; // uses of the staging area before this item (stg_full / stg_free phases)
 
     for (uint32_t item_n = 0; ok; ++item_n) {
     const int slot = item_n & 1;
@@ -602,6 +618,13 @@ fa_decoupled_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         const float inv = 1.0f / l;
         const bool live = q_row < p.seq_q;
         const int esize = p.out_f32 ? 4 : 2;
+        const uint32_t my_use = stage_uses + ((t == 1 && w.n_blocks[0] > 0) ? 1u : 0u);
+        if (bulk_out && my_use > 0 && !mbar_wait(&sh->stg_free, (my_use - 1) & 1, abort_flag)) {
+          if (lane == 0)
+            fad_report(kStatusWaitTimeout, 2 + t, 71);
+          ok = false;
+          break;
+        }
         uint8_t *out_row = static_cast<uint8_t *>(p.O) +
                            (static_cast<size_t>(bh) * p.seq_q + static_cast<size_t>(live ? q_row : 0)) *
                                static_cast<size_t>(p.head_dim) * esize;
@@ -636,7 +659,13 @@ fa_decoupled_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 if (cc + 8 * v < p.head_dim)
                   dst[v] = make_uint4(wv[4 * v], wv[4 * v + 1], wv[4 * v + 2], wv[4 * v + 3]);
             }
-            if constexpr (kExtra) {
+            if (kExtra && bulk_out) {
+              uint4 *dst = reinterpret_cast<uint4 *>(extra_stage + static_cast<size_t>(row) * p.head_dim * 2 + cc * 2);
+#pragma unroll
+              for (int v = 0; v < 4; ++v)
+                if (cc + 8 * v < p.head_dim)
+                  dst[v] = make_uint4(wv[4 * v], wv[4 * v + 1], wv[4 * v + 2], wv[4 * v + 3]);
+            } else if constexpr (kExtra) {
               const int first_row = q_row - lane; // a warp's 32 rows are consecutive
               store_extra_chunk_16bit(ex, extra_stage + (warp - 4) * 2048, lane, wv,
                                       (static_cast<size_t>(bh) * p.seq_q + first_row) * p.head_dim * 2 + static_cast<size_t>(cc) * 2,
@@ -652,9 +681,39 @@ fa_decoupled_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         __syncwarp();
         if (lane == 0)
           mbar_arrive(&sh->o_free[t]);
+        if (bulk_out) {
+          fence_proxy_async_smem(); // the staged rows, before the bulk copies read them
+          __syncwarp();
+          if (lane == 0)
+            mbar_arrive(&sh->stg_full);
+          if (quarter == 0) {
+            // The tile's first warp waits for all four; one of its threads sends
+            // the tile and waits only until the copies have READ the staging area.
+            if (!mbar_wait(&sh->stg_full, my_use & 1, abort_flag)) {
+              if (lane == 0)
+                fad_report(kStatusWaitTimeout, 2 + t, 72);
+              ok = false;
+            } else if (lane == 0) {
+              const int q0 = q_row - row;
+              const int rows_live = min(kBlockM, p.seq_q - q0);
+              const uint32_t bytes = static_cast<uint32_t>(rows_live) * static_cast<uint32_t>(p.head_dim) * 2u;
+              const size_t off = (static_cast<size_t>(bh) * p.seq_q + q0) * static_cast<size_t>(p.head_dim) * 2;
+#pragma unroll 1
+              for (int x = 0; x < ex.n; ++x)
+                bulk_store_global(static_cast<uint8_t *>(ex.o[x]) + off, extra_stage, bytes);
+              tma_store_commit();
+              tma_store_wait_read<0>();
+              mbar_arrive(&sh->stg_free);
+            }
+          }
+          __syncwarp();
+        }
       }
     }
+    stage_uses += (w.n_blocks[0] > 0) + (w.n_blocks[1] > 0);
     } // work items
+    if (bulk_out && quarter == 0 && lane == 0)
+      tma_store_wait<0>(); // this thread's copies have landed before the kernel ends
   }
 
   tc_fence_before_sync();
@@ -732,7 +791,7 @@ int launch_flash_attention_decoupled(const FaParams &p, const FaExtra &extra, co
     // compiler actually gave it; refuse to launch rather than risk a grow
     // request that can never be satisfied.
     KernelInfo info;
-    const int smem_bytes = kSmemBytes + (extra.n > 0 ? kExtraStageBytes : 0);
+    const int smem_bytes = kSmemBytes + (extra.n > 0 ? kStageBytes : 0);
     err = prepare_kernel(kernel, smem_bytes, &info);
     if (err != cudaSuccess)
       return;

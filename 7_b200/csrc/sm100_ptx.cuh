@@ -152,6 +152,15 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap *tmap, const void
                "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
                : "memory");
 }
+// Untiled bulk copy shared memory -> global memory (any global address this GPU
+// can write, a peer's mapped memory included): both addresses 16-byte aligned,
+// the size a multiple of 16 bytes; completion through the issuing thread's
+// bulk groups like the tiled stores.
+__device__ __forceinline__ void bulk_store_global(void *gmem_dst, const void *smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst), "r"(smem_u32(smem_src)),
+               "r"(bytes)
+               : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void tma_store_wait_read() {
   asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");

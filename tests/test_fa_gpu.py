@@ -312,6 +312,9 @@ def test_more_queued_launches_than_ticket_counters(cuda, wc, oracle):
     (6, 512, 128, True, False),
     (3, 384, 64, False, False),     # head dimension below 128: only the first 64 columns exist
     (2, 272, 128, True, True),      # ragged length, f32 output
+    (3, 400, 96, True, False),      # ragged length and a narrow head in the 16-bit type
+    (80, 1024, 128, True, False),   # more work items than SMs: a CTA's items share its staging area in turn
+    (80, 512, 128, False, False),   # ... with both tiles of an item finishing together
 ])
 def test_multi_output_writes_every_target(cuda, wc, oracle, BH, S, D, causal, out_f32):
     """wave_cuda_flash_attention_fwd_multi_output: O lands in every target (on
