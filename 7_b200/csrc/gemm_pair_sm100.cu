@@ -140,11 +140,21 @@ __device__ __forceinline__ void pair_report(int code, int role, int detail) {
   }
 }
 
-template <int OUT, int PN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
-gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const __grid_constant__ CUtensorMap tmap_b_half, const __grid_constant__ CUtensorMap tmap_c,
-                 const GemmParams p) {
+// Tensor maps over the further copies of C of a launch (same shape, strides
+// and box as the map of C itself): a kernel parameter of the variant that
+// sends every finished piece to them with TMA stores, and of that variant only.
+struct PairExtraMaps {
+  CUtensorMap m[7];
+};
+
+// The kernel's body.  kTmaExtra: the further copies of C (p.n_extra of them,
+// plain addresses) get each 128 x 64 piece by a TMA store from the same staging
+// tile as C itself (`em`); otherwise they are written with stores from the
+// epilogue warps (the only way to a multicast address).
+template <int OUT, int PN, bool kTmaExtra>
+__device__ __forceinline__ void gemm_pair_body(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b,
+                                               const CUtensorMap &tmap_b_half, const CUtensorMap &tmap_c,
+                                               const GemmParams &p, const PairExtraMaps *em) {
   using T = typename OutT<OUT>::type;
   using Cfg = PairCfg<PN>;
   constexpr int kPairN = PN;
@@ -451,9 +461,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             if (warp == 2 && lane == 0) {
               tma_store_2d_evict_first(&tmap_c, buf, n_tile0 + n_off + c,
                                        mb * kPairM + static_cast<int>(rank) * kRows);
+              if constexpr (kTmaExtra) {
+                // The same piece to every further copy of C (peer GPUs' memory when
+                // the column blocks are being gathered): one more TMA store each,
+                // in the same bulk group; no thread touches the data again.
+#pragma unroll 1
+                for (int x = 0; x < p.n_extra; ++x)
+                  tma_store_2d(&em->m[x], buf, n_tile0 + n_off + c, mb * kPairM + static_cast<int>(rank) * kRows);
+              }
               tma_store_commit();
             }
-            if (p.n_extra > 0) {
+            if (!kTmaExtra && p.n_extra > 0) {
               // The same 128 x 64 piece to every further copy of C (peer GPUs'
               // memory when the column blocks are being gathered): the four warps
               // read the staging tile back, un-swizzled, and write whole 128-byte
@@ -558,9 +576,37 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 }
 
 template <int OUT, int PN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_b_half, const __grid_constant__ CUtensorMap tmap_c,
+                 const GemmParams p) {
+  gemm_pair_body<OUT, PN, false>(tmap_a, tmap_b, tmap_b_half, tmap_c, p, nullptr);
+}
+
+template <int OUT, int PN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_pair_extra_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                       const __grid_constant__ CUtensorMap tmap_b_half, const __grid_constant__ CUtensorMap tmap_c,
+                       const GemmParams p, const __grid_constant__ PairExtraMaps em) {
+  gemm_pair_body<OUT, PN, true>(tmap_a, tmap_b, tmap_b_half, tmap_c, p, &em);
+}
+
+template <int OUT, int PN>
 cudaError_t launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tbh, const CUtensorMap &tc,
-                        const GemmParams &p, int grid, cudaStream_t stream) {
+                        const GemmParams &p, const CUtensorMap *extra_maps, int grid, cudaStream_t stream) {
   constexpr int smem = PairCfg<PN>::kSmemBytes;
+  if constexpr (OUT != WAVE_GEMM_OUT_F32) {
+    if (extra_maps) {
+      PairExtraMaps em;
+      for (int i = 0; i < 7; ++i)
+        em.m[i] = extra_maps[i < p.n_extra ? i : 0];
+      cudaError_t err = prepare_kernel(gemm_pair_extra_kernel<OUT, PN>, smem, nullptr);
+      if (err != cudaSuccess)
+        return err;
+      gemm_pair_extra_kernel<OUT, PN><<<grid, kThreads, smem, stream>>>(ta, tb, tbh, tc, p, em);
+      return cudaGetLastError();
+    }
+  }
   cudaError_t err = prepare_kernel(gemm_pair_kernel<OUT, PN>, smem, nullptr);
   if (err != cudaSuccess)
     return err;
@@ -570,14 +616,14 @@ cudaError_t launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const CUte
 
 template <int PN>
 cudaError_t launch_pair_out(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tbh, const CUtensorMap &tc,
-                            const GemmParams &p, int grid, cudaStream_t stream) {
+                            const GemmParams &p, const CUtensorMap *extra_maps, int grid, cudaStream_t stream) {
   switch (p.out_type) {
   case WAVE_GEMM_OUT_F32:
-    return launch_pair<WAVE_GEMM_OUT_F32, PN>(ta, tb, tbh, tc, p, grid, stream);
+    return launch_pair<WAVE_GEMM_OUT_F32, PN>(ta, tb, tbh, tc, p, extra_maps, grid, stream);
   case WAVE_GEMM_OUT_F16:
-    return launch_pair<WAVE_GEMM_OUT_F16, PN>(ta, tb, tbh, tc, p, grid, stream);
+    return launch_pair<WAVE_GEMM_OUT_F16, PN>(ta, tb, tbh, tc, p, extra_maps, grid, stream);
   case WAVE_GEMM_OUT_BF16:
-    return launch_pair<WAVE_GEMM_OUT_BF16, PN>(ta, tb, tbh, tc, p, grid, stream);
+    return launch_pair<WAVE_GEMM_OUT_BF16, PN>(ta, tb, tbh, tc, p, extra_maps, grid, stream);
   }
   return cudaErrorInvalidValue;
 }
@@ -595,16 +641,18 @@ int gemm_pair_box_rows() { return kRows; }
 // (read only when tile_n is 256 and p.split_from < p.num_tiles) one of 64 rows,
 // `tmap_c` (read only when p.c_tma is set) a box of 64 columns x 128 rows over
 // the row-major 16-bit output.  Rows of C a store may touch beyond M, and
-// columns beyond N, are clipped by the tensor map.
+// columns beyond N, are clipped by the tensor map.  `extra_maps` (or null):
+// p.n_extra maps like `tmap_c` over the further copies of C, which then get
+// every piece by TMA store (16-bit output with p.c_tma only).
 cudaError_t launch_gemm_pair(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, const CUtensorMap &tmap_b_half,
-                             const CUtensorMap &tmap_c, const GemmParams &p, int tile_n, int grid,
-                             cudaStream_t stream) {
+                             const CUtensorMap &tmap_c, const GemmParams &p, const CUtensorMap *extra_maps, int tile_n,
+                             int grid, cudaStream_t stream) {
   if (tile_n == 128)
-    return launch_pair_out<128>(tmap_a, tmap_b, tmap_b_half, tmap_c, p, grid, stream);
+    return launch_pair_out<128>(tmap_a, tmap_b, tmap_b_half, tmap_c, p, extra_maps, grid, stream);
   if (tile_n > 128 && tile_n <= 256 && tile_n % 32 == 0) {
     GemmParams q = p;
     q.pair_tile_n = tile_n;
-    return launch_pair_out<256>(tmap_a, tmap_b, tmap_b_half, tmap_c, q, grid, stream);
+    return launch_pair_out<256>(tmap_a, tmap_b, tmap_b_half, tmap_c, q, extra_maps, grid, stream);
   }
   return cudaErrorInvalidValue;
 }

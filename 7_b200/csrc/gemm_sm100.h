@@ -64,8 +64,8 @@ int gemm_pair_tile_m();
 int gemm_pair_tile_n();
 int gemm_pair_box_rows();
 cudaError_t launch_gemm_pair(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b, const CUtensorMap &tmap_b_half,
-                             const CUtensorMap &tmap_c, const GemmParams &p, int tile_n, int grid,
-                             cudaStream_t stream);
+                             const CUtensorMap &tmap_c, const GemmParams &p, const CUtensorMap *extra_maps, int tile_n,
+                             int grid, cudaStream_t stream);
 cudaError_t gemm_pair_read_status(int out[4], bool clear);
 
 } // namespace wave

@@ -858,7 +858,21 @@ int gemm_launch(const wave_gemm_desc *d, const void *A, const void *B, void *C, 
     for (int i = 0; i < n_extra; ++i)
       p.extra_c[i] = extra_c[i];
   }
-  cudaError_t err = plan.pair ? wave::launch_gemm_pair(ta, tb, tbh, tc, p, plan.tile_n, plan.grid, static_cast<cudaStream_t>(stream))
+  // Plain further targets (peer GPUs' copies of C) get a tensor map each: the
+  // kernel sends them every finished piece with one more TMA store.
+  CUtensorMap extra_maps[7];
+  const bool tma_extra = n_extra > 0 && !extra_multimem;
+  if (tma_extra) {
+    const uint64_t dims[2] = {static_cast<uint64_t>(plan.Nk), static_cast<uint64_t>(plan.Mk)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(ld) * 2};
+    const uint32_t box[2] = {64, static_cast<uint32_t>(wave::gemm_pair_box_rows())};
+    for (int i = 0; i < n_extra; ++i)
+      if ((rc = wave::make_tensor_map_16bit(&extra_maps[i], d->out_type == WAVE_BF16, extra_c[i], 2, dims, strides, box)) !=
+          WAVE_OK)
+        return rc;
+  }
+  cudaError_t err = plan.pair ? wave::launch_gemm_pair(ta, tb, tbh, tc, p, tma_extra ? extra_maps : nullptr, plan.tile_n,
+                                                       plan.grid, static_cast<cudaStream_t>(stream))
                               : wave::launch_gemm(ta, tb, tc, p, plan.tile_n, plan.grid, static_cast<cudaStream_t>(stream));
   if (err != cudaSuccess)
     return cuda_fail(err, "gemm launch");
