@@ -402,7 +402,7 @@ def time_gather(torch, sh, work, dist, stream, world) -> tuple[dict, object]:
 def time_fused_gather(torch, wc, sh, work, dist, stream, rank, world, oracle) -> dict:
     """The all-gather fused into the kernel: every rank writes its block (GEMM:
     N-column block of C; attention: (batch, head) slab of O) straight into every
-    rank's copy of the full output -- peer-mapped memory, plain stores out of
+    rank's copy of the full output -- peer-mapped memory, TMA / bulk stores out of
     the epilogue while the kernel computes on, or one multimem.st per 16 bytes to
     an NVLink multicast address -- followed by a one-element all-reduce as the
     barrier after which the copies may be read.  Timed as one step, max over
@@ -471,7 +471,7 @@ def time_fused_gather(torch, wc, sh, work, dist, stream, rank, world, oracle) ->
     res = timed(unicast)
     entry = "wave_cuda_gemm_multi_output" if gemm else "wave_cuda_flash_attention_fwd_multi_output"
     res.update({"kernel": f"{entry}: this rank's block written to every rank's copy of the output from the kernel's "
-                          "epilogue over NVLink (peer-mapped memory, plain stores), then a one-element all-reduce as barrier",
+                          "epilogue over NVLink (peer-mapped memory, TMA / bulk stores from shared memory), then a one-element all-reduce as barrier",
                 "launches": 2 * (iters + 3), "bytes_sent_per_rank": (world - 1) * block_bytes,
                 "sent_gbs_per_rank": (world - 1) * block_bytes / (res["ms_per_step"] * 1e-3) / 1e9})
     if out.multicast_ptr:

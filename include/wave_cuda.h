@@ -137,7 +137,7 @@ int wave_cuda_gemm(const wave_gemm_desc *desc, const void *A, const void *B, voi
 /* No counterpart in the reference, which is single-device.  The GEMM with its
  * result written to several buffers at once: C_targets[0] exactly as
  * wave_cuda_gemm writes C, and every finished 128 x 64 piece of it also, with
- * plain 16-byte stores out of the epilogue's staging tile, to
+ * one more TMA store each out of the epilogue's staging tile, to
  * C_targets[1 .. n_targets-1] at the same offsets and leading dimension.  This
  * is the all-gather of an N-column-sharded GEMM fused into the kernel: rank r
  * of a job whose ranks hold peer-mapped copies of the full C (column-major:
