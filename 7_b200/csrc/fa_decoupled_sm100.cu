@@ -99,7 +99,7 @@ struct FaShared {
   uint64_t pv_done[2]; // P*V has run: P may be overwritten, O is at rest
   uint64_t o_free[2];  // the epilogue has read O out
   uint64_t stg_full;   // further outputs: a tile's O is in the staging area (one arrival per warp of the tile)
-  uint64_t stg_free;   // ... and the bulk copies to the further buffers have read it
+  uint64_t stg_free;   // ... and has been read out of it again (one arrival per warp of the tile)
   uint32_t tmem_base;
   int abort_flag;
   int item_idx[2];
@@ -213,7 +213,7 @@ fa_decoupled_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       mbar_init(&sh->o_free[s], 4);
     }
     mbar_init(&sh->stg_full, 4);
-    mbar_init(&sh->stg_free, 1);
+    mbar_init(&sh->stg_free, 4);
     sh->abort_flag = 0;
     fence_barrier_init();
   }
@@ -459,7 +459,7 @@ fa_decoupled_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     // (the tile's rows are one contiguous piece of O), so that no softmax thread
     // waits for stores that cross NVLink.  The two tiles take turns on the one
     // staging area, in the order tile 0, tile 1 of each item.
-    const bool bulk_out = kExtra && !ex.multimem && !p.out_f32;
+    const bool bulk_out = kExtra && !p.out_f32; // plain targets: bulk copies; a multicast target: multimem.st from the staged tile
     uint32_t stage_uses = 0; // uses of the staging area before this item (stg_full / stg_free phases)
 
     for (uint32_t item_n = 0; ok; ++item_n) {
@@ -661,18 +661,12 @@ fa_decoupled_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 if (cc + 8 * v < p.head_dim)
                   dst[v] = make_uint4(wv[4 * v], wv[4 * v + 1], wv[4 * v + 2], wv[4 * v + 3]);
             }
-            if (kExtra && bulk_out) {
+            if constexpr (kExtra) { // 16-bit O: into the staging area, row by row as it lies in memory
               uint4 *dst = reinterpret_cast<uint4 *>(extra_stage + static_cast<size_t>(row) * p.head_dim * 2 + cc * 2);
 #pragma unroll
               for (int v = 0; v < 4; ++v)
                 if (cc + 8 * v < p.head_dim)
                   dst[v] = make_uint4(wv[4 * v], wv[4 * v + 1], wv[4 * v + 2], wv[4 * v + 3]);
-            } else if constexpr (kExtra) {
-              const int first_row = q_row - lane; // a warp's 32 rows are consecutive
-              store_extra_chunk_16bit(ex, extra_stage + (warp - 4) * 2048, lane, wv,
-                                      (static_cast<size_t>(bh) * p.seq_q + first_row) * p.head_dim * 2 + static_cast<size_t>(cc) * 2,
-                                      static_cast<size_t>(p.head_dim) * 2, min(32, max(0, p.seq_q - first_row)),
-                                      min(64, (p.head_dim - cc) * 2));
             }
           }
         }
@@ -688,7 +682,27 @@ fa_decoupled_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           __syncwarp();
           if (lane == 0)
             mbar_arrive(&sh->stg_full);
-          if (quarter == 0) {
+          const int q0 = q_row - row;
+          const int rows_live = min(kBlockM, p.seq_q - q0);
+          const uint32_t bytes = static_cast<uint32_t>(rows_live) * static_cast<uint32_t>(p.head_dim) * 2u;
+          const size_t off = (static_cast<size_t>(bh) * p.seq_q + q0) * static_cast<size_t>(p.head_dim) * 2;
+          if (ex.multimem) {
+            // One multimem.st per 16 bytes, the tile's 128 threads side by side
+            // (a warp writes 512 contiguous bytes per instruction); the switch
+            // delivers each to every GPU's copy.  Every warp needs all rows staged.
+            if (!mbar_wait(&sh->stg_full, my_use & 1, abort_flag)) {
+              if (lane == 0)
+                fad_report(kStatusWaitTimeout, 2 + t, 72);
+              ok = false;
+            } else {
+#pragma unroll 4
+              for (uint32_t b = static_cast<uint32_t>(row) * 16u; b < bytes; b += kBlockM * 16u)
+                multimem_st_16B(static_cast<uint8_t *>(ex.o[0]) + off + b, *reinterpret_cast<const uint4 *>(extra_stage + b));
+              __syncwarp();
+              if (lane == 0)
+                mbar_arrive(&sh->stg_free);
+            }
+          } else if (quarter == 0) {
             // The tile's first warp waits for all four; one of its threads sends
             // the tile and waits only until the copies have READ the staging area.
             if (!mbar_wait(&sh->stg_full, my_use & 1, abort_flag)) {
@@ -696,10 +710,6 @@ fa_decoupled_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 fad_report(kStatusWaitTimeout, 2 + t, 72);
               ok = false;
             } else if (lane == 0) {
-              const int q0 = q_row - row;
-              const int rows_live = min(kBlockM, p.seq_q - q0);
-              const uint32_t bytes = static_cast<uint32_t>(rows_live) * static_cast<uint32_t>(p.head_dim) * 2u;
-              const size_t off = (static_cast<size_t>(bh) * p.seq_q + q0) * static_cast<size_t>(p.head_dim) * 2;
 #pragma unroll 1
               for (int x = 0; x < ex.n; ++x)
                 bulk_store_global(static_cast<uint8_t *>(ex.o[x]) + off, extra_stage, bytes);
@@ -707,6 +717,8 @@ fa_decoupled_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
               tma_store_wait_read<0>();
               mbar_arrive(&sh->stg_free);
             }
+          } else if (lane == 0) {
+            mbar_arrive(&sh->stg_free); // this warp does not read the staging area
           }
           __syncwarp();
         }
@@ -714,7 +726,7 @@ fa_decoupled_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     }
     stage_uses += (w.n_blocks[0] > 0) + (w.n_blocks[1] > 0);
     } // work items
-    if (bulk_out && quarter == 0 && lane == 0)
+    if (bulk_out && !ex.multimem && quarter == 0 && lane == 0)
       tma_store_wait<0>(); // this thread's copies have landed before the kernel ends
   }
 
