@@ -17,7 +17,8 @@
 // maximum moves in steps of 80 keys instead of 128, so results agree with the
 // other kernels to rounding, not bit for bit.  No load uses cluster multicast.
 // The variants with further output buffers (other GPUs' copies of O) stage a
-// tile's O in shared memory and send it with one bulk copy per buffer.
+// tile's O in shared memory and send it with one bulk copy per buffer, or to a
+// multicast address with multimem stores from the staged tile.
 #include "../../include/wave_cuda.h"
 #include "backend_env.h"
 #include "fa_sm100.h"
