@@ -15,6 +15,7 @@ struct EnvKnobs {
   bool gemm_tma_store = true;    // WAVE_CUDA_GEMM_TMA_STORE=0: per-thread stores instead of the TMA-store epilogue
   int gemm_l2_hints = 2;         // WAVE_CUDA_GEMM_L2_HINTS: 0 none, 1 A evict-last + B evict-first, 2 A evict-last only
   bool gemm_col_swap = true;     // WAVE_CUDA_GEMM_COL_SWAP=0: column-major 16-bit C without the operand swap
+  bool gemm_pdl = true;          // WAVE_CUDA_GEMM_PDL=0: GEMM launches without programmatic dependent launch
   int fa_kernel = 0;             // WAVE_CUDA_FA_KERNEL: 0 auto, 1 pingpong, 2 stream, 3 pair, 4 decoupled
   int fa_poly = -1;              // WAVE_CUDA_FA_POLY: eighths of the exponentials on the FMA pipe, -1 = each kernel's default
   int fa_stagger = -1;           // WAVE_CUDA_FA_STAGGER: cycles, -1 = the library's default

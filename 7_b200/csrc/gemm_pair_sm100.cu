@@ -195,6 +195,13 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap &tmap_a, const 
   cluster_wait();
   tc_fence_after_sync();
   const uint32_t tmem_base = sh->tmem_base;
+  // Programmatic dependent launch: everything above touched only this CTA's own
+  // state, so it may run while the kernel before this one on the stream is still
+  // finishing; from here on global memory is read and written, which has to wait
+  // for that kernel to be complete.  The next kernel on the stream may be set up
+  // as soon as SMs come free.  (Both are no-ops for a launch without the attribute.)
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
@@ -591,6 +598,23 @@ gemm_pair_extra_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
   gemm_pair_body<OUT, PN, true>(tmap_a, tmap_b, tmap_b_half, tmap_c, p, &em);
 }
 
+// One launch; with `pdl` the stream may begin it (up to its griddepcontrol.wait)
+// while the kernel before it is still finishing.
+template <typename Kernel, typename... Args>
+cudaError_t launch_config(int grid, int smem, cudaStream_t stream, int pdl, Kernel kernel, const Args &...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = static_cast<size_t>(smem);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 template <int OUT, int PN>
 cudaError_t launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tbh, const CUtensorMap &tc,
                         const GemmParams &p, const CUtensorMap *extra_maps, int grid, cudaStream_t stream) {
@@ -603,15 +627,13 @@ cudaError_t launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const CUte
       cudaError_t err = prepare_kernel(gemm_pair_extra_kernel<OUT, PN>, smem, nullptr);
       if (err != cudaSuccess)
         return err;
-      gemm_pair_extra_kernel<OUT, PN><<<grid, kThreads, smem, stream>>>(ta, tb, tbh, tc, p, em);
-      return cudaGetLastError();
+      return launch_config(grid, smem, stream, p.pdl, gemm_pair_extra_kernel<OUT, PN>, ta, tb, tbh, tc, p, em);
     }
   }
   cudaError_t err = prepare_kernel(gemm_pair_kernel<OUT, PN>, smem, nullptr);
   if (err != cudaSuccess)
     return err;
-  gemm_pair_kernel<OUT, PN><<<grid, kThreads, smem, stream>>>(ta, tb, tbh, tc, p);
-  return cudaGetLastError();
+  return launch_config(grid, smem, stream, p.pdl, gemm_pair_kernel<OUT, PN>, ta, tb, tbh, tc, p);
 }
 
 template <int PN>

@@ -147,6 +147,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = sh->tmem_base;
+  // Programmatic dependent launch: the set-up above touched only this CTA's own
+  // state and may run while the kernel before this one on the stream is still
+  // finishing; global memory (operands, C, Stream-K scratch and counters) waits
+  // for that kernel to be complete.  No-ops for a launch without the attribute.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
@@ -425,8 +431,17 @@ cudaError_t launch_one(const CUtensorMap &ta, const CUtensorMap &tb, const CUten
   cudaError_t err = prepare_kernel(gemm_kernel<BN, OUT>, Cfg::kSmemBytes, nullptr);
   if (err != cudaSuccess)
     return err;
-  gemm_kernel<BN, OUT><<<grid, kThreads, Cfg::kSmemBytes, stream>>>(ta, tb, tc, p);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = p.pdl ? 1 : 0; // the stream may begin this launch, up to its griddepcontrol.wait, early
+  return cudaLaunchKernelEx(&cfg, gemm_kernel<BN, OUT>, ta, tb, tc, p);
 }
 
 template <int BN>

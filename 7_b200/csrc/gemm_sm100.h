@@ -48,6 +48,7 @@ struct GemmParams {
   // the last K step of every segment, so that the UMMA thread's wait for it runs
   // out and the bounded-wait unwind can be observed.  Always 0 in the product.
   int test_skip_last_k;
+  int pdl; // host side only: launch with programmatic stream serialization
 };
 
 int gemm_tile_m();

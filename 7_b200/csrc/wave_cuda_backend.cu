@@ -89,6 +89,8 @@ EnvKnobs read_env() {
     e.gemm_l2_hints = atoi(v);
   if (const char *v = getenv("WAVE_CUDA_GEMM_COL_SWAP"))
     e.gemm_col_swap = strcmp(v, "0") != 0;
+  if (const char *v = getenv("WAVE_CUDA_GEMM_PDL"))
+    e.gemm_pdl = strcmp(v, "0") != 0;
   if (const char *v = getenv("WAVE_CUDA_FA_KERNEL"))
     e.fa_kernel = !strcmp(v, "pingpong") ? 1 : !strcmp(v, "stream") ? 2 : !strcmp(v, "pair") ? 3 : !strcmp(v, "decoupled") ? 4 : 0;
   if (const char *v = getenv("WAVE_CUDA_FA_POLY"))
@@ -837,6 +839,7 @@ int gemm_launch(const wave_gemm_desc *d, const void *A, const void *B, void *C, 
   // for measurements).
   const wave::EnvKnobs env = wave::env_knobs();
   p.l2_hints = env.gemm_l2_hints;
+  p.pdl = env.gemm_pdl ? 1 : 0;
   CUtensorMap tc = ta;
   if ((plan.pair || plan.tile_n >= 64) && p.stride_n == 1 && !p.tile_packed && d->out_type != WAVE_F32 &&
       plan.Nk >= 64 && env.gemm_tma_store) {
