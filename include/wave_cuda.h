@@ -90,12 +90,15 @@ void *_mlir_ciface_wave_memref_to_ptr_global_f64(void *memref1d);
  * CTA pairs idle runs as half-width items or, with streamk_workers = 0 and a
  * workspace, has its K iterations dealt over all pairs (Stream-K tail).
  * Column-major 16-bit C is computed as the row-major C^T = B * A^T (operands
- * swapped inside the library; bit-identical results).  The environment
+ * swapped inside the library; bit-identical results).  Launches carry the
+ * programmatic-stream-serialization attribute: a kernel's set-up may overlap
+ * the end of the kernel before it on the stream, its first access to global
+ * memory waits for that kernel to be complete.  The environment
  * variables WAVE_CUDA_GEMM_KERNEL=pair|pair128|single,
  * WAVE_CUDA_GEMM_SPLIT_TAIL=0, WAVE_CUDA_GEMM_STREAMK_TAIL=0,
- * WAVE_CUDA_GEMM_TMA_STORE=0, WAVE_CUDA_GEMM_COL_SWAP=0 and
- * WAVE_CUDA_GEMM_L2_HINTS=0|1|2 override the choices (knobs for measurements;
- * results do not change).                                                    */
+ * WAVE_CUDA_GEMM_TMA_STORE=0, WAVE_CUDA_GEMM_COL_SWAP=0,
+ * WAVE_CUDA_GEMM_L2_HINTS=0|1|2 and WAVE_CUDA_GEMM_PDL=0 override the choices
+ * (knobs for measurements; results do not change).                           */
 typedef struct wave_gemm_desc {
   int M, N, K;                 /* positive multiples of 16 (wave_matmul.py:533-536)      */
   int bm, bn;                  /* waves per workgroup along M / N; bn a power of two      */
